@@ -1,0 +1,150 @@
+// extern "C" surface of libdsv4_prologue.so: argument validation, variant choice, launch.
+// Declarations and the reference interface each entry point replaces: include/dsv4_prologue.h.
+#include <atomic>
+#include <cstdlib>
+
+#include "../../include/dsv4_prologue.h"
+#include "dsv4_common.cuh"
+
+namespace dsv4 {
+namespace {
+std::atomic<int64_t> g_launches{0};
+std::atomic<int> g_variant{-1};  // -1: not initialised from the environment yet
+
+int current_variant() {
+    int v = g_variant.load(std::memory_order_relaxed);
+    if (v < 0) {
+        v = DSV4_VARIANT_AUTO;
+        if (const char* e = std::getenv("DSV4_VARIANT")) {
+            const int parsed = std::atoi(e);
+            if (parsed >= DSV4_VARIANT_AUTO && parsed <= DSV4_VARIANT_BULK) v = parsed;
+        }
+        g_variant.store(v, std::memory_order_relaxed);
+    }
+    return v;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int validate(const void* q, const void* kv, const void* k_cache, const int64_t* slot_mapping,
+             const int64_t* position_ids, const float* cos_sin_cache, int64_t num_tokens, int64_t num_heads,
+             int64_t num_tokens_insert, int64_t cache_block_size, int64_t kv_block_stride_bytes) {
+    if (num_tokens < 0 || num_heads < 0 || num_tokens_insert < 0 || num_tokens_insert > num_tokens)
+        return DSV4_ERR_BAD_SIZE;
+    if (num_tokens == 0) return DSV4_OK;
+    if (!position_ids || !cos_sin_cache) return DSV4_ERR_NULL_POINTER;
+    if (num_heads > 0 && !q) return DSV4_ERR_NULL_POINTER;
+    if (num_tokens_insert > 0) {
+        if (!kv || !k_cache || !slot_mapping) return DSV4_ERR_NULL_POINTER;
+        if (cache_block_size <= 0 || kv_block_stride_bytes < cache_block_size * (kTokenDataBytes + kScaleBytes))
+            return DSV4_ERR_BAD_SIZE;
+    }
+    if (!aligned16(q) || !aligned16(kv) || !aligned16(cos_sin_cache)) return DSV4_ERR_MISALIGNED;
+    if (num_heads > 0 && num_tokens > INT64_MAX / (num_heads * kRowBytes)) return DSV4_ERR_TOO_LARGE;
+    return DSV4_OK;
+}
+
+PrologueParams make_params(void* q, const void* kv, void* k_cache, const int64_t* slot_mapping,
+                           const int64_t* position_ids, const float* cos_sin_cache, float eps, int64_t num_tokens,
+                           int64_t num_heads, int64_t num_tokens_insert, int64_t cache_block_size,
+                           int64_t kv_block_stride_bytes) {
+    PrologueParams p{};
+    p.q = static_cast<uint8_t*>(q);
+    p.kv = static_cast<const uint8_t*>(kv);
+    p.k_cache = static_cast<uint8_t*>(k_cache);
+    p.slot_mapping = slot_mapping;
+    p.position_ids = position_ids;
+    p.cos_sin = cos_sin_cache;
+    p.eps = eps;
+    p.num_tokens = num_tokens;
+    p.num_heads = num_heads;
+    p.num_tokens_insert = num_tokens_insert;
+    p.block_size = cache_block_size > 0 ? cache_block_size : 1;
+    p.block_stride = kv_block_stride_bytes;
+    p.cache_aligned16 = aligned16(k_cache) && (kv_block_stride_bytes % 16 == 0);
+    return p;
+}
+}  // namespace
+
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+}  // namespace dsv4
+
+using namespace dsv4;
+
+extern "C" {
+
+int dsv4_qnorm_rope_kv_insert(void* q, const void* kv, void* k_cache, const int64_t* slot_mapping,
+                              const int64_t* position_ids, const float* cos_sin_cache, float eps,
+                              int64_t num_tokens, int64_t num_heads, int64_t num_tokens_insert,
+                              int64_t cache_block_size, int64_t kv_block_stride_bytes, void* cuda_stream) {
+    const int rc = validate(q, kv, k_cache, slot_mapping, position_ids, cos_sin_cache, num_tokens, num_heads,
+                            num_tokens_insert, cache_block_size, kv_block_stride_bytes);
+    if (rc != DSV4_OK || num_tokens == 0) return rc;
+    const PrologueParams p = make_params(q, kv, k_cache, slot_mapping, position_ids, cos_sin_cache, eps, num_tokens,
+                                         num_heads, num_tokens_insert, cache_block_size, kv_block_stride_bytes);
+    cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+    int variant = current_variant();
+    if (variant == DSV4_VARIANT_AUTO) variant = DSV4_VARIANT_ROWS;
+    const cudaError_t err = variant == DSV4_VARIANT_BULK ? launch_prologue_bulk(p, stream)
+                                                         : launch_prologue_rows(p, false, stream);
+    return static_cast<int>(err);
+}
+
+int dsv4_qnorm_rope_kv_insert_checked(void* q, const void* kv, void* k_cache, const int64_t* slot_mapping,
+                                      const int64_t* position_ids, const float* cos_sin_cache, float eps,
+                                      int64_t num_tokens, int64_t num_heads, int64_t num_tokens_insert,
+                                      int64_t cache_block_size, int64_t kv_block_stride_bytes,
+                                      int64_t num_blocks, int64_t max_pos, int32_t* status, void* cuda_stream) {
+    const int rc = validate(q, kv, k_cache, slot_mapping, position_ids, cos_sin_cache, num_tokens, num_heads,
+                            num_tokens_insert, cache_block_size, kv_block_stride_bytes);
+    if (rc != DSV4_OK || num_tokens == 0) return rc;
+    if (!status) return DSV4_ERR_NULL_POINTER;
+    if (num_blocks < 0 || max_pos < 0) return DSV4_ERR_BAD_SIZE;
+    PrologueParams p = make_params(q, kv, k_cache, slot_mapping, position_ids, cos_sin_cache, eps, num_tokens,
+                                   num_heads, num_tokens_insert, cache_block_size, kv_block_stride_bytes);
+    p.num_slots = num_blocks * p.block_size;
+    p.max_pos = max_pos;
+    p.status = status;
+    return static_cast<int>(launch_prologue_rows(p, true, static_cast<cudaStream_t>(cuda_stream)));
+}
+
+int dsv4_gather_dequant_k_cache(const void* k_cache, const int64_t* slots, int64_t num_slots, void* out,
+                                int64_t out_row_stride, int64_t cache_block_size,
+                                int64_t kv_block_stride_bytes, void* cuda_stream) {
+    if (num_slots < 0 || out_row_stride < kHeadDim) return DSV4_ERR_BAD_SIZE;
+    if (num_slots == 0) return DSV4_OK;
+    if (!k_cache || !slots || !out) return DSV4_ERR_NULL_POINTER;
+    if (cache_block_size <= 0 || kv_block_stride_bytes < cache_block_size * (kTokenDataBytes + kScaleBytes))
+        return DSV4_ERR_BAD_SIZE;
+    if (!aligned16(out) || (out_row_stride % 8) != 0) return DSV4_ERR_MISALIGNED;
+    return static_cast<int>(launch_gather_dequant(static_cast<const uint8_t*>(k_cache), slots, num_slots,
+                                                  static_cast<uint8_t*>(out), out_row_stride, cache_block_size,
+                                                  kv_block_stride_bytes, static_cast<cudaStream_t>(cuda_stream)));
+}
+
+int dsv4_set_variant(int variant) {
+    if (variant < DSV4_VARIANT_AUTO || variant > DSV4_VARIANT_BULK) return DSV4_ERR_BAD_VARIANT;
+    const int previous = current_variant();
+    g_variant.store(variant, std::memory_order_relaxed);
+    return previous;
+}
+
+int dsv4_get_variant(void) { return current_variant(); }
+
+int64_t dsv4_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+const char* dsv4_error_string(int code) {
+    switch (code) {
+        case DSV4_OK: return "success";
+        case DSV4_ERR_NULL_POINTER: return "a required pointer is NULL";
+        case DSV4_ERR_BAD_SIZE: return "bad size (negative, num_tokens_insert > num_tokens, or cache block too small)";
+        case DSV4_ERR_MISALIGNED: return "q, kv, cos_sin_cache and out must be 16-byte aligned";
+        case DSV4_ERR_BAD_VARIANT: return "unknown kernel variant";
+        case DSV4_ERR_TOO_LARGE: return "size exceeds what this entry point supports";
+        default: return code > 0 ? cudaGetErrorString(static_cast<cudaError_t>(code)) : "unknown dsv4 error";
+    }
+}
+
+const char* dsv4_version(void) { return "dsv4-prologue 0.1 sm_100a"; }
+
+}  // extern "C"

@@ -1,0 +1,263 @@
+// Device-side building blocks shared by the prologue kernels (sm_100a only).
+//
+// Register layout of one 512-element bf16 row held by one warp ("A/B layout"):
+//   lane i keeps uint4 A = elements [8i, 8i+8)        (bytes 16i .. 16i+15)
+//          and  uint4 B = elements [256+8i, 256+8i+8)  (bytes 512+16i ..)
+// so each warp-wide 16-byte access covers 512 contiguous bytes, every 64-element
+// quantisation group is 8 adjacent lanes of one register (A: groups 0-3, B lanes
+// 0-23: groups 4-6) and the 64-element rotary tail [448,512) is B of lanes 24-31,
+// whose interleaved (even, odd) pairs are lane-local.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace dsv4 {
+
+constexpr int kHeadDim = 512;
+constexpr int kRopeDim = 64;
+constexpr int kNopeDim = 448;
+constexpr int kRowBytes = kHeadDim * 2;
+constexpr int kTokenDataBytes = 576;
+constexpr int kScaleBytes = 8;
+constexpr int kCosSinRowBytes = 256;
+constexpr int kFirstRopeLane = 24;
+
+struct PrologueParams {
+    uint8_t* q;             // bf16 [num_tokens, num_heads, 512]
+    const uint8_t* kv;      // bf16 [num_tokens, 512]
+    uint8_t* k_cache;       // bytes
+    const int64_t* slot_mapping;
+    const int64_t* position_ids;
+    const float* cos_sin;   // fp32 [max_pos, 64]
+    float eps;
+    int64_t num_tokens;
+    int64_t num_heads;
+    int64_t num_tokens_insert;
+    int64_t block_size;
+    int64_t block_stride;   // bytes between cache blocks
+    // range checks (checked build only)
+    int64_t num_slots;
+    int64_t max_pos;
+    int32_t* status;
+    int cache_aligned16;    // k_cache base and block stride are multiples of 16
+};
+
+// ---- memory access ---------------------------------------------------------
+
+// Streaming 16-byte load: data is touched once, keep it out of L1.
+__device__ __forceinline__ uint4 ld_stream16(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ void st_stream16(void* p, uint4 v) {
+    asm volatile("st.global.L1::no_allocate.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z),
+                 "r"(v.w)
+                 : "memory");
+}
+
+__device__ __forceinline__ void st_global8(void* p, uint2 v) {
+    asm volatile("st.global.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(v.x), "r"(v.y) : "memory");
+}
+
+__device__ __forceinline__ float4 ld_readonly_f4(const float* p) {
+    return __ldg(reinterpret_cast<const float4*>(p));
+}
+
+// ---- number formats --------------------------------------------------------
+
+__device__ __forceinline__ float bf16_lo(uint32_t u) { return __uint_as_float(u << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t u) { return __uint_as_float(u & 0xffff0000u); }
+
+// Two floats -> packed bf16 pair, round to nearest even (lo in bits 0-15).
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+
+// Four floats -> four e4m3 bytes (f0 in the lowest byte), round to nearest even, saturating.
+__device__ __forceinline__ uint32_t pack_e4m3x4(float f0, float f1, float f2, float f3) {
+    uint16_t lo, hi;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(lo) : "f"(f1), "f"(f0));
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(f3), "f"(f2));
+    return static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+}
+
+// Two e4m3 bytes (low 16 bits of `pair`) -> two floats, exact.
+__device__ __forceinline__ float2 unpack_e4m3x2(uint16_t pair) {
+    uint32_t h2;
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"(pair));
+    float lo, hi;
+    asm("{.reg .f16 l, h; mov.b32 {l, h}, %2; cvt.f32.f16 %0, l; cvt.f32.f16 %1, h;}" : "=f"(lo), "=f"(hi) : "r"(h2));
+    return make_float2(lo, hi);
+}
+
+__device__ __forceinline__ void unpack8(const uint4& v, float (&x)[8]) {
+    x[0] = bf16_lo(v.x), x[1] = bf16_hi(v.x);
+    x[2] = bf16_lo(v.y), x[3] = bf16_hi(v.y);
+    x[4] = bf16_lo(v.z), x[5] = bf16_hi(v.z);
+    x[6] = bf16_lo(v.w), x[7] = bf16_hi(v.w);
+}
+
+__device__ __forceinline__ uint4 pack8(const float (&x)[8]) {
+    return make_uint4(pack_bf16x2(x[0], x[1]), pack_bf16x2(x[2], x[3]), pack_bf16x2(x[4], x[5]),
+                      pack_bf16x2(x[6], x[7]));
+}
+
+// Sum of squares of the 8 bf16 values of a register (x*x is exact in fp32 for bf16 x).
+__device__ __forceinline__ float sumsq8(const uint4& v, float acc) {
+    float x[8];
+    unpack8(v, x);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc = fmaf(x[i], x[i], acc);
+    return acc;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) v += __shfl_xor_sync(0xffffffffu, v, m);
+    return v;
+}
+
+// 1/sqrt(mean + eps) with both operations correctly rounded, the way the CPU torch path
+// evaluates rsqrt; keeps the normalised row within 1 bf16 ulp of that path.
+__device__ __forceinline__ float inv_rms(float sum_of_squares, float eps) {
+    const float variance = __fmul_rn(sum_of_squares, 1.0f / kHeadDim);
+    return __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(variance, eps)));
+}
+
+// GPT-J rotation of 4 interleaved (even, odd) pairs; c/s are the 4 cosines / sines of
+// those pairs.  Products are rounded separately (no FMA) so the result equals the
+// reference's `e*c - o*s`, `e*s + o*c` bit for bit.
+__device__ __forceinline__ void rotate4(float (&x)[8], const float4& c, const float4& s) {
+    const float cc[4] = {c.x, c.y, c.z, c.w};
+    const float ss[4] = {s.x, s.y, s.z, s.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float e = x[2 * j], o = x[2 * j + 1];
+        x[2 * j] = __fsub_rn(__fmul_rn(e, cc[j]), __fmul_rn(o, ss[j]));
+        x[2 * j + 1] = __fadd_rn(__fmul_rn(e, ss[j]), __fmul_rn(o, cc[j]));
+    }
+}
+
+// Scale 8 bf16 values by r (one rounding) and repack; `rope` lanes also rotate.
+__device__ __forceinline__ uint4 scale8(const uint4& v, float r) {
+    float x[8];
+    unpack8(v, x);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) x[i] = __fmul_rn(x[i], r);
+    return pack8(x);
+}
+
+__device__ __forceinline__ uint4 scale_rotate8(const uint4& v, float r, const float4& c, const float4& s) {
+    float x[8];
+    unpack8(v, x);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) x[i] = __fmul_rn(x[i], r);
+    rotate4(x, c, s);
+    return pack8(x);
+}
+
+// ---- UE8M0 quantisation of one 64-element group -----------------------------
+
+// Stored scale byte for a group whose absolute maximum is `amax`:
+// clamp(ceil(log2(max(amax, 1e-4) / 448)) + 127, 0, 255), obtained from the bit pattern of
+// the quotient: its biased exponent, plus one when any mantissa bit is set.  Identical to
+// the log2/ceil statement for every bf16 amax (the quotient of a bf16 by 448 is either an
+// exact power of two or at least 0.4 % away from one).
+__device__ __forceinline__ uint32_t ue8m0_code(float amax) {
+    const float raw = __fdiv_rn(fmaxf(amax, 1e-4f), 448.0f);
+    const uint32_t u = __float_as_uint(raw);
+    const uint32_t code = ((u >> 23) & 0xffu) + ((u & 0x7fffffu) ? 1u : 0u);
+    return code > 255u ? 255u : code;
+}
+
+__device__ __forceinline__ float abs_max8(const uint4& v) {
+    // |bf16| compare as integers on the magnitude bits, then widen once
+    float x[8];
+    unpack8(v, x);
+    float m = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) m = fmaxf(m, fabsf(x[i]));
+    return m;
+}
+
+// 8 bf16 -> 8 e4m3 bytes of value x / 2^(code-127) (division by a power of two: exact).
+__device__ __forceinline__ uint2 quant8(const uint4& v, uint32_t code) {
+    const float scale = __uint_as_float(code << 23);
+    float x[8];
+    unpack8(v, x);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) x[i] = fminf(fmaxf(__fdiv_rn(x[i], scale), -448.0f), 448.0f);
+    return make_uint2(pack_e4m3x4(x[0], x[1], x[2], x[3]), pack_e4m3x4(x[4], x[5], x[6], x[7]));
+}
+
+// One latent-KV row (A/B layout, registers a,b of this lane) -> its cache slot.
+// `data` = first byte of the token's 576-byte record, `scales` = its 8 scale bytes.
+// c/s: cosines / sines of this lane's 4 rotary pairs (used by lanes >= 24 only).
+__device__ __forceinline__ void kv_row_to_cache(const uint4& a, const uint4& b, int lane, const float4& c,
+                                                const float4& s, uint8_t* data, uint8_t* scales, bool aligned16) {
+    float ma = abs_max8(a), mb = abs_max8(b);
+#pragma unroll
+    for (int m = 1; m <= 4; m <<= 1) {
+        ma = fmaxf(ma, __shfl_xor_sync(0xffffffffu, ma, m));
+        mb = fmaxf(mb, __shfl_xor_sync(0xffffffffu, mb, m));
+    }
+    const uint32_t code_a = ue8m0_code(ma), code_b = ue8m0_code(mb);
+    const uint2 qa = quant8(a, code_a);
+    const bool rope_lane = lane >= kFirstRopeLane;
+    uint2 qb = make_uint2(0u, 0u);
+    uint4 rb = make_uint4(0u, 0u, 0u, 0u);
+    if (rope_lane) {
+        float x[8];
+        unpack8(b, x);
+        rotate4(x, c, s);
+        rb = pack8(x);
+    } else {
+        qb = quant8(b, code_b);
+    }
+    // 7 scale codes + zero pad, assembled in lane 0 (groups 0-3 from A, 4-6 from B)
+    uint32_t lo = __shfl_sync(0xffffffffu, code_a, 0) | (__shfl_sync(0xffffffffu, code_a, 8) << 8) |
+                  (__shfl_sync(0xffffffffu, code_a, 16) << 16) | (__shfl_sync(0xffffffffu, code_a, 24) << 24);
+    uint32_t hi = __shfl_sync(0xffffffffu, code_b, 0) | (__shfl_sync(0xffffffffu, code_b, 8) << 8) |
+                  (__shfl_sync(0xffffffffu, code_b, 16) << 16);
+    if (aligned16) {
+        st_global8(data + 8 * lane, qa);
+        if (rope_lane) {
+            *reinterpret_cast<uint4*>(data + kNopeDim + 16 * (lane - kFirstRopeLane)) = rb;
+        } else {
+            st_global8(data + 256 + 8 * lane, qb);
+        }
+        if (lane == 0) st_global8(scales, make_uint2(lo, hi));
+    } else {
+        const uint32_t wa[2] = {qa.x, qa.y};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) data[8 * lane + i] = static_cast<uint8_t>(wa[i >> 2] >> (8 * (i & 3)));
+        if (rope_lane) {
+            const uint32_t wr[4] = {rb.x, rb.y, rb.z, rb.w};
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+                data[kNopeDim + 16 * (lane - kFirstRopeLane) + i] = static_cast<uint8_t>(wr[i >> 2] >> (8 * (i & 3)));
+        } else {
+            const uint32_t wb[2] = {qb.x, qb.y};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) data[256 + 8 * lane + i] = static_cast<uint8_t>(wb[i >> 2] >> (8 * (i & 3)));
+        }
+        if (lane < 8) scales[lane] = static_cast<uint8_t>((lane < 4 ? lo : hi) >> (8 * (lane & 3)));
+    }
+}
+
+// Launchers implemented by the kernel files; each returns cudaGetLastError() of its launch.
+cudaError_t launch_prologue_rows(const PrologueParams& p, bool checked, cudaStream_t stream);
+cudaError_t launch_prologue_bulk(const PrologueParams& p, cudaStream_t stream);
+cudaError_t launch_gather_dequant(const uint8_t* k_cache, const int64_t* slots, int64_t num_slots, uint8_t* out,
+                                  int64_t out_row_stride, int64_t block_size, int64_t block_stride,
+                                  cudaStream_t stream);
+void count_launch();
+
+}  // namespace dsv4

@@ -1,0 +1,17 @@
+"""flaggems_vllm for NVIDIA B200: the DeepSeek-V4 attention-prologue hot path.
+
+Keeps the import surface the reference package offers for this path
+(src/flaggems_vllm/__init__.py:21-46): the operator at package level and under
+`flaggems_vllm.ops`, the compatibility alias, `device`, `vendor_name`, `runtime`.
+"""
+from . import _native, ops, runtime, utils  # noqa: F401
+from .ops import *  # noqa: F401,F403
+from .ops import fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert as _prologue
+
+device = runtime.device.name
+vendor_name = runtime.device.vendor_name
+
+# compatibility alias kept by the reference (src/flaggems_vllm/__init__.py:37-46)
+ops_deepseek_v4_qnorm_rope_kv_rope_quant_insert = _prologue
+
+__version__ = "0.1.0"

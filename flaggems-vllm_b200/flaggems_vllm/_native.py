@@ -1,0 +1,88 @@
+"""ctypes binding of libdsv4_prologue.so (the C ABI declared in include/dsv4_prologue.h).
+
+There is no fallback: if the library has not been built, or a call is made on a
+machine without a CUDA device, the caller gets an exception, never a silent
+CPU or eager-PyTorch substitute.
+"""
+from __future__ import annotations
+
+import ctypes
+from pathlib import Path
+
+LIB_NAME = "libdsv4_prologue.so"
+LIB_PATH = Path(__file__).resolve().parent / LIB_NAME
+
+EXPORTS = (
+    "dsv4_qnorm_rope_kv_insert",
+    "dsv4_qnorm_rope_kv_insert_checked",
+    "dsv4_gather_dequant_k_cache",
+    "dsv4_set_variant",
+    "dsv4_get_variant",
+    "dsv4_launch_count",
+    "dsv4_error_string",
+    "dsv4_version",
+)
+
+VARIANT_AUTO, VARIANT_ROWS, VARIANT_BULK = 0, 1, 2
+
+_lib = None
+
+
+class NativeLibraryMissing(RuntimeError):
+    pass
+
+
+class Dsv4Error(RuntimeError):
+    def __init__(self, code: int, text: str):
+        super().__init__(f"libdsv4_prologue: {text} (code {code})")
+        self.code = code
+
+
+def lib() -> ctypes.CDLL:
+    """Load (once) and return the library; raises NativeLibraryMissing if it was never built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise NativeLibraryMissing(
+            f"{LIB_PATH} is missing: build it with `python -m flaggems_vllm.build` "
+            "(nvcc, sm_100a). This package has no CPU or PyTorch fallback."
+        )
+    L = ctypes.CDLL(str(LIB_PATH))
+    vp, i64, i32, f32 = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_float
+    L.dsv4_qnorm_rope_kv_insert.argtypes = [vp, vp, vp, vp, vp, vp, f32, i64, i64, i64, i64, i64, vp]
+    L.dsv4_qnorm_rope_kv_insert.restype = i32
+    L.dsv4_qnorm_rope_kv_insert_checked.argtypes = [vp, vp, vp, vp, vp, vp, f32, i64, i64, i64, i64, i64,
+                                                    i64, i64, vp, vp]
+    L.dsv4_qnorm_rope_kv_insert_checked.restype = i32
+    L.dsv4_gather_dequant_k_cache.argtypes = [vp, vp, i64, vp, i64, i64, i64, vp]
+    L.dsv4_gather_dequant_k_cache.restype = i32
+    L.dsv4_set_variant.argtypes = [i32]
+    L.dsv4_set_variant.restype = i32
+    L.dsv4_get_variant.restype = i32
+    L.dsv4_launch_count.restype = i64
+    L.dsv4_error_string.argtypes = [i32]
+    L.dsv4_error_string.restype = ctypes.c_char_p
+    L.dsv4_version.restype = ctypes.c_char_p
+    _lib = L
+    return L
+
+
+def check(code: int) -> None:
+    if code != 0:
+        raise Dsv4Error(code, lib().dsv4_error_string(code).decode())
+
+
+def launch_count() -> int:
+    return int(lib().dsv4_launch_count())
+
+
+def set_variant(variant: int) -> int:
+    prev = lib().dsv4_set_variant(int(variant))
+    if prev < 0:
+        raise Dsv4Error(prev, lib().dsv4_error_string(prev).decode())
+    return prev
+
+
+def version() -> str:
+    return lib().dsv4_version().decode()

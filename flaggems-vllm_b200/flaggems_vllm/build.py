@@ -1,0 +1,59 @@
+"""Builds libdsv4_prologue.so in place with nvcc for sm_100a: `python -m flaggems_vllm.build`.
+
+Cross-compiles without a GPU.  The CUDA runtime is linked statically so the library
+loads (and exports its symbols) on a machine that has no driver.
+"""
+from __future__ import annotations
+
+import os
+import shutil
+import subprocess
+import sys
+from pathlib import Path
+
+PKG = Path(__file__).resolve().parent
+CSRC = PKG.parent / "csrc"
+OUT = PKG / "libdsv4_prologue.so"
+SOURCES = ("abi.cu", "prologue_rows.cu", "prologue_bulk.cu", "gather_dequant.cu")
+HEADERS = ("dsv4_common.cuh", "../../include/dsv4_prologue.h")
+
+
+def nvcc_path() -> str:
+    exe = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not Path(exe).exists():
+        raise RuntimeError("nvcc not found; it is required to build libdsv4_prologue.so")
+    return exe
+
+
+def command(extra_flags=()) -> list[str]:
+    return [
+        nvcc_path(), "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+        "-Xcompiler", "-fPIC", "-shared", "-cudart", "static", *extra_flags,
+        "-o", str(OUT), *[str(CSRC / s) for s in SOURCES],
+    ]
+
+
+def up_to_date() -> bool:
+    if not OUT.exists():
+        return False
+    newest = max((CSRC / f).resolve().stat().st_mtime for f in SOURCES + HEADERS)
+    return OUT.stat().st_mtime >= newest
+
+
+def build(force: bool = False, verbose: bool = False, extra_flags=()) -> Path:
+    if not force and up_to_date():
+        return OUT
+    cmd = command(extra_flags)
+    env = dict(os.environ)
+    env.pop("CC", None), env.pop("CXX", None)  # let nvcc pick the system host compiler
+    res = subprocess.run(cmd, capture_output=True, text=True, env=env)
+    if verbose or res.returncode != 0:
+        sys.stderr.write(" ".join(cmd) + "\n" + res.stdout + res.stderr)
+    if res.returncode != 0:
+        raise RuntimeError("nvcc failed building libdsv4_prologue.so")
+    return OUT
+
+
+if __name__ == "__main__":
+    print(build(force="--force" in sys.argv, verbose=True,
+                extra_flags=("-Xptxas", "-v") if "--ptxas" in sys.argv else ()))

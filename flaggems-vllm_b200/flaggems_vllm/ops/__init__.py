@@ -1,0 +1,12 @@
+"""Operators of this package (reference: src/flaggems_vllm/ops/__init__.py:61-63,191)."""
+from .fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert import (
+    fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert,
+    fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert_checked,
+)
+from .gather_dequant_k_cache import gather_dequant_k_cache_slots
+
+__all__ = [
+    "fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert",
+    "fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert_checked",
+    "gather_dequant_k_cache_slots",
+]

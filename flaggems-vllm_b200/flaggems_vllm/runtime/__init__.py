@@ -1,0 +1,21 @@
+"""The two runtime names callers and the reference's tests use (reference:
+src/flaggems_vllm/runtime/__init__.py:23-84).  There is one backend - NVIDIA B200 - so
+there is no vendor detection and no operator override table."""
+from __future__ import annotations
+
+import torch
+
+
+class _Device:
+    name = "cuda"
+    vendor_name = "nvidia"
+
+    @property
+    def device_count(self) -> int:
+        return torch.cuda.device_count()
+
+
+device = _Device()
+torch_device_fn = torch.cuda
+
+__all__ = ["device", "torch_device_fn"]

@@ -1,0 +1,112 @@
+/*
+ * C ABI of libdsv4_prologue.so — the B200 (sm_100a) implementation of the
+ * DeepSeek-V4 attention prologue and of the reader of the cache rows it writes.
+ *
+ * Plain pointers and sizes only; every pointer is a DEVICE pointer unless the
+ * parameter name ends in `_host`.  No entry point allocates, synchronises or
+ * reads device memory back unless its comment says so; work is enqueued on
+ * `cuda_stream` (a cudaStream_t passed as void*, NULL = the legacy default
+ * stream) of the CURRENT device.
+ *
+ * Return value of every int-returning function: 0 on success, a negative
+ * DSV4_ERR_* code when the arguments are rejected before anything is launched,
+ * or a positive cudaError_t reported by the launch.
+ */
+#ifndef DSV4_PROLOGUE_H
+#define DSV4_PROLOGUE_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DSV4_OK 0
+#define DSV4_ERR_NULL_POINTER (-1) /* a required pointer is NULL */
+#define DSV4_ERR_BAD_SIZE (-2)     /* negative size, num_tokens_insert > num_tokens, block too small */
+#define DSV4_ERR_MISALIGNED (-3)   /* q / kv / cos_sin_cache / out not 16-byte aligned */
+#define DSV4_ERR_BAD_VARIANT (-4)  /* unknown kernel variant id */
+#define DSV4_ERR_TOO_LARGE (-5)    /* size exceeds what the entry point supports */
+
+/* Layout constants of one cached token (reference:
+ * src/flaggems_vllm/ops/fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert.py:35-43). */
+#define DSV4_HEAD_DIM 512
+#define DSV4_ROPE_DIM 64
+#define DSV4_NOPE_DIM 448
+#define DSV4_TOKEN_DATA_BYTES 576 /* 448 e4m3 + 64 bf16 */
+#define DSV4_SCALE_BYTES 8        /* 7 UE8M0 codes + 1 zero byte */
+
+/* Kernel variants selectable with dsv4_set_variant (0 = choose by problem size). */
+#define DSV4_VARIANT_AUTO 0
+#define DSV4_VARIANT_ROWS 1 /* one launch, 16-byte vector loads/stores through registers */
+#define DSV4_VARIANT_BULK 2 /* persistent CTAs, bulk-async (TMA) copies through a shared-memory ring */
+
+/*
+ * The fused prologue.  Replaces the reference's Python+Triton operator
+ *   fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert(q, kv, k_cache, slot_mapping,
+ *       position_ids, cos_sin_cache, eps, cache_block_size)
+ * (src/flaggems_vllm/ops/fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert.py:289-351,
+ * kernel :20-286) with the same effects:
+ *   q              bf16 [num_tokens, num_heads, 512], contiguous, rewritten in place:
+ *                  weight-less RMSNorm over 512 (fp32, eps) then GPT-J RoPE on [448,512)
+ *   kv             bf16 [num_tokens, 512], contiguous, read only
+ *   k_cache        bytes; block b starts at k_cache + b*kv_block_stride_bytes and holds
+ *                  cache_block_size*576 data bytes then cache_block_size*8 scale bytes
+ *   slot_mapping   int64 [num_tokens_insert], num_tokens_insert <= num_tokens; token t is
+ *                  stored at slot_mapping[t] unless that is negative or t >= num_tokens_insert
+ *   position_ids   int64 [num_tokens]; row index into cos_sin_cache
+ *   cos_sin_cache  fp32 [max_pos, 64] = 32 cos | 32 sin
+ * Nothing is bounds-checked on the device (as in the reference): slots and positions
+ * must be in range.  q, kv and cos_sin_cache must be 16-byte aligned; k_cache may have
+ * any alignment (a slower byte-store path is taken unless base and stride are
+ * multiples of 16).
+ */
+int dsv4_qnorm_rope_kv_insert(void* q, const void* kv, void* k_cache, const int64_t* slot_mapping,
+                              const int64_t* position_ids, const float* cos_sin_cache, float eps,
+                              int64_t num_tokens, int64_t num_heads, int64_t num_tokens_insert,
+                              int64_t cache_block_size, int64_t kv_block_stride_bytes, void* cuda_stream);
+
+/*
+ * Same operator with the device-side range checks the reference lacks: a token whose
+ * position is outside [0, max_pos) or whose slot is >= num_blocks*cache_block_size is
+ * left unprocessed and a bit is OR-ed into *status (device int32, caller-zeroed):
+ * bit 0 = bad position, bit 1 = bad slot.  Used by the test-suite in place of a
+ * memory checker.  Always the DSV4_VARIANT_ROWS kernel.
+ */
+int dsv4_qnorm_rope_kv_insert_checked(void* q, const void* kv, void* k_cache, const int64_t* slot_mapping,
+                                      const int64_t* position_ids, const float* cos_sin_cache, float eps,
+                                      int64_t num_tokens, int64_t num_heads, int64_t num_tokens_insert,
+                                      int64_t cache_block_size, int64_t kv_block_stride_bytes,
+                                      int64_t num_blocks, int64_t max_pos, int32_t* status, void* cuda_stream);
+
+/*
+ * Reader of the rows written above: out[i, 0:512] (bf16, row stride out_row_stride
+ * elements) = token stored at slots[i]: 448 values e4m3 * 2^(code-127) rounded to bf16,
+ * then the 64 cached bf16 RoPE values; a negative slot gives a zero row.  The per-token
+ * arithmetic of the reference's
+ *   dequantize_and_gather_k_cache
+ * (src/flaggems_vllm/ops/deepseek_v4_attention_dequantize_and_gather_k_cache.py:86-120)
+ * addressed by slot instead of (request, block table).
+ */
+int dsv4_gather_dequant_k_cache(const void* k_cache, const int64_t* slots, int64_t num_slots, void* out,
+                                int64_t out_row_stride, int64_t cache_block_size,
+                                int64_t kv_block_stride_bytes, void* cuda_stream);
+
+/* Process-wide kernel variant (DSV4_VARIANT_*); also read once from the environment
+ * variable DSV4_VARIANT.  Returns the previous value or DSV4_ERR_BAD_VARIANT. */
+int dsv4_set_variant(int variant);
+int dsv4_get_variant(void);
+
+/* Number of kernels this library has launched in this process (all entry points). */
+int64_t dsv4_launch_count(void);
+
+/* Human-readable text for a return code of this library. */
+const char* dsv4_error_string(int code);
+
+/* "dsv4-prologue <version> sm_100a". */
+const char* dsv4_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DSV4_PROLOGUE_H */

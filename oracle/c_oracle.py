@@ -1,0 +1,108 @@
+"""ctypes front end of the C oracle (`dsv4_oracle.c`).  TEST INFRASTRUCTURE ONLY.
+
+All tensors are CPU tensors.  The library is built by `oracle/Makefile`
+(`build()` below runs it); nothing here touches a GPU.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import subprocess
+from pathlib import Path
+
+import torch
+
+_DIR = Path(__file__).resolve().parent
+_LIB_PATH = _DIR / "libdsv4_oracle.so"
+_lib = None
+
+
+def build(force: bool = False) -> Path:
+    """Compile the oracle with the Makefile beside it (gcc, OpenMP, no FP contraction)."""
+    src = _DIR / "dsv4_oracle.c"
+    if force or not _LIB_PATH.exists() or _LIB_PATH.stat().st_mtime < src.stat().st_mtime:
+        subprocess.run(["make", "-C", str(_DIR), "-B"], check=True, capture_output=True)
+    return _LIB_PATH
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        build()
+        L = ctypes.CDLL(str(_LIB_PATH))
+        i64, vp, f32, i32 = ctypes.c_int64, ctypes.c_void_p, ctypes.c_float, ctypes.c_int
+        L.dsv4_oracle_prologue.argtypes = [vp, vp, vp, vp, vp, vp, f32, i64, i64, i64, i64, i64, i32]
+        L.dsv4_oracle_prologue.restype = i32
+        L.dsv4_oracle_gather_dequant.argtypes = [vp, vp, i64, vp, i64, i64, i32]
+        L.dsv4_oracle_gather_dequant.restype = i32
+        for name in ("dsv4_oracle_bf16_from_f32", "dsv4_oracle_e4m3_from_f32", "dsv4_oracle_f32_from_e4m3"):
+            getattr(L, name).argtypes = [vp, vp, i64]
+            getattr(L, name).restype = None
+        L.dsv4_oracle_ue8m0_codes.argtypes = [vp, vp, vp, i64]
+        L.dsv4_oracle_ue8m0_codes.restype = None
+        L.dsv4_oracle_version.restype = ctypes.c_char_p
+        _lib = L
+    return _lib
+
+
+def _cpu(t: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    assert t.device.type == "cpu" and t.dtype == dtype and t.is_contiguous(), (t.device, t.dtype)
+    return t
+
+
+def prologue(q, kv, k_cache, slot_mapping, position_ids, cos_sin_cache, eps, cache_block_size, threads=0) -> None:
+    """Same arguments and in-place effects as the operator, on CPU tensors."""
+    _cpu(q, torch.bfloat16), _cpu(kv, torch.bfloat16), _cpu(k_cache, torch.uint8)
+    _cpu(slot_mapping, torch.int64), _cpu(position_ids, torch.int64), _cpu(cos_sin_cache, torch.float32)
+    n, h, d = q.shape
+    assert d == 512 and kv.shape == (n, 512) and k_cache.dim() == 2
+    rc = lib().dsv4_oracle_prologue(
+        q.data_ptr(), kv.data_ptr(), k_cache.data_ptr(), slot_mapping.data_ptr(), position_ids.data_ptr(),
+        cos_sin_cache.data_ptr(), float(eps), n, h, slot_mapping.shape[0], int(cache_block_size),
+        k_cache.stride(0), int(threads or os.cpu_count() or 1),
+    )
+    if rc != 0:
+        raise ValueError(f"dsv4_oracle_prologue rejected its arguments (rc={rc})")
+
+
+def gather_dequant(k_cache, slots, cache_block_size, threads=0) -> torch.Tensor:
+    """bf16 [len(slots), 512]: the de-quantised cached tokens at `slots`."""
+    _cpu(k_cache, torch.uint8), _cpu(slots, torch.int64)
+    out = torch.empty(slots.shape[0], 512, dtype=torch.bfloat16)
+    rc = lib().dsv4_oracle_gather_dequant(
+        k_cache.data_ptr(), slots.data_ptr(), slots.shape[0], out.data_ptr(), int(cache_block_size),
+        k_cache.stride(0), int(threads or os.cpu_count() or 1),
+    )
+    if rc != 0:
+        raise ValueError(f"dsv4_oracle_gather_dequant rejected its arguments (rc={rc})")
+    return out
+
+
+def e4m3_from_f32(x: torch.Tensor) -> torch.Tensor:
+    x = _cpu(x.contiguous(), torch.float32)
+    out = torch.empty(x.shape, dtype=torch.uint8)
+    lib().dsv4_oracle_e4m3_from_f32(x.data_ptr(), out.data_ptr(), x.numel())
+    return out
+
+
+def f32_from_e4m3(b: torch.Tensor) -> torch.Tensor:
+    b = _cpu(b.contiguous(), torch.uint8)
+    out = torch.empty(b.shape, dtype=torch.float32)
+    lib().dsv4_oracle_f32_from_e4m3(b.data_ptr(), out.data_ptr(), b.numel())
+    return out
+
+
+def bf16_from_f32(x: torch.Tensor) -> torch.Tensor:
+    x = _cpu(x.contiguous(), torch.float32)
+    out = torch.empty(x.shape, dtype=torch.bfloat16)
+    lib().dsv4_oracle_bf16_from_f32(x.data_ptr(), out.data_ptr(), x.numel())
+    return out
+
+
+def ue8m0_codes(amax: torch.Tensor):
+    """(codes by the log2/ceil statement, codes by the bit-pattern derivation)."""
+    amax = _cpu(amax.contiguous(), torch.float32)
+    a = torch.empty(amax.shape, dtype=torch.uint8)
+    b = torch.empty(amax.shape, dtype=torch.uint8)
+    lib().dsv4_oracle_ue8m0_codes(amax.data_ptr(), a.data_ptr(), b.data_ptr(), amax.numel())
+    return a, b

@@ -1,0 +1,294 @@
+/*
+ * CPU oracle for the DeepSeek-V4 attention prologue
+ * (fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert) and for the reader of the
+ * cache rows it writes.
+ *
+ * TEST INFRASTRUCTURE ONLY.  Nothing in the shipped package may link, load or
+ * call this file: it exists so that tests, the smoke check and the benchmark's
+ * CPU-baseline leg have an independent statement of the arithmetic to compare
+ * the CUDA kernels with.  It is a plain-C restatement of the torch reference
+ * path that the upstream project keeps inside its own test file
+ * (tests/test_fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert.py); each
+ * function cites the lines it follows.  Parity is pinned: the Python test-suite
+ * checks this file against golden vectors produced by running that upstream
+ * torch path itself (tests/golden/make_golden.py).
+ *
+ * Build: see oracle/Makefile (must keep -ffp-contract=off: the reference rounds
+ * every product separately, an FMA would change results).
+ */
+#include <math.h>
+#include <stdint.h>
+#include <string.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+enum {
+    HEAD_DIM = 512,
+    ROPE_DIM = 64,
+    NOPE_DIM = 448,
+    HALF_ROPE = 32,
+    QUANT_GROUP = 64,
+    NUM_GROUPS = 7,
+    SCALE_BYTES = 8,       /* 7 UE8M0 codes + 1 zero pad byte per cached token */
+    TOKEN_DATA_BYTES = 576 /* 448 e4m3 bytes + 64 bf16 */
+};
+
+/* ---- scalar conversions ------------------------------------------------ */
+
+static inline float bf16_bits_to_f32(uint16_t h) {
+    uint32_t u = (uint32_t)h << 16;
+    float f;
+    memcpy(&f, &u, 4);
+    return f;
+}
+
+/* float -> bfloat16, round to nearest even (what Tensor.to(torch.bfloat16) does). */
+static inline uint16_t f32_to_bf16_bits(float f) {
+    uint32_t u;
+    memcpy(&u, &f, 4);
+    if ((u & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((u >> 16) | 0x0040u); /* quiet NaN */
+    uint32_t lsb = (u >> 16) & 1u;
+    u += 0x7fffu + lsb;
+    return (uint16_t)(u >> 16);
+}
+
+/*
+ * float -> float8_e4m3fn bit pattern, round to nearest even, subnormals kept
+ * (the conversion of T:166-175, `x.to(torch.float8_e4m3fn).view(torch.uint8)`).
+ * Format: 1 sign, 4 exponent (bias 7), 3 mantissa; no infinities; 0x7f is NaN;
+ * largest finite 448 = 0x7e; smallest normal 2^-6; subnormal step 2^-9.
+ * Written out from the format definition; pinned against torch in the tests.
+ */
+static inline uint8_t f32_to_e4m3_bits(float f) {
+    uint32_t u;
+    memcpy(&u, &f, 4);
+    uint8_t sign = (uint8_t)((u >> 24) & 0x80u);
+    uint32_t a = u & 0x7fffffffu;
+    if (a > 0x7f800000u) return (uint8_t)(sign | 0x7fu); /* NaN */
+    float af;
+    memcpy(&af, &a, 4);
+    uint32_t code;
+    if (af < 0.015625f) { /* below 2^-6: count subnormal steps of 2^-9 */
+        float steps = nearbyintf(af * 512.0f); /* ties to even under the default mode */
+        code = (uint32_t)steps;                /* 0..8; 8 is the smallest normal */
+    } else {
+        int32_t e = (int32_t)(a >> 23) - 127; /* unbiased exponent, >= -6 here */
+        uint32_t frac = a & 0x7fffffu;
+        uint32_t m = frac >> 20;
+        uint32_t rest = frac & 0xfffffu;
+        if (rest > 0x80000u || (rest == 0x80000u && (m & 1u))) m++;
+        if (m == 8u) {
+            m = 0;
+            e++;
+        }
+        if (e > 8) return (uint8_t)(sign | 0x7fu);
+        code = ((uint32_t)(e + 7) << 3) | m;
+        if (code > 0x7fu) code = 0x7fu; /* rounded past 448: the NaN pattern, as torch */
+    }
+    return (uint8_t)(sign | code);
+}
+
+static inline float e4m3_bits_to_f32(uint8_t b) {
+    uint32_t e = (b >> 3) & 0xfu, m = b & 7u;
+    float v;
+    if (e == 0xfu && m == 7u) return NAN;
+    if (e == 0) v = (float)m * 0.001953125f; /* m * 2^-9 */
+    else v = ldexpf(1.0f + (float)m * 0.125f, (int)e - 7);
+    return (b & 0x80u) ? -v : v;
+}
+
+/*
+ * UE8M0 scale of one 64-element quant group, the way the reference states it
+ * (T:217-223 and T:236-237): exponent = ceil(log2(max(amax,1e-4)/448)),
+ * stored code = clamp(exponent+127, 0, 255), scale = 2^(code-127) built from bits
+ * (T:154-163).
+ */
+static inline int ue8m0_exponent_logpath(float amax) {
+    float block_max = amax < 1e-4f ? 1e-4f : amax;
+    float raw = block_max / 448.0f;
+    return (int)ceilf(log2f(raw));
+}
+
+/*
+ * The same exponent from the bit pattern of `raw` (no log): biased exponent
+ * field, plus one when any mantissa bit is set.  This is the derivation the CUDA
+ * kernel uses; the tests prove it equal to the log path for every bf16 amax.
+ */
+static inline int ue8m0_exponent_bitpath(float amax) {
+    float block_max = amax < 1e-4f ? 1e-4f : amax;
+    float raw = block_max / 448.0f;
+    uint32_t u;
+    memcpy(&u, &raw, 4);
+    return (int)((u >> 23) & 0xffu) - 127 + ((u & 0x7fffffu) ? 1 : 0);
+}
+
+static inline float pow2_from_code(int code) {
+    uint32_t u = (uint32_t)code << 23;
+    float f;
+    memcpy(&f, &u, 4);
+    return f;
+}
+
+static inline int clampi(int v, int lo, int hi) { return v < lo ? lo : (v > hi ? hi : v); }
+
+/* ---- exported scalar probes (used by the tests to pin the conversions) --- */
+
+void dsv4_oracle_bf16_from_f32(const float* src, uint16_t* dst, int64_t n) {
+    for (int64_t i = 0; i < n; ++i) dst[i] = f32_to_bf16_bits(src[i]);
+}
+
+void dsv4_oracle_e4m3_from_f32(const float* src, uint8_t* dst, int64_t n) {
+    for (int64_t i = 0; i < n; ++i) dst[i] = f32_to_e4m3_bits(src[i]);
+}
+
+void dsv4_oracle_f32_from_e4m3(const uint8_t* src, float* dst, int64_t n) {
+    for (int64_t i = 0; i < n; ++i) dst[i] = e4m3_bits_to_f32(src[i]);
+}
+
+/* codes_log / codes_bits: stored UE8M0 byte for each amax, by both derivations. */
+void dsv4_oracle_ue8m0_codes(const float* amax, uint8_t* codes_log, uint8_t* codes_bits, int64_t n) {
+    for (int64_t i = 0; i < n; ++i) {
+        codes_log[i] = (uint8_t)clampi(ue8m0_exponent_logpath(amax[i]) + 127, 0, 255);
+        codes_bits[i] = (uint8_t)clampi(ue8m0_exponent_bitpath(amax[i]) + 127, 0, 255);
+    }
+}
+
+/* ---- the path ----------------------------------------------------------- */
+
+/*
+ * GPT-J (interleaved pair) rotation of a 64-float tail, T:93-140: pair j is
+ * elements (2j, 2j+1); cs row = 32 cos then 32 sin.  Two rounded products, then
+ * one rounded add or subtract.
+ */
+static inline void rope_tail(float* tail, const float* cs) {
+    for (int j = 0; j < HALF_ROPE; ++j) {
+        float e = tail[2 * j], o = tail[2 * j + 1];
+        float c = cs[j], s = cs[HALF_ROPE + j];
+        float ec = e * c, os = o * s, es = e * s, oc = o * c;
+        tail[2 * j] = ec - os;
+        tail[2 * j + 1] = es + oc;
+    }
+}
+
+/* One query row in place: weight-less RMSNorm in fp32 (T:143-148), rotate the
+ * tail, round everything to bf16 (T:137-140). */
+static void q_row(uint16_t* row, const float* cs, float eps) {
+    float x[HEAD_DIM];
+    double acc = 0.0; /* correctly rounded sum: the centre of every fp32 summation order */
+    for (int i = 0; i < HEAD_DIM; ++i) {
+        x[i] = bf16_bits_to_f32(row[i]);
+        acc += (double)x[i] * (double)x[i];
+    }
+    float variance = (float)acc / (float)HEAD_DIM;
+    float r = 1.0f / sqrtf(variance + eps);
+    for (int i = 0; i < HEAD_DIM; ++i) x[i] = x[i] * r;
+    rope_tail(x + NOPE_DIM, cs);
+    for (int i = 0; i < HEAD_DIM; ++i) row[i] = f32_to_bf16_bits(x[i]);
+}
+
+/* One latent KV row into its cache slot, T:178-243 (+ rotation of the raw tail,
+ * T:328-333).  `kv_row` is not written. */
+static void kv_row_insert(const uint16_t* kv_row, const float* cs, uint8_t* k_cache, int64_t slot,
+                          int64_t block_size, int64_t block_stride) {
+    int64_t block = slot / block_size, pos = slot % block_size;
+    uint8_t* block_base = k_cache + block * block_stride;
+    uint8_t* data = block_base + pos * TOKEN_DATA_BYTES;
+    uint8_t* scales = block_base + block_size * TOKEN_DATA_BYTES + pos * SCALE_BYTES;
+
+    float tail[ROPE_DIM];
+    for (int i = 0; i < ROPE_DIM; ++i) tail[i] = bf16_bits_to_f32(kv_row[NOPE_DIM + i]);
+    rope_tail(tail, cs);
+    for (int i = 0; i < ROPE_DIM; ++i) {
+        uint16_t b = f32_to_bf16_bits(tail[i]);
+        memcpy(data + NOPE_DIM + 2 * i, &b, 2);
+    }
+    for (int g = 0; g < NUM_GROUPS; ++g) {
+        float v[QUANT_GROUP], amax = 0.0f;
+        for (int i = 0; i < QUANT_GROUP; ++i) {
+            v[i] = bf16_bits_to_f32(kv_row[g * QUANT_GROUP + i]);
+            float a = fabsf(v[i]);
+            if (a > amax || a != a) amax = a; /* NaN sticks, like torch.max */
+        }
+        int exponent = ue8m0_exponent_logpath(amax);
+        int code = clampi(exponent + 127, 0, 255);
+        float scale = pow2_from_code(code);
+        for (int i = 0; i < QUANT_GROUP; ++i) {
+            float t = v[i] / scale;
+            if (t < -448.0f) t = -448.0f;
+            if (t > 448.0f) t = 448.0f;
+            data[g * QUANT_GROUP + i] = f32_to_e4m3_bits(t);
+        }
+        scales[g] = (uint8_t)code;
+    }
+    scales[NUM_GROUPS] = 0;
+}
+
+/*
+ * The whole op on host memory, same argument meaning as the reference's entry
+ * point (src/flaggems_vllm/ops/fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert.py:289-351)
+ * and the same result as its oracle `ref_impl` (T:316-333) — except that kv is
+ * left untouched, as the operator's contract says (the upstream oracle rotates
+ * its private copy).  q [N,H,512] bf16 in place; kv [N,512] bf16; k_cache bytes
+ * with `block_stride` bytes per block; slot_mapping [n_insert] (entries < 0
+ * skipped; tokens >= n_insert never inserted); position_ids [N]; cos_sin
+ * [max_pos,64] fp32.  Returns 0, or -1 on a negative size.
+ */
+int dsv4_oracle_prologue(uint16_t* q, const uint16_t* kv, uint8_t* k_cache, const int64_t* slot_mapping,
+                         const int64_t* position_ids, const float* cos_sin, float eps, int64_t num_tokens,
+                         int64_t num_heads, int64_t num_tokens_insert, int64_t block_size, int64_t block_stride,
+                         int num_threads) {
+    if (num_tokens < 0 || num_heads < 0 || num_tokens_insert < 0 || num_tokens_insert > num_tokens) return -1;
+#ifdef _OPENMP
+    if (num_threads > 0) omp_set_num_threads(num_threads);
+#else
+    (void)num_threads;
+#endif
+#pragma omp parallel for schedule(static)
+    for (int64_t t = 0; t < num_tokens; ++t) {
+        const float* cs = cos_sin + position_ids[t] * ROPE_DIM;
+        for (int64_t h = 0; h < num_heads; ++h) q_row(q + (t * num_heads + h) * HEAD_DIM, cs, eps);
+        if (t < num_tokens_insert && slot_mapping[t] >= 0)
+            kv_row_insert(kv + t * HEAD_DIM, cs, k_cache, slot_mapping[t], block_size, block_stride);
+    }
+    return 0;
+}
+
+/*
+ * Reader of the rows written above: out[i,:] for i < n_slots is the bf16
+ * de-quantised token stored at slots[i] — 448 values e4m3 * 2^(code-127) rounded
+ * to bf16, then the 64 bf16 RoPE values copied.  Follows the arithmetic of
+ * src/flaggems_vllm/ops/deepseek_v4_attention_dequantize_and_gather_k_cache.py:86-120
+ * (value = e4m3 * exp2(code - 127); RoPE part copied).  A slot < 0 yields a zero row.
+ */
+int dsv4_oracle_gather_dequant(const uint8_t* k_cache, const int64_t* slots, int64_t n_slots, uint16_t* out,
+                               int64_t block_size, int64_t block_stride, int num_threads) {
+    if (n_slots < 0) return -1;
+#ifdef _OPENMP
+    if (num_threads > 0) omp_set_num_threads(num_threads);
+#else
+    (void)num_threads;
+#endif
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < n_slots; ++i) {
+        uint16_t* row = out + i * HEAD_DIM;
+        int64_t slot = slots[i];
+        if (slot < 0) {
+            memset(row, 0, HEAD_DIM * 2);
+            continue;
+        }
+        int64_t block = slot / block_size, pos = slot % block_size;
+        const uint8_t* block_base = k_cache + block * block_stride;
+        const uint8_t* data = block_base + pos * TOKEN_DATA_BYTES;
+        const uint8_t* scales = block_base + block_size * TOKEN_DATA_BYTES + pos * SCALE_BYTES;
+        for (int g = 0; g < NUM_GROUPS; ++g) {
+            float scale = exp2f((float)scales[g] - 127.0f);
+            for (int j = 0; j < QUANT_GROUP; ++j)
+                row[g * QUANT_GROUP + j] = f32_to_bf16_bits(e4m3_bits_to_f32(data[g * QUANT_GROUP + j]) * scale);
+        }
+        memcpy(row + NOPE_DIM, data + NOPE_DIM, ROPE_DIM * 2);
+    }
+    return 0;
+}
+
+const char* dsv4_oracle_version(void) { return "dsv4-oracle 1"; }

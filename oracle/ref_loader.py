@@ -1,0 +1,67 @@
+"""Loads the upstream test file and hands out its own torch reference functions.
+
+TEST INFRASTRUCTURE ONLY, and usable only where the upstream source tree is
+present: it is how the golden vectors under tests/golden/ were produced and how
+the restatements in this folder are checked against the real thing.  The upstream
+package itself cannot be imported without a GPU and its SQL dependency, so the
+test module is executed with small stand-in modules for the names it imports;
+its pure-torch reference functions (`ref_impl` and helpers) need nothing else.
+"""
+from __future__ import annotations
+
+import importlib.util
+import os
+import sys
+import types
+from pathlib import Path
+
+UPSTREAM_ENV = "DSV4_UPSTREAM_ROOT"
+DEFAULT_ROOT = "/root/reference"
+OP = "fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert"
+
+
+def upstream_root() -> Path | None:
+    root = Path(os.environ.get(UPSTREAM_ENV, DEFAULT_ROOT))
+    return root if (root / "tests" / f"test_{OP}.py").exists() else None
+
+
+def load_upstream_test_module():
+    """The upstream test module object (has ref_impl, make_cos_sin_cache, k_cache_compare...)."""
+    root = upstream_root()
+    if root is None:
+        raise FileNotFoundError("upstream tree not present")
+    saved = {k: sys.modules.get(k) for k in list(sys.modules) if k == "flaggems_vllm" or k.startswith("flaggems_vllm.")}
+    for k in saved:
+        del sys.modules[k]
+
+    def mod(name, **attrs):
+        m = types.ModuleType(name)
+        m.__dict__.update(attrs)
+        sys.modules[name] = m
+        return m
+
+    def _unbound(*_a, **_k):
+        raise RuntimeError("stand-in: the operator is not bound in the reference loader")
+
+    dev_fn = types.SimpleNamespace(empty_cache=lambda: None, synchronize=lambda: None)
+    runtime = mod("flaggems_vllm.runtime", torch_device_fn=dev_fn)
+    pkg = mod("flaggems_vllm", device="cpu", vendor_name="nvidia", runtime=runtime, __path__=[])
+    setattr(pkg, OP, _unbound)
+    mod("flaggems_vllm.ops", __path__=[])
+    mod(f"flaggems_vllm.ops.{OP}", **{OP: _unbound})
+    mod("flaggems_vllm.utils", __path__=[])
+    mod("flaggems_vllm.utils.device_info", get_device_capability=lambda: (10, 0))
+    mod("_dsv4_upstream_tests", __path__=[])
+    mod("_dsv4_upstream_tests.conftest", QUICK_MODE=True)
+    try:
+        spec = importlib.util.spec_from_file_location(
+            "_dsv4_upstream_tests.t", root / "tests" / f"test_{OP}.py"
+        )
+        module = importlib.util.module_from_spec(spec)
+        sys.modules[spec.name] = module
+        spec.loader.exec_module(module)
+    finally:
+        for k in [k for k in sys.modules if k == "flaggems_vllm" or k.startswith("flaggems_vllm.")]:
+            del sys.modules[k]
+        sys.modules.update({k: v for k, v in saved.items() if v is not None})
+    return module

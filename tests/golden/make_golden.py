@@ -1,0 +1,138 @@
+"""Writes the golden vectors under tests/golden/ by running the UPSTREAM torch reference.
+
+    python tests/golden/make_golden.py          # needs the upstream tree (see oracle/ref_loader.py)
+
+Every case feeds seeded inputs to the upstream test file's own `ref_impl`
+(tests/test_fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert.py:316-333) on CPU and
+stores inputs and outputs (bf16 as uint16 bit patterns) in one compressed .npz per case.
+The upstream tree is not available where the GPU tests run, so the vectors are committed.
+`cpu_ref` (256 tokens x 8 heads) stores its inputs' SHA-256 instead of the 2 MiB q tensor:
+inputs are regenerated from the seed by flaggems_vllm.testing.workloads and the test checks
+the digest before trusting the comparison.
+"""
+from __future__ import annotations
+
+import hashlib
+import sys
+from pathlib import Path
+
+import numpy as np
+import torch
+
+HERE = Path(__file__).resolve().parent
+ROOT = HERE.parent.parent
+sys.path[:0] = [str(ROOT), str(ROOT / "flaggems-vllm_b200")]
+
+from oracle import ref_loader  # noqa: E402
+from flaggems_vllm.testing import workloads  # noqa: E402
+
+TOKEN_BYTES = 584
+
+
+def u16(t: torch.Tensor) -> np.ndarray:
+    return t.contiguous().view(torch.int16).numpy().view(np.uint16)
+
+
+def sha(t: torch.Tensor) -> str:
+    return hashlib.sha256(t.contiguous().view(torch.uint8).numpy().tobytes()).hexdigest()
+
+
+def case_inputs(name: str):
+    """(q, kv, k_cache, slot_mapping, positions, max_pos, block_size) for the small stored cases."""
+    g = torch.Generator().manual_seed({"q_path": 0, "kv_path_bs16": 1, "kv_path_bs64": 1, "dp_padding": 3,
+                                       "mixed": 5, "edge_rows": 6, "padded_stride": 7}[name])
+    rn = lambda *s: torch.randn(*s, generator=g).to(torch.bfloat16)  # noqa: E731
+    if name == "q_path":  # T:358-402 shape family: kv zero, every slot -1
+        n, h, bs, nb = 17, 8, 16, 2
+        return rn(n, h, 512), torch.zeros(n, 512, dtype=torch.bfloat16), torch.zeros(nb, bs * TOKEN_BYTES, dtype=torch.uint8), \
+            torch.full((n,), -1, dtype=torch.int64), torch.arange(n), 4096, bs
+    if name in ("kv_path_bs16", "kv_path_bs64"):  # T:419-462
+        bs = 16 if name.endswith("16") else 64
+        n = 17 if bs == 16 else 64
+        nb = (n + bs - 1) // bs + 1
+        return torch.zeros(n, 1, 512, dtype=torch.bfloat16), rn(n, 512), torch.zeros(nb, bs * TOKEN_BYTES, dtype=torch.uint8), \
+            torch.arange(n), torch.arange(n), 4096, bs
+    if name == "dp_padding":  # T:468-515: slot_mapping shorter than q
+        n, pad, bs = 17, 5, 16
+        nb = (n + bs - 1) // bs + 1
+        return torch.zeros(n + pad, 1, 512, dtype=torch.bfloat16), rn(n + pad, 512), \
+            torch.zeros(nb, bs * TOKEN_BYTES, dtype=torch.uint8), torch.arange(n), torch.arange(n + pad), 4096, bs
+    if name == "mixed":  # what upstream never tests: random positions, scattered slots, -1 among them, dirty cache
+        n, h, bs, nb = 33, 8, 16, 6
+        slots = torch.randperm(nb * bs, generator=g)[:n]
+        slots[torch.randperm(n, generator=g)[:6]] = -1
+        return rn(n, h, 512), rn(n, 512), torch.randint(0, 256, (nb, bs * TOKEN_BYTES), generator=g, dtype=torch.uint8), \
+            slots, torch.randint(0, 4096, (n,), generator=g), 4096, bs
+    if name == "edge_rows":  # quantisation corner cases in kv; q rows with extreme norms
+        n, h, bs, nb = 32, 2, 16, 3
+        q, kv = rn(n, h, 512), rn(n, 512)
+        kvf = kv.float()
+        kvf[0] = 0.0                                    # all-zero groups: amax clamps to 1e-4
+        kvf[1] *= 1e-5                                  # below the clamp
+        kvf[2] *= 1e4                                   # large
+        kvf[3] *= 50.0                                  # outlier row
+        for k in range(4, 20):                          # amax = 7 * 2^k exactly -> amax/448 is a power of two
+            kvf[k, :448] = kvf[k, :448].clamp(-1, 1)
+            kvf[k, 5:448:64] = 7.0 * 2.0 ** (k - 12)
+            kvf[k, :448] = kvf[k, :448].clamp(-7.0 * 2.0 ** (k - 12), 7.0 * 2.0 ** (k - 12))
+        kvf[20, :448] = 448.0                            # scale exactly 1, every value saturates the format top
+        kvf[21, :448] = -448.0
+        kvf[22, :448:2] = 1e-4                           # exactly at the clamp
+        kvf[23, :448] = torch.linspace(-3, 3, 448)      # ties and subnormals after scaling
+        kvf[24, :448] = torch.linspace(-0.02, 0.02, 448)
+        kvf[24, 7] = 3.5
+        qf = q.float()
+        qf[0] = 0.0                                     # zero row: rsqrt(eps)
+        qf[1] *= 1e-3
+        qf[2] *= 50.0
+        qf[3] *= 1e4
+        return qf.to(torch.bfloat16), kvf.to(torch.bfloat16), \
+            torch.randint(0, 256, (nb, bs * TOKEN_BYTES), generator=g, dtype=torch.uint8), \
+            torch.randperm(nb * bs, generator=g)[:n], torch.randint(0, 4096, (n,), generator=g), 4096, bs
+    if name == "padded_stride":  # block pitch larger than bs*584 (and 16-byte aligned): a strided view
+        n, h, bs, nb = 20, 3, 16, 4
+        slots = torch.randperm(nb * bs, generator=g)[:n]
+        slots[3] = -1
+        return rn(n, h, 512), rn(n, 512), torch.randint(0, 256, (nb, bs * TOKEN_BYTES + 64), generator=g, dtype=torch.uint8), \
+            slots, torch.randint(0, 4096, (n,), generator=g), 4096, bs
+    raise KeyError(name)
+
+
+SMALL_CASES = ("q_path", "kv_path_bs16", "kv_path_bs64", "dp_padding", "mixed", "edge_rows", "padded_stride")
+
+
+def main() -> None:
+    T = ref_loader.load_upstream_test_module()
+    for name in SMALL_CASES:
+        q, kv, kc, slots, pos, max_pos, bs = case_inputs(name)
+        slots, pos = slots.to(torch.int64), pos.to(torch.int64)
+        cs = T.make_cos_sin_cache(max_pos, 64, torch.float32, "cpu")  # theta 10000 for max_pos <= 8192
+        q_out, kv_work, kc_out = q.clone(), kv.clone(), kc.clone()
+        T.ref_impl(q_out, kv_work, kc_out, slots.clone(), pos.clone(), cs.clone(), 1e-6, bs)
+        np.savez_compressed(
+            HERE / f"{name}.npz", q=u16(q), kv=u16(kv), k_cache=kc.numpy(), slot_mapping=slots.numpy(),
+            position_ids=pos.numpy(), max_pos=max_pos, block_size=bs, eps=1e-6, q_out=u16(q_out), k_cache_out=kc_out.numpy(),
+        )
+        print(name, "ok")
+
+    # BASELINE config 1 (CPU torch reference path, seed 0): digest-checked regenerated inputs
+    w = workloads.make("cpu_ref", device="cpu", seed=0)
+    cs_up = T.make_cos_sin_cache(4096, 64, torch.float32, "cpu")
+    assert torch.equal(cs_up, w.cos_sin_cache), "workload cos/sin table differs from the upstream helper"
+    q_out, kc_out = w.q.clone(), w.k_cache.clone()
+    T.ref_impl(q_out, w.kv.clone(), kc_out, w.slot_mapping.clone(), w.position_ids.clone(), w.cos_sin_cache.clone(),
+               w.eps, w.cache_block_size)
+    blk, off = w.slot_mapping // 64, w.slot_mapping % 64
+    data = kc_out.view(64, -1)[:, : 64 * 576].reshape(64, 64, 576)[blk, off]
+    scales = kc_out.view(64, -1)[:, 64 * 576 :].reshape(64, 64, 8)[blk, off]
+    np.savez_compressed(
+        HERE / "cpu_ref.npz",
+        input_sha=np.array([sha(w.q), sha(w.kv), sha(w.k_cache), sha(w.slot_mapping), sha(w.position_ids)]),
+        q_out_head=u16(q_out[:48]), q_out_sha=sha(q_out), k_cache_out_sha=sha(kc_out),
+        rows_data=data.numpy(), rows_scales=scales.numpy(), torch_version=torch.__version__,
+    )
+    print("cpu_ref ok")
+
+
+if __name__ == "__main__":
+    main()
