@@ -1,0 +1,372 @@
+#!/usr/bin/env python
+"""Benchmark of the fused DeepSeek-V4 attention prologue on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+One step = one pass of the operator over one batch of synthetic tokens.
+  N = 1 : workload "long_prefill" (32768 tokens x 128 heads, 10 % slots = -1, 1 % outlier rows)
+  N > 1 : workload "sharded": 32768*N tokens split unevenly (seeded Dirichlet(5), each >= 4096)
+          over the ranks, one K cache per GPU, no collective on the data path (weak scaling).
+Rank 0 prints ONE JSON line: tokens/s over all GPUs (`value`, inputs resident in HBM), the
+roofline of the kernel (algorithmic bytes / CUDA-event time against the measured copy
+bandwidth), the same metric end to end from pinned host buffers (`e2e`), a CPU baseline, the
+SM clocks sampled during the timed region and the number of kernel launches timed.
+`--impl reference` times the CPU torch statement of the reference path instead.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path[:0] = [str(ROOT / "flaggems-vllm_b200"), str(ROOT)]
+
+import torch  # noqa: E402
+
+METRIC = "fused qnorm/RoPE/FP8-insert tokens/s"
+HBM_FALLBACK_GBS = 6650.0  # earlier measurement on this pool, used only if MEASURED_PEAKS.json is absent
+NOMINAL_HBM_GBS = 8000.0
+CPU_SAMPLE_TOKENS = 2048
+# DRAM traffic per fully valid token (read+write) from the ncu capture summarised under profiles/;
+# None until a capture exists.  Scaled by tokens for the reported launch.
+NCU_DRAM_BYTES_PER_TOKEN = None
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    ap.add_argument("--workload", default=None, help="override the N=1 workload (decode, prefill, long_prefill)")
+    ap.add_argument("--variant", type=int, default=None, help="kernel variant id (default: library's choice)")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extra", action="store_true", help="skip the decode / prefill side measurements")
+    return ap.parse_args()
+
+
+def dist_env():
+    return int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+
+
+def hbm_peak():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return HBM_FALLBACK_GBS, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi polling of one GPU during the timed region (reads settings, changes none)."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.proc = None
+        try:
+            uuid = torch.cuda.get_device_properties(index).uuid
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id=GPU-{uuid}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0])), mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def time_steps(fn, steps: int, warmup: int, stream, sync_all):
+    """W untimed steps, then exactly K steps between two CUDA events on the launching stream,
+    bracketed by a barrier + device synchronise on both sides.  Returns seconds for the K steps."""
+    for _ in range(warmup):
+        fn()
+    sync_all()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record(stream)
+    for _ in range(steps):
+        fn()
+    t1.record(stream)
+    sync_all()
+    return t0.elapsed_time(t1) * 1e-3
+
+
+def cpu_baseline(workload, budget_s: float = 12.0):
+    """The CPU torch statement of the reference path (oracle/torch_path.py) on the first
+    CPU_SAMPLE_TOKENS tokens of the workload, all host threads; best of >= 5 runs within a budget."""
+    from oracle import torch_path
+
+    n = min(CPU_SAMPLE_TOKENS, workload.num_tokens)
+    n_ins = min(n, workload.slot_mapping.shape[0])
+    q = workload.q[:n].cpu()
+    kv = workload.kv[:n].cpu()
+    slots = workload.slot_mapping[:n_ins].cpu()
+    pos = workload.position_ids[:n].cpu()
+    cs = workload.cos_sin_cache.cpu()
+    valid = slots >= 0
+    compact = torch.full_like(slots, -1)
+    compact[valid] = torch.arange(int(valid.sum()))
+    cache = torch.zeros(n // 64 + 1, 64 * 584, dtype=torch.uint8)
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    best, runs, t_start = float("inf"), 0, time.perf_counter()
+    while runs < 5 or (time.perf_counter() - t_start < budget_s and runs < 50):
+        qq = q.clone()
+        t = time.perf_counter()
+        torch_path.prologue(qq, kv, cache, compact, pos, cs, workload.eps, 64)
+        best = min(best, time.perf_counter() - t)
+        runs += 1
+    return {"value": n / best, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"first {n} tokens x {workload.num_heads} heads of the workload, torch CPU path, best of {runs} runs",
+            "ms_per_sample": best * 1e3}
+
+
+def run_reference(args, rank, world):
+    """--impl reference: the reference's CPU torch path (restated in oracle/torch_path.py; the
+    upstream tree does not travel to the GPU box) on a bounded sample per step."""
+    if rank != 0:
+        return
+    from flaggems_vllm.testing import workloads
+    from oracle import torch_path
+
+    name = args.workload or ("long_prefill" if world == 1 else "sharded")
+    n = CPU_SAMPLE_TOKENS
+    w = workloads.make("long_prefill" if name != "sharded" else "sharded", device="cpu", seed=0, num_tokens=n,
+                       num_blocks=n // 64 + 8, world=world if name == "sharded" else 1,
+                       total_tokens=None if name != "sharded" else 32768 * world)
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    q0 = w.q.clone()
+
+    def step():
+        q = q0.clone()
+        t = time.perf_counter()
+        torch_path.prologue(q, w.kv, w.k_cache, w.slot_mapping, w.position_ids, w.cos_sin_cache, w.eps, 64)
+        return time.perf_counter() - t
+
+    for _ in range(args.warmup):
+        step()
+    total = sum(step() for _ in range(args.steps))
+    value = n * args.steps / total
+    sample = f"{n} tokens x {w.num_heads} heads per step (bounded sample of the workload), torch CPU path"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": total / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": name, "num_heads": w.num_heads, "sample_tokens": n},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }), flush=True)
+
+
+def side_measurement(name, steps, warmup, op, native):
+    """decode / prefill configurations, reported beside the headline (N=1, rank 0 only).
+    The 256-token decode batch fits in L2, so it rotates over enough independent q/kv sets to
+    exceed L2 between reuses."""
+    from flaggems_vllm.testing import workloads
+
+    w = workloads.make(name, device="cuda", seed=0)
+    sets = 1
+    q_sets, kv_sets, slot_sets = [w.q], [w.kv], [w.slot_mapping]
+    set_bytes = w.q.numel() * 2
+    if set_bytes < 512 * 1024 * 1024:
+        sets = max(2, (512 * 1024 * 1024 + set_bytes - 1) // set_bytes)
+        perm = torch.randperm(w.k_cache.shape[0] * 64, device="cuda")
+        for i in range(1, sets):
+            q_sets.append(torch.randn_like(w.q))
+            kv_sets.append(torch.randn_like(w.kv))
+            slot_sets.append(perm[i * w.num_tokens : (i + 1) * w.num_tokens].to(torch.int64).contiguous())
+    state = {"i": 0}
+
+    def fn():
+        i = state["i"] % sets
+        state["i"] += 1
+        op(q_sets[i], kv_sets[i], w.k_cache, slot_sets[i], w.position_ids, w.cos_sin_cache, w.eps, 64)
+
+    stream = torch.cuda.current_stream()
+    secs = time_steps(fn, steps, warmup, stream, torch.cuda.synchronize)
+    nbytes = w.algorithmic_bytes()
+    return {"tokens": w.num_tokens, "us_per_launch": secs / steps * 1e6, "tokens_per_s": w.num_tokens * steps / secs,
+            "hbm_gbs": nbytes * steps / secs / 1e9, "rotating_sets": sets}
+
+
+def main():
+    args = parse_args()
+    rank, local_rank, world = dist_env()
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the operator has no CPU path")
+    assert args.warmup >= 0 and args.steps >= 1
+
+    import flaggems_vllm
+    from flaggems_vllm import _native
+    from flaggems_vllm.testing import workloads
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    distributed = world > 1
+    if distributed:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=dev)
+    if args.variant is not None:
+        _native.set_variant(args.variant)
+    op = flaggems_vllm.fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert
+
+    if world == 1:
+        name = args.workload or "long_prefill"
+        w = workloads.make(name, device=dev, seed=0)
+    else:
+        name = "sharded"
+        w = workloads.make("sharded", device=dev, seed=0, rank=rank, world=world, total_tokens=32768 * world)
+    stream = torch.cuda.current_stream(dev)
+
+    def sync_all():
+        torch.cuda.synchronize(dev)
+        if distributed:
+            dist.barrier()
+            torch.cuda.synchronize(dev)
+
+    def step():
+        op(*w.args())
+
+    # ---- device-resident throughput ("value") and the roofline of the kernel
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    launches0 = _native.launch_count()
+    secs = time_steps(step, args.steps, args.warmup, stream, sync_all)
+    launches = _native.launch_count() - launches0 - args.warmup
+    clocks = sampler.stop() if sampler else None
+    my_bytes = w.algorithmic_bytes()
+    stats = torch.tensor([secs, float(w.num_tokens), float(my_bytes), float(launches)], dtype=torch.float64, device=dev)
+    if distributed:
+        mx = stats.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        sm = stats.clone()
+        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+        secs_max, tokens, nbytes, launches_total = float(mx[0]), float(sm[1]), float(sm[2]), int(sm[3])
+        largest_tokens, largest_bytes = float(mx[1]), float(mx[2])
+    else:
+        secs_max, tokens, nbytes, launches_total = secs, float(w.num_tokens), float(my_bytes), launches
+        largest_tokens, largest_bytes = tokens, nbytes
+
+    # ---- end to end from pinned host buffers through the public API
+    e2e = None
+    if not args.no_e2e:
+        pipe = flaggems_vllm.HostStagedPrologue(w.num_heads, chunk_tokens=2048, device=dev)
+        hq = torch.empty(w.q.shape, dtype=w.q.dtype, pin_memory=True)
+        hq.copy_(w.q)
+        hq_out = torch.empty(w.q.shape, dtype=w.q.dtype, pin_memory=True)
+        hkv = w.kv.cpu().pin_memory()
+        hslots = w.slot_mapping.cpu().pin_memory()
+        hpos = w.position_ids.cpu().pin_memory()
+        e2e_steps = max(2, min(args.steps, 5))
+
+        def e2e_step():
+            pipe(hq, hkv, w.k_cache, hslots, hpos, w.cos_sin_cache, w.eps, 64, q_out_host=hq_out)
+
+        for _ in range(min(args.warmup, 2) or 1):
+            e2e_step()
+        sync_all()
+        # the staged call makes the caller's stream wait for its last copy, so two events on that
+        # stream bracket the host->device copies, the kernels and the device->host copies
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record(stream)
+        for _ in range(e2e_steps):
+            e2e_step()
+        t1.record(stream)
+        sync_all()
+        e2e_secs = t0.elapsed_time(t1) * 1e-3 / e2e_steps
+        h2d = hq.numel() * 2 + hkv.numel() * 2 + hslots.numel() * 8 + hpos.numel() * 8
+        d2h = hq_out.numel() * 2
+        es = torch.tensor([e2e_secs, float(h2d), float(d2h)], dtype=torch.float64, device=dev)
+        if distributed:
+            em = es.clone()
+            dist.all_reduce(em, op=dist.ReduceOp.MAX)
+            esum = es.clone()
+            dist.all_reduce(esum, op=dist.ReduceOp.SUM)
+            e2e_secs, h2d, d2h = float(em[0]), float(esum[1]), float(esum[2])
+        e2e = {"value": tokens / e2e_secs, "unit": "tokens/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
+               "ms_per_step": e2e_secs * 1e3, "chunk_tokens": 2048, "launches_per_step": pipe.launches,
+               "note": "q/kv/slots/positions from pinned host memory, rewritten q back to pinned host memory; K cache and cos/sin table device-resident"}
+        del hq, hq_out
+
+    if rank != 0:
+        if distributed:
+            dist.destroy_process_group()
+        return
+
+    peak, peak_kind = hbm_peak()
+    # the kernel on the rank with the most bytes is the one the step waits for
+    achieved = largest_bytes / (secs_max / args.steps) / 1e9
+    traffic = None
+    if NCU_DRAM_BYTES_PER_TOKEN is not None:
+        traffic = NCU_DRAM_BYTES_PER_TOKEN * largest_tokens
+    line = {
+        "metric": METRIC, "value": tokens * args.steps / secs_max, "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": secs_max / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": name, "num_heads": w.num_heads, "tokens_total": int(tokens),
+                   "tokens_largest_shard": int(largest_tokens), "cache_blocks_per_gpu": int(w.k_cache.shape[0]),
+                   "cache_block_size": 64, "parallelism": f"token-sharded x{world}, no collective",
+                   "l2": "inputs (>= 1 GiB of q per GPU) exceed the 126 MB L2; no flush between steps",
+                   "variant": _native.lib().dsv4_get_variant()},
+        "hbm_gbs_aggregate": nbytes * args.steps / secs_max / 1e9,
+        "hbm_frac_of_nominal_8tbs": achieved / NOMINAL_HBM_GBS,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": traffic, "peak_source": f"{peak_kind} copy bandwidth",
+                     "algorithmic_bytes_per_launch": int(largest_bytes),
+                     "kernel_ms": secs_max / args.steps * 1e3},
+        "clocks": clocks, "gpu_launches": launches_total, "e2e": e2e,
+    }
+    if not args.no_cpu_baseline and world == 1:
+        line["cpu_baseline"] = cpu_baseline(w)
+    if not args.no_extra and world == 1:
+        del w
+        torch.cuda.empty_cache()
+        line["other_configs"] = {n: side_measurement(n, max(args.steps, 50), max(args.warmup, 5), op, _native)
+                                 for n in ("decode", "prefill")}
+    print(json.dumps(line), flush=True)
+    if distributed:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -4,9 +4,11 @@ from .fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert import (
     fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert_checked,
 )
 from .gather_dequant_k_cache import gather_dequant_k_cache_slots
+from .host_staged import HostStagedPrologue
 
 __all__ = [
     "fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert",
     "fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert_checked",
     "gather_dequant_k_cache_slots",
+    "HostStagedPrologue",
 ]

@@ -127,7 +127,7 @@ def _sequence_runs(n: int, run: int, start_hi: int, g, device):
 
 
 def make(name: str, device="cpu", seed: int = 0, *, num_tokens: int | None = None,
-         num_heads: int | None = None, rank: int = 0, world: int = 1,
+         num_heads: int | None = None, num_blocks: int | None = None, rank: int = 0, world: int = 1,
          total_tokens: int | None = None) -> Workload:
     """Build one of the named workloads.
 
@@ -138,7 +138,7 @@ def make(name: str, device="cpu", seed: int = 0, *, num_tokens: int | None = Non
     long_prefill  N=32768 H=128 max_pos 131072 65536 blocks  10% slots = -1, 1% of rows x50 (q and kv)
     sharded       rank `rank` of `world`: N = its Dirichlet share of `total_tokens`
                   (default 32768 per GPU), H=128, max_pos 65536, 65536-block cache of its own
-    `num_tokens` / `num_heads` override the sizes (used by reduced-size tests).
+    `num_tokens` / `num_heads` / `num_blocks` override the sizes (used by reduced-size tests).
     """
     bs = 64
     dev = torch.device(device)
@@ -156,7 +156,9 @@ def make(name: str, device="cpu", seed: int = 0, *, num_tokens: int | None = Non
     }[name]
     n = num_tokens if num_tokens is not None else spec[0]
     h = num_heads if num_heads is not None else spec[1]
-    max_pos, num_blocks = spec[2], spec[3]
+    max_pos = spec[2]
+    num_blocks = num_blocks if num_blocks is not None else spec[3]
+    assert num_blocks * bs >= n, "cache too small for distinct slots"
 
     q = _randn_bf16((n, h, HEAD_DIM), g, dev)
     kv = _randn_bf16((n, HEAD_DIM), g, dev)

@@ -1,0 +1,345 @@
+"""Parity of the CUDA prologue (called through the Python entry point -> C ABI) with the CPU
+oracle and with the golden vectors of the upstream torch reference.
+
+Bars (see flaggems_vllm.testing.compare): cache rows byte-identical (required: >= 99.9 % of e4m3
+bytes identical, rest 1 ulp; scale bytes identical), untouched cache bytes bit-identical, q within
+1 bf16 ulp.  Shape families follow the upstream tests
+(tests/test_fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert.py:358-573) and the five
+benchmark configurations; the cases upstream does not cover (scattered slots, -1 among valid
+slots, random positions, padded or unaligned block pitch, odd head counts) are added.
+"""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+import flaggems_vllm
+from conftest import GOLDEN, SMALL_GOLDEN_CASES, load_golden
+from flaggems_vllm import _native
+from flaggems_vllm.testing import compare, workloads
+from oracle import c_oracle
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+VARIANTS = {"rows": _native.VARIANT_ROWS, "bulk": _native.VARIANT_BULK}
+op = flaggems_vllm.fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert
+
+
+@pytest.fixture(params=sorted(VARIANTS))
+def variant(request):
+    prev = _native.set_variant(VARIANTS[request.param])
+    yield request.param
+    _native.set_variant(prev)
+
+
+@pytest.fixture(autouse=True)
+def _free_device_memory():
+    yield
+    torch.cuda.empty_cache()
+
+
+def oracle_of(q, kv, k_cache, slots, pos, cs, eps, bs):
+    """Run the C oracle on host copies; returns (q_ref, k_cache_ref) on the host."""
+    qh, kch = q.cpu().clone(), k_cache.cpu().clone()
+    c_oracle.prologue(qh, kv.cpu(), kch, slots.cpu(), pos.cpu(), cs.cpu(), eps, bs)
+    return qh, kch
+
+
+def run_and_check(q, kv, k_cache, slots, pos, cs, eps, bs, *, q_ref=None, kc_ref=None):
+    """Launch on the GPU, compare everything with the oracle (or the given expectations)."""
+    if q_ref is None:
+        q_ref, kc_ref = oracle_of(q, kv, k_cache, slots, pos, cs, eps, bs)
+    kv_before, kc_before = kv.clone(), k_cache.clone()
+    launches = _native.launch_count()
+    op(q, kv, k_cache, slots, pos, cs, eps, bs)
+    torch.cuda.synchronize()
+    assert _native.launch_count() == launches + 1, "the operator is one kernel launch"
+    assert torch.equal(kv, kv_before), "kv must not be written"
+    compare.assert_untouched(k_cache, kc_before, slots, bs)
+    kc_host = k_cache.cpu()
+    assert torch.equal(kc_host, kc_ref), "cache differs from the oracle"
+    compare.assert_cache_close(kc_host, kc_ref, slots.cpu(), bs, exact=True)
+    return compare.assert_q_close(q.cpu(), q_ref)
+
+
+def random_case(n, h, bs, nb, seed, *, n_insert=None, minus_one=0, stride_pad=0, zero_cache=False):
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(n, h, 512, generator=g).to(torch.bfloat16)
+    kv = torch.randn(n, 512, generator=g).to(torch.bfloat16)
+    kc = torch.randint(0, 256, (nb, bs * 584 + stride_pad), generator=g, dtype=torch.uint8)
+    if zero_cache:
+        kc.zero_()
+    n_ins = n if n_insert is None else n_insert
+    slots = torch.randperm(nb * bs, generator=g)[:n_ins].to(torch.int64)
+    if minus_one:
+        slots[torch.randperm(n_ins, generator=g)[:minus_one]] = -1
+    pos = torch.randint(0, 4096, (n,), generator=g, dtype=torch.int64)
+    cs = workloads.cos_sin_table(4096)
+    return [t.to(DEV) for t in (q, kv, kc, slots, pos, cs)]
+
+
+# ---- golden vectors made by the upstream torch reference -------------------------------------
+
+
+@pytest.mark.parametrize("case", SMALL_GOLDEN_CASES)
+def test_golden_vectors(variant, case):
+    g = load_golden(case)
+    dev = {k: (v.to(DEV) if isinstance(v, torch.Tensor) else v) for k, v in g.items()}
+    run_and_check(dev["q"], dev["kv"], dev["k_cache"], dev["slot_mapping"], dev["position_ids"], dev["cos_sin_cache"],
+                  g["eps"], g["block_size"], q_ref=g["q_out"], kc_ref=g["k_cache_out"])
+
+
+def test_cpu_ref_config_matches_upstream_golden(variant):
+    """BASELINE config "CPU torch reference path, seed 0" (256 tokens x 8 heads)."""
+    z = np.load(GOLDEN / "cpu_ref.npz")
+    w = workloads.make("cpu_ref", device="cpu", seed=0)
+    q, kv, kc, slots, pos, cs = [t.to(DEV) for t in (w.q, w.kv, w.k_cache, w.slot_mapping, w.position_ids, w.cos_sin_cache)]
+    run_and_check(q, kv, kc, slots, pos, cs, w.eps, 64)
+    d, s = compare.gather_rows(kc.cpu(), w.slot_mapping, 64)
+    assert torch.equal(d, torch.from_numpy(z["rows_data"])) and torch.equal(s, torch.from_numpy(z["rows_scales"]))
+    head = torch.from_numpy(z["q_out_head"].view(np.int16).copy()).view(torch.bfloat16)
+    assert int(compare.bf16_ulp_distance(q[:48].cpu(), head).max()) <= 1
+
+
+# ---- the upstream test families, against the oracle --------------------------------------------
+
+
+@pytest.mark.parametrize("num_tokens", [1, 4, 17, 64])
+@pytest.mark.parametrize("n_heads", [8, 64])
+def test_q_path(variant, num_tokens, n_heads):
+    """T:358-402: kv zero, every slot -1, positions 0..N-1; only q changes."""
+    q, kv, kc, slots, pos, cs = random_case(num_tokens, n_heads, 16, 2, seed=0, zero_cache=True)
+    kv.zero_(), slots.fill_(-1)
+    pos.copy_(torch.arange(num_tokens))
+    run_and_check(q, kv, kc, slots, pos, cs, 1e-6, 16)
+    assert int(kc.abs().max()) == 0
+
+
+@pytest.mark.parametrize("num_tokens", [1, 4, 17, 64])
+@pytest.mark.parametrize("block_size", [16, 64])
+def test_kv_path(variant, num_tokens, block_size):
+    """T:419-462: one zero q head, kv random, slots 0..N-1."""
+    nb = (num_tokens + block_size - 1) // block_size + 1
+    q, kv, kc, slots, pos, cs = random_case(num_tokens, 1, block_size, nb, seed=1, zero_cache=True)
+    q.zero_()
+    slots.copy_(torch.arange(num_tokens)), pos.copy_(torch.arange(num_tokens))
+    run_and_check(q, kv, kc, slots, pos, cs, 1e-6, block_size)
+
+
+@pytest.mark.parametrize("num_tokens", [4, 17])
+@pytest.mark.parametrize("pad", [1, 5])
+@pytest.mark.parametrize("block_size", [16, 64])
+def test_dp_padding(variant, num_tokens, pad, block_size):
+    """T:468-515: slot_mapping shorter than q; padded tokens get q work, no cache write."""
+    nb = (num_tokens + block_size - 1) // block_size + 1
+    q, kv, kc, slots, pos, cs = random_case(num_tokens + pad, 2, block_size, nb, seed=3, n_insert=num_tokens)
+    run_and_check(q, kv, kc, slots, pos, cs, 1e-6, block_size)
+
+
+@pytest.mark.parametrize("num_tokens", [1, 4, 17, 64, 777])
+@pytest.mark.parametrize("n_heads", [64, 128])
+@pytest.mark.parametrize("block_size", [16, 64])
+def test_combined(variant, num_tokens, n_heads, block_size):
+    """T:521-573 (small sizes; the large ones are the configuration tests below)."""
+    nb = (num_tokens + block_size - 1) // block_size + 1
+    q, kv, kc, slots, pos, cs = random_case(num_tokens, n_heads, block_size, nb, seed=2)
+    run_and_check(q, kv, kc, slots, pos, cs, 1e-6, block_size)
+
+
+# ---- what upstream does not test ----------------------------------------------------------------
+
+
+@pytest.mark.parametrize("n_heads", [1, 2, 3, 5, 7, 15, 17, 33, 100])
+def test_head_counts_that_do_not_divide_the_row_tile(variant, n_heads):
+    q, kv, kc, slots, pos, cs = random_case(53, n_heads, 16, 8, seed=10 + n_heads, minus_one=7)
+    run_and_check(q, kv, kc, slots, pos, cs, 1e-6, 16)
+
+
+def test_zero_heads_and_zero_tokens(variant):
+    q, kv, kc, slots, pos, cs = random_case(9, 0, 16, 2, seed=4)
+    run_and_check(q, kv, kc, slots, pos, cs, 1e-6, 16)
+    before = kc.clone()
+    e = torch.empty
+    op(e(0, 8, 512, dtype=torch.bfloat16, device=DEV), e(0, 512, dtype=torch.bfloat16, device=DEV), kc,
+       e(0, dtype=torch.int64, device=DEV), e(0, dtype=torch.int64, device=DEV), cs, 1e-6, 16)
+    torch.cuda.synchronize()
+    assert torch.equal(kc, before)
+
+
+@pytest.mark.parametrize("stride_pad,offset", [(64, 0), (16, 16), (8, 0), (1, 0), (0, 8), (0, 3)])
+def test_block_pitch_and_alignment(variant, stride_pad, offset):
+    """Padded block pitch and cache bases that are not 16-byte aligned (byte-store path)."""
+    bs, nb, n = 16, 5, 40
+    q, kv, kc, slots, pos, cs = random_case(n, 4, bs, nb, seed=20 + stride_pad + offset, minus_one=3, stride_pad=stride_pad)
+    pitch = kc.shape[1]
+    backing = torch.randint(0, 256, (nb * pitch + 64,), dtype=torch.uint8, device=DEV)
+    view = backing[offset : offset + nb * pitch].view(nb, pitch)
+    view.copy_(kc)
+    guard = backing.clone()
+    run_and_check(q, kv, view, slots, pos, cs, 1e-6, bs)
+    assert torch.equal(backing[:offset], guard[:offset]) and torch.equal(backing[offset + nb * pitch :], guard[offset + nb * pitch :])
+
+
+def test_guard_bands_around_q_kv_and_cache(variant):
+    """Inputs carved out of larger sentinel-filled buffers: nothing outside them is written."""
+    n, h, bs, nb = 37, 6, 16, 4
+    q, kv, kc, slots, pos, cs = random_case(n, h, bs, nb, seed=30, minus_one=5)
+    band = 4096
+
+    def carve(t):
+        raw = torch.full((t.numel() * t.element_size() + 2 * band,), 0xA5, dtype=torch.uint8, device=DEV)
+        inner = raw[band : band + t.numel() * t.element_size()].view(t.dtype).view(t.shape)
+        inner.copy_(t)
+        return raw, inner
+
+    raw_q, q2 = carve(q)
+    raw_kv, kv2 = carve(kv)
+    raw_kc, kc2 = carve(kc)
+    run_and_check(q2, kv2, kc2, slots, pos, cs, 1e-6, bs)
+    for raw in (raw_q, raw_kv, raw_kc):
+        assert int((raw[:band] != 0xA5).sum()) == 0 and int((raw[-band:] != 0xA5).sum()) == 0
+
+
+def test_checked_build_reports_and_skips_bad_indices():
+    """The range-checked entry point stands in for a memory checker: out-of-range positions and
+    slots are skipped and reported, everything else is processed as usual."""
+    n, h, bs, nb = 64, 4, 16, 6
+    q, kv, kc, slots, pos, cs = random_case(n, h, bs, nb, seed=40)
+    checked = flaggems_vllm.fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert_checked
+    q0, kc0 = q.clone(), kc.clone()
+    assert checked(q, kv, kc, slots, pos, cs, 1e-6, bs) == 0
+    q_ref, kc_ref = oracle_of(q0, kv, kc0, slots, pos, cs, 1e-6, bs)
+    assert torch.equal(kc.cpu(), kc_ref)
+    compare.assert_q_close(q.cpu(), q_ref)
+
+    q, kc = q0.clone(), kc0.clone()
+    bad_pos, bad_slot = [3, 17], [5, 40]
+    pos2, slots2 = pos.clone(), slots.clone()
+    pos2[bad_pos[0]], pos2[bad_pos[1]] = 4096, -1
+    slots2[bad_slot[0]], slots2[bad_slot[1]] = nb * bs, nb * bs + 1000
+    assert checked(q, kv, kc, slots2, pos2, cs, 1e-6, bs) == 3
+    # expectation: bad-position tokens untouched everywhere; bad-slot tokens only lose the insert
+    pos_ok, slots_exp = pos2.clone(), slots2.clone()
+    pos_ok[bad_pos] = 0
+    slots_exp[bad_pos + bad_slot] = -1
+    q_ref, kc_ref = oracle_of(q0, kv, kc0, slots_exp, pos_ok, cs, 1e-6, bs)
+    q_ref[bad_pos] = q0[bad_pos].cpu()
+    assert torch.equal(kc.cpu(), kc_ref)
+    compare.assert_q_close(q.cpu(), q_ref)
+
+
+def test_stream_and_cuda_graph_capture(variant):
+    """Runs on the caller's current stream and can be captured: no allocation, no sync inside."""
+    q, kv, kc, slots, pos, cs = random_case(33, 16, 16, 4, seed=50)
+    q_ref, kc_ref = oracle_of(q, kv, kc, slots, pos, cs, 1e-6, 16)
+    q_in = q.clone()
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        op(q, kv, kc, slots, pos, cs, 1e-6, 16)  # warm-up outside capture
+        q.copy_(q_in)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=s):
+            op(q, kv, kc, slots, pos, cs, 1e-6, 16)
+        q.copy_(q_in)
+        graph.replay()
+    s.synchronize()
+    assert torch.equal(kc.cpu(), kc_ref)
+    compare.assert_q_close(q.cpu(), q_ref)
+
+
+# ---- the benchmark configurations ---------------------------------------------------------------
+
+
+def test_decode_config(variant):
+    w = workloads.make("decode", device=DEV, seed=0)
+    run_and_check(*w.args())
+
+
+def test_prefill_config_full_comparison(variant):
+    """8192 tokens x 128 heads, compared in full with the oracle (q is 1 GiB)."""
+    w = workloads.make("prefill", device=DEV, seed=0)
+    q_ref, _ = oracle_of(w.q, w.kv, torch.zeros(1, 64 * 584, dtype=torch.uint8), w.slot_mapping[:0], w.position_ids,
+                         w.cos_sin_cache, w.eps, 64)
+    check_cache_rows_against_compact_oracle(w, run=True)
+    st = compare.assert_q_close(w.q.cpu(), q_ref)
+    assert st["elements"] == 8192 * 128 * 512
+
+
+def check_cache_rows_against_compact_oracle(w, run: bool):
+    """Large caches are not copied to the host: the oracle inserts the same tokens into a compact
+    cache (slot = rank among the valid slots; a row's bytes do not depend on where it is stored) and
+    the rows are compared; untouched bytes are checked on the device."""
+    bs = w.cache_block_size
+    before = w.k_cache.clone()
+    kv_before = w.kv.clone()
+    if run:
+        op(*w.args())
+        torch.cuda.synchronize()
+    assert torch.equal(w.kv, kv_before)
+    compare.assert_untouched(w.k_cache, before, w.slot_mapping, bs)
+    del before
+    slots = w.slot_mapping.cpu()
+    valid = slots >= 0
+    compact = torch.full_like(slots, -1)
+    compact[valid] = torch.arange(int(valid.sum()))
+    small = torch.zeros((int(valid.sum()) + bs - 1) // bs + 1, bs * 584, dtype=torch.uint8)
+    n_ins = slots.shape[0]
+    c_oracle.prologue(torch.empty(n_ins, 0, 512, dtype=torch.bfloat16), w.kv[:n_ins].cpu(), small, compact,
+                      w.position_ids[:n_ins].cpu(), w.cos_sin_cache.cpu(), w.eps, bs)
+    d_ref, s_ref = compare.gather_rows(small, compact[valid], bs)
+    d, s = compare.gather_rows(w.k_cache, w.slot_mapping[w.slot_mapping >= 0], bs)
+    assert torch.equal(d.cpu(), d_ref), "cached data rows differ from the oracle"
+    assert torch.equal(s.cpu(), s_ref), "cached scale rows differ from the oracle"
+
+
+def test_long_prefill_config_sampled(variant):
+    """32768 tokens x 128 heads, 10 % slots -1, 1 % outlier rows (q is 4 GiB): every cache row and
+    every untouched byte is checked; q is checked on all outlier tokens plus a random sample."""
+    w = workloads.make("long_prefill", device=DEV, seed=0)
+    g = torch.Generator().manual_seed(123)
+    outliers = torch.nonzero(w.kv.float().abs().amax(dim=1) > 20.0).flatten().cpu()
+    sample = torch.unique(torch.cat([outliers, torch.randperm(w.num_tokens, generator=g)[:512],
+                                     torch.tensor([0, w.num_tokens - 1])]))
+    q_in = w.q[sample.to(DEV)].cpu()
+    check_cache_rows_against_compact_oracle(w, run=True)
+    pos = w.position_ids.cpu()[sample]
+    c_oracle.prologue(q_in, torch.empty(sample.numel(), 512, dtype=torch.bfloat16), torch.zeros(1, 64 * 584, dtype=torch.uint8),
+                      torch.empty(0, dtype=torch.int64), pos, w.cos_sin_cache.cpu(), w.eps, 64)
+    st = compare.assert_q_close(w.q[sample.to(DEV)].cpu(), q_in)
+    assert outliers.numel() >= 300 and st["elements"] == sample.numel() * 128 * 512
+    # size-independent property on the whole tensor: every normalised row has unit RMS
+    for a in range(0, w.num_tokens, 4096):
+        rms = w.q[a : a + 4096, :, :].float().pow(2).mean(dim=-1).sqrt()
+        assert float((rms - 1.0).abs().max()) < 5e-3
+
+
+def test_sharded_config_ranks_are_independent(variant):
+    """Two shards of the token-sharded configuration at reduced size: each rank's result equals the
+    oracle on that rank's tokens alone (no cross-rank state), on caches of their own."""
+    for rank in range(2):
+        w = workloads.make("sharded", device=DEV, seed=0, rank=rank, world=2, total_tokens=8192 + 4096,
+                           num_heads=16, num_blocks=1024)
+        run_and_check(*w.args())
+
+
+def test_full_size_properties_determinism_and_slot_invariance(variant):
+    """At the prefill size: two runs from the same inputs give identical bytes, and the bytes of a
+    cached row do not depend on the slot it is stored in."""
+    w = workloads.make("prefill", device=DEV, seed=1)
+    q0, kc0 = w.q.clone(), w.k_cache.clone()
+    op(*w.args())
+    q1, kc1 = w.q.clone(), w.k_cache.clone()
+    w.q.copy_(q0), w.k_cache.copy_(kc0)
+    op(*w.args())
+    torch.cuda.synchronize()
+    assert torch.equal(w.q.view(torch.int16), q1.view(torch.int16)) and torch.equal(w.k_cache, kc1)
+    del q1, kc1
+    other = torch.randperm(w.k_cache.shape[0] * 64, device=DEV)[: w.num_tokens].to(torch.int64)
+    d1, s1 = compare.gather_rows(w.k_cache, w.slot_mapping, 64)
+    d1, s1 = d1.clone(), s1.clone()
+    w.q.copy_(q0), w.k_cache.copy_(kc0)
+    op(w.q, w.kv, w.k_cache, other, w.position_ids, w.cos_sin_cache, w.eps, 64)
+    d2, s2 = compare.gather_rows(w.k_cache, other, 64)
+    assert torch.equal(d1, d2) and torch.equal(s1, s2)
