@@ -34,9 +34,10 @@ METRIC = "fused qnorm/RoPE/FP8-insert tokens/s"
 HBM_FALLBACK_GBS = 6650.0  # earlier measurement on this pool, used only if MEASURED_PEAKS.json is absent
 NOMINAL_HBM_GBS = 8000.0
 CPU_SAMPLE_TOKENS = 2048
-# DRAM traffic per fully valid token (read+write) from the ncu capture summarised under profiles/;
-# None until a capture exists.  Scaled by tokens for the reported launch.
-NCU_DRAM_BYTES_PER_TOKEN = None
+# DRAM traffic per token (dram__bytes_read.sum + dram__bytes_write.sum) of one ncu capture of the
+# kernel on the 8192-token prefill workload (profiles/prologue_rows_kernel_prefill.md), scaled by
+# tokens for the reported launch: traffic grows in proportion to tokens (no reuse across tokens).
+NCU_DRAM_BYTES_PER_TOKEN = 257123  # (1.084464 + 1.021883) GB over 8192 tokens x 128 heads, see profiles/
 
 
 def parse_args():
@@ -195,6 +196,21 @@ def run_reference(args, rank, world):
     }), flush=True)
 
 
+def hbm_ceiling(native, nbytes: int, stream):
+    """This GPU's streaming rates for the prologue's access pattern without arithmetic
+    (dsv4_hbm_probe): in place (1 read : 1 write, the operator's mix), read-only, write-only."""
+    rows = max(1, nbytes // 1024)
+    buf = torch.empty(rows * 1024, dtype=torch.uint8, device="cuda")
+    lib, out = native.lib(), {}
+    for mode, name, traffic in ((0, "inplace_gbs", 2), (1, "read_gbs", 1), (2, "write_gbs", 1)):
+        def fn():
+            native.check(lib.dsv4_hbm_probe(mode, buf.data_ptr(), rows, stream.cuda_stream))
+        secs = time_steps(fn, 10, 3, stream, torch.cuda.synchronize)
+        out[name] = traffic * rows * 1024 * 10 / secs / 1e9
+    out["buffer_bytes"] = rows * 1024
+    return out
+
+
 def side_measurement(name, steps, warmup, op, native):
     """decode / prefill configurations, reported beside the headline (N=1, rank 0 only).
     The 256-token decode batch fits in L2, so it rotates over enough independent q/kv sets to
@@ -238,7 +254,7 @@ def main():
 
     import flaggems_vllm
     from flaggems_vllm import _native
-    from flaggems_vllm.testing import workloads
+    from flaggems_vllm.testing import sharding, workloads
 
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
@@ -275,17 +291,11 @@ def main():
     launches = _native.launch_count() - launches0 - args.warmup
     clocks = sampler.stop() if sampler else None
     my_bytes = w.algorithmic_bytes()
-    stats = torch.tensor([secs, float(w.num_tokens), float(my_bytes), float(launches)], dtype=torch.float64, device=dev)
-    if distributed:
-        mx = stats.clone()
-        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
-        sm = stats.clone()
-        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
-        secs_max, tokens, nbytes, launches_total = float(mx[0]), float(sm[1]), float(sm[2]), int(sm[3])
-        largest_tokens, largest_bytes = float(mx[1]), float(mx[2])
-    else:
-        secs_max, tokens, nbytes, launches_total = secs, float(w.num_tokens), float(my_bytes), launches
-        largest_tokens, largest_bytes = tokens, nbytes
+    agg = sharding.aggregate(secs, w.num_tokens, my_bytes, launches, status=_native.device_error(), device=dev)
+    secs_max, tokens, nbytes, launches_total = agg["seconds"], float(agg["tokens"]), float(agg["bytes"]), agg["launches"]
+    largest_tokens, largest_bytes = float(agg["largest_tokens"]), float(agg["largest_bytes"])
+    if agg["failed"]:
+        raise SystemExit("a kernel reported a device-side error; no number is printed")
 
     # ---- end to end from pinned host buffers through the public API
     e2e = None
@@ -337,7 +347,7 @@ def main():
     # the kernel on the rank with the most bytes is the one the step waits for
     achieved = largest_bytes / (secs_max / args.steps) / 1e9
     traffic = None
-    if NCU_DRAM_BYTES_PER_TOKEN is not None:
+    if NCU_DRAM_BYTES_PER_TOKEN is not None and w.num_heads == 128:
         traffic = NCU_DRAM_BYTES_PER_TOKEN * largest_tokens
     line = {
         "metric": METRIC, "value": tokens * args.steps / secs_max, "unit": "tokens/s", "n_gpus": world,
@@ -359,8 +369,13 @@ def main():
     if not args.no_cpu_baseline and world == 1:
         line["cpu_baseline"] = cpu_baseline(w)
     if not args.no_extra and world == 1:
+        q_bytes = w.q.numel() * 2
         del w
         torch.cuda.empty_cache()
+        ceiling = hbm_ceiling(_native, q_bytes, stream)
+        line["roofline"]["inplace_copy_ceiling_gbs"] = ceiling["inplace_gbs"]
+        line["roofline"]["frac_of_inplace_ceiling"] = achieved / ceiling["inplace_gbs"]
+        line["hbm_ceiling"] = ceiling
         line["other_configs"] = {n: side_measurement(n, max(args.steps, 50), max(args.warmup, 5), op, _native)
                                  for n in ("decode", "prefill")}
     print(json.dumps(line), flush=True)

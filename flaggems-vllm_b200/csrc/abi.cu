@@ -40,7 +40,9 @@ int validate(const void* q, const void* kv, const void* k_cache, const int64_t* 
             return DSV4_ERR_BAD_SIZE;
     }
     if (!aligned16(q) || !aligned16(kv) || !aligned16(cos_sin_cache)) return DSV4_ERR_MISALIGNED;
-    if (num_heads > 0 && num_tokens > INT64_MAX / (num_heads * kRowBytes)) return DSV4_ERR_TOO_LARGE;
+    // kernels index q rows and tokens with 32 bits (2^31 rows of 1 KiB are 2 TiB, beyond any GPU)
+    if (num_tokens >= (1LL << 31) || num_heads >= (1LL << 31)) return DSV4_ERR_TOO_LARGE;
+    if (num_heads > 0 && num_tokens > ((1LL << 31) - 1) / num_heads) return DSV4_ERR_TOO_LARGE;
     return DSV4_OK;
 }
 
@@ -62,6 +64,7 @@ PrologueParams make_params(void* q, const void* kv, void* k_cache, const int64_t
     p.block_size = cache_block_size > 0 ? cache_block_size : 1;
     p.block_stride = kv_block_stride_bytes;
     p.cache_aligned16 = aligned16(k_cache) && (kv_block_stride_bytes % 16 == 0);
+    make_fast_divisor(static_cast<uint32_t>(num_heads > 0 ? num_heads : 1), &p.heads_mul, &p.heads_shift);
     return p;
 }
 }  // namespace
@@ -120,6 +123,24 @@ int dsv4_gather_dequant_k_cache(const void* k_cache, const int64_t* slots, int64
     return static_cast<int>(launch_gather_dequant(static_cast<const uint8_t*>(k_cache), slots, num_slots,
                                                   static_cast<uint8_t*>(out), out_row_stride, cache_block_size,
                                                   kv_block_stride_bytes, static_cast<cudaStream_t>(cuda_stream)));
+}
+
+int dsv4_hbm_probe(int mode, void* buffer, int64_t rows, void* cuda_stream) {
+    if (mode < 0 || mode > 2) return DSV4_ERR_BAD_VARIANT;
+    if (rows < 0 || rows >= (1LL << 31)) return DSV4_ERR_BAD_SIZE;
+    if (rows == 0) return DSV4_OK;
+    if (!buffer) return DSV4_ERR_NULL_POINTER;
+    if (!aligned16(buffer)) return DSV4_ERR_MISALIGNED;
+    return static_cast<int>(launch_hbm_probe(mode, static_cast<uint8_t*>(buffer), rows, nullptr,
+                                             static_cast<cudaStream_t>(cuda_stream)));
+}
+
+int dsv4_device_error(int32_t* value_host) {
+    if (!value_host) return DSV4_ERR_NULL_POINTER;
+    int v = 0;
+    const cudaError_t err = read_device_error(&v);
+    *value_host = v;
+    return static_cast<int>(err);
 }
 
 int dsv4_set_variant(int variant) {

@@ -1,12 +1,17 @@
 // Device-side building blocks shared by the prologue kernels (sm_100a only).
 //
-// Register layout of one 512-element bf16 row held by one warp ("A/B layout"):
+// Register layouts of one 512-element bf16 row held by one warp.
+// "A/B layout" (latent-KV rows):
 //   lane i keeps uint4 A = elements [8i, 8i+8)        (bytes 16i .. 16i+15)
 //          and  uint4 B = elements [256+8i, 256+8i+8)  (bytes 512+16i ..)
 // so each warp-wide 16-byte access covers 512 contiguous bytes, every 64-element
 // quantisation group is 8 adjacent lanes of one register (A: groups 0-3, B lanes
 // 0-23: groups 4-6) and the 64-element rotary tail [448,512) is B of lanes 24-31,
 // whose interleaved (even, odd) pairs are lane-local.
+// "A/B/T layout" (q rows): A as above, B only in lanes 0-23 (elements 256..447), and the
+// rotary tail as one 4-byte (even, odd) pair per lane: lane j keeps T = elements
+// 448+2j, 449+2j.  All 32 lanes then share the rotation work (6 flops each) instead of 8
+// lanes doing 4 pairs while 24 wait; accesses stay fully coalesced (512 + 384 + 128 bytes).
 #pragma once
 
 #include <cuda_runtime.h>
@@ -41,7 +46,24 @@ struct PrologueParams {
     int64_t max_pos;
     int32_t* status;
     int cache_aligned16;    // k_cache base and block stride are multiples of 16
+    // row / num_heads for row < 2^31 without a divide: (row * heads_mul) >> heads_shift
+    uint32_t heads_mul;
+    uint32_t heads_shift;
 };
+
+// floor(n / d) for n < 2^31 via the multiplier the host derived with make_fast_divisor().
+__device__ __forceinline__ uint32_t fast_div(uint32_t n, uint32_t mul, uint32_t shift) {
+    return static_cast<uint32_t>((static_cast<uint64_t>(n) * mul) >> shift);
+}
+
+// mul = ceil(2^shift / d), shift = 31 + ceil(log2 d): exact for every n < 2^31 and 1 <= d < 2^31,
+// because the error d*mul - 2^shift is below d <= 2^(shift-31), so n*error < 2^shift.
+inline void make_fast_divisor(uint32_t d, uint32_t* mul, uint32_t* shift) {
+    uint32_t l = 0;
+    while ((1ull << l) < d) ++l;
+    *shift = 31 + l;
+    *mul = static_cast<uint32_t>(((1ull << *shift) + d - 1) / d);
+}
 
 // ---- memory access ---------------------------------------------------------
 
@@ -58,6 +80,16 @@ __device__ __forceinline__ void st_stream16(void* p, uint4 v) {
     asm volatile("st.global.L1::no_allocate.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z),
                  "r"(v.w)
                  : "memory");
+}
+
+__device__ __forceinline__ uint32_t ld_stream4(const void* p) {
+    uint32_t v;
+    asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v) : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ void st_stream4(void* p, uint32_t v) {
+    asm volatile("st.global.L1::no_allocate.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
 __device__ __forceinline__ void st_global8(void* p, uint2 v) {
@@ -109,26 +141,58 @@ __device__ __forceinline__ uint4 pack8(const float (&x)[8]) {
                       pack_bf16x2(x[6], x[7]));
 }
 
-// Sum of squares of the 8 bf16 values of a register (x*x is exact in fp32 for bf16 x).
-__device__ __forceinline__ float sumsq8(const uint4& v, float acc) {
-    float x[8];
-    unpack8(v, x);
+// ---- q row arithmetic ---------------------------------------------------------
+
+// DSV4_EXACT_SUMSQ=1 accumulates the sum of squares in double, which makes it the correctly
+// rounded sum whatever the order (x*x is exact, 512 terms fit double with room to spare), so
+// 1/rms equals the CPU oracle's bit for bit when DSV4_IEEE_RSQRT=1 too.  Default 0: fp32 sum
+// (the double version costs 6-30 % of the kernel's speed, measured on B200; the fp32 sum moves
+// about 1e-5 of the outputs by one bf16 ulp).
+#ifndef DSV4_EXACT_SUMSQ
+#define DSV4_EXACT_SUMSQ 0
+#endif
+
+#if DSV4_EXACT_SUMSQ
+typedef double sumsq_t;
+#else
+typedef float sumsq_t;
+#endif
+
+__device__ __forceinline__ sumsq_t sumsq_add8(const float (&x)[8], sumsq_t acc) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) acc = fmaf(x[i], x[i], acc);
+    for (int i = 0; i < 8; ++i) {
+#if DSV4_EXACT_SUMSQ
+        acc = fma(static_cast<double>(x[i]), static_cast<double>(x[i]), acc);
+#else
+        acc = fmaf(x[i], x[i], acc);
+#endif
+    }
     return acc;
 }
 
-__device__ __forceinline__ float warp_sum(float v) {
+__device__ __forceinline__ sumsq_t warp_sum(sumsq_t v) {
 #pragma unroll
     for (int m = 16; m > 0; m >>= 1) v += __shfl_xor_sync(0xffffffffu, v, m);
     return v;
 }
 
-// 1/sqrt(mean + eps) with both operations correctly rounded, the way the CPU torch path
-// evaluates rsqrt; keeps the normalised row within 1 bf16 ulp of that path.
-__device__ __forceinline__ float inv_rms(float sum_of_squares, float eps) {
-    const float variance = __fmul_rn(sum_of_squares, 1.0f / kHeadDim);
-    return __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(variance, eps)));
+// 1/sqrt(mean + eps).  Default: the hardware reciprocal-square-root approximation refined by one
+// Newton step (error about 1 fp32 ulp, 6 instructions).  With DSV4_IEEE_RSQRT=1: IEEE square root
+// then IEEE division, the two roundings the CPU torch path performs (about 20 instructions).
+// Either way the result is 2^-16 of a bf16 ulp away from the other; the kernel is issue-bound
+// enough for the difference in instruction count to show.
+#ifndef DSV4_IEEE_RSQRT
+#define DSV4_IEEE_RSQRT 0
+#endif
+__device__ __forceinline__ float inv_rms(sumsq_t sum_of_squares, float eps) {
+    const float v = __fadd_rn(__fmul_rn(static_cast<float>(sum_of_squares), 1.0f / kHeadDim), eps);
+#if DSV4_IEEE_RSQRT
+    return __fdiv_rn(1.0f, __fsqrt_rn(v));
+#else
+    const float r0 = rsqrtf(v);
+    const float half_v_r0 = 0.5f * v * r0;
+    return fmaf(r0, fmaf(-half_v_r0, r0, 0.5f), r0);  // r0 * (1.5 - 0.5 v r0^2)
+#endif
 }
 
 // GPT-J rotation of 4 interleaved (even, odd) pairs; c/s are the 4 cosines / sines of
@@ -145,22 +209,28 @@ __device__ __forceinline__ void rotate4(float (&x)[8], const float4& c, const fl
     }
 }
 
-// Scale 8 bf16 values by r (one rounding) and repack; `rope` lanes also rotate.
-__device__ __forceinline__ uint4 scale8(const uint4& v, float r) {
-    float x[8];
-    unpack8(v, x);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) x[i] = __fmul_rn(x[i], r);
-    return pack8(x);
+// Rotation of the single (even, odd) pair a lane holds in the A/B/T layout; same rounding.
+__device__ __forceinline__ uint32_t scale_rotate_pair(uint32_t packed, float r, float c, float s) {
+    const float e = __fmul_rn(bf16_lo(packed), r), o = __fmul_rn(bf16_hi(packed), r);
+    return pack_bf16x2(__fsub_rn(__fmul_rn(e, c), __fmul_rn(o, s)), __fadd_rn(__fmul_rn(e, s), __fmul_rn(o, c)));
 }
 
-__device__ __forceinline__ uint4 scale_rotate8(const uint4& v, float r, const float4& c, const float4& s) {
-    float x[8];
-    unpack8(v, x);
+__device__ __forceinline__ void scale8(float (&x)[8], float r) {
 #pragma unroll
     for (int i = 0; i < 8; ++i) x[i] = __fmul_rn(x[i], r);
-    rotate4(x, c, s);
-    return pack8(x);
+}
+
+// One q row in the A/B/T register layout (xb all zero in lanes >= 24): 1/rms of the row, the
+// same value in every lane.
+__device__ __forceinline__ float row_inv_rms(const float (&xa)[8], const float (&xb)[8], uint32_t tail, float eps) {
+    sumsq_t acc = sumsq_add8(xb, sumsq_add8(xa, sumsq_t(0)));
+    const float e = bf16_lo(tail), o = bf16_hi(tail);
+#if DSV4_EXACT_SUMSQ
+    acc = fma(static_cast<double>(o), static_cast<double>(o), fma(static_cast<double>(e), static_cast<double>(e), acc));
+#else
+    acc = fmaf(o, o, fmaf(e, e, acc));
+#endif
+    return inv_rms(warp_sum(acc), eps);
 }
 
 // ---- UE8M0 quantisation of one 64-element group -----------------------------
@@ -178,7 +248,6 @@ __device__ __forceinline__ uint32_t ue8m0_code(float amax) {
 }
 
 __device__ __forceinline__ float abs_max8(const uint4& v) {
-    // |bf16| compare as integers on the magnitude bits, then widen once
     float x[8];
     unpack8(v, x);
     float m = 0.0f;
@@ -258,6 +327,8 @@ cudaError_t launch_prologue_bulk(const PrologueParams& p, cudaStream_t stream);
 cudaError_t launch_gather_dequant(const uint8_t* k_cache, const int64_t* slots, int64_t num_slots, uint8_t* out,
                                   int64_t out_row_stride, int64_t block_size, int64_t block_stride,
                                   cudaStream_t stream);
+cudaError_t launch_hbm_probe(int mode, uint8_t* buf, int64_t rows, uint32_t* sink, cudaStream_t stream);
 void count_launch();
+cudaError_t read_device_error(int* value);
 
 }  // namespace dsv4

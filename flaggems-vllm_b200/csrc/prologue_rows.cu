@@ -4,9 +4,9 @@
 // Grid = [kv CTAs][q CTAs].  A q CTA owns a tile of TILE = WARPS*RPW consecutive
 // rows of q viewed as [num_tokens*num_heads, 512]; it issues all of its row
 // loads first, stages the cos|sin rows of the (usually one) tokens the tile
-// touches in shared memory while those loads are in flight, reduces the sum of
-// squares per warp with shuffles, synchronises once and writes the rows back in
-// place.  A kv CTA handles WARPS tokens of the latent KV, one per warp; those
+// touches in shared memory while those loads are in flight, synchronises once,
+// then each warp finishes its rows one after the other: sum of squares reduced
+// with shuffles, scale, rotate, store in place.  A kv CTA handles WARPS tokens of the latent KV, one per warp; those
 // CTAs come first in the grid so they never form the tail of the launch.
 //
 // Replaces the per-(token, head) Triton programs of the reference
@@ -56,26 +56,31 @@ __global__ void __launch_bounds__(WARPS * 32, MIN_CTAS) prologue_rows_kernel(con
         return;
     }
 
-    // ---- q rows: RMSNorm + RoPE tail, in place
-    const int64_t total_rows = p.num_tokens * p.num_heads;
-    const int64_t tile_row0 = (static_cast<int64_t>(blockIdx.x) - kv_ctas) * TILE;
-    const int64_t row0 = tile_row0 + warp * RPW;
+    // ---- q rows: RMSNorm + RoPE tail, in place (row and token indices fit 32 bits: host-checked)
+    const uint32_t total_rows = static_cast<uint32_t>(p.num_tokens * p.num_heads);
+    const uint32_t tile_row0 = (blockIdx.x - static_cast<uint32_t>(kv_ctas)) * TILE;
+    const uint32_t row0 = tile_row0 + warp * RPW;
 
+    // 1. every row load of the CTA goes out first (A/B/T layout, 16 + 16 + 4 bytes per lane)
     uint4 a[RPW], b[RPW];
+    uint32_t tail[RPW];
 #pragma unroll
     for (int i = 0; i < RPW; ++i) {
         a[i] = b[i] = make_uint4(0u, 0u, 0u, 0u);
+        tail[i] = 0u;
         if (row0 + i < total_rows) {
-            const uint8_t* row = p.q + (row0 + i) * kRowBytes;
+            const uint8_t* row = p.q + static_cast<uint64_t>(row0 + i) * kRowBytes;
             a[i] = ld_stream16(row + 16 * lane);
-            b[i] = ld_stream16(row + 512 + 16 * lane);
+            if (lane < kFirstRopeLane) b[i] = ld_stream16(row + 512 + 16 * lane);
+            tail[i] = ld_stream4(row + 2 * kNopeDim + 4 * lane);
         }
     }
 
-    // cos|sin rows of the tokens this tile touches -> shared memory (16 threads per token)
-    const int64_t first_token = tile_row0 / p.num_heads;
-    const int64_t last_row = (tile_row0 + TILE < total_rows ? tile_row0 + TILE : total_rows) - 1;
-    const int n_tokens = static_cast<int>(last_row / p.num_heads - first_token) + 1;
+    // 2. while they fly: cos|sin rows of the tokens this tile touches -> shared memory
+    //    (16 threads per token, 16 bytes each)
+    const uint32_t first_token = fast_div(tile_row0, p.heads_mul, p.heads_shift);
+    const uint32_t last_row = (tile_row0 + TILE < total_rows ? tile_row0 + TILE : total_rows) - 1;
+    const int n_tokens = static_cast<int>(fast_div(last_row, p.heads_mul, p.heads_shift) - first_token) + 1;
     for (int j = threadIdx.x >> 4; j < n_tokens; j += WARPS * 2) {
         const int part = threadIdx.x & 15;
         int64_t pos = p.position_ids[first_token + j];
@@ -89,39 +94,23 @@ __global__ void __launch_bounds__(WARPS * 32, MIN_CTAS) prologue_rows_kernel(con
         }
         *reinterpret_cast<float4*>(&cs_smem[j][4 * part]) = ld_readonly_f4(p.cos_sin + pos * kRopeDim + 4 * part);
     }
-
-    float r[RPW];
-#pragma unroll
-    for (int i = 0; i < RPW; ++i) r[i] = inv_rms(warp_sum(sumsq8(b[i], sumsq8(a[i], 0.0f))), p.eps);
-    // Keep the rows packed across the barrier (16 registers per pair of rows instead of 32
-    // unpacked floats): the empty asm makes the compiler unpack them again for the store.
-#pragma unroll
-    for (int i = 0; i < RPW; ++i) {
-        asm volatile("" : "+r"(a[i].x), "+r"(a[i].y), "+r"(a[i].z), "+r"(a[i].w));
-        asm volatile("" : "+r"(b[i].x), "+r"(b[i].y), "+r"(b[i].z), "+r"(b[i].w));
-    }
-
     __syncthreads();
 
-    const int my_token0 = static_cast<int>(row0 / p.num_heads - first_token);
-    const int rem0 = static_cast<int>(row0 - (first_token + my_token0) * p.num_heads);
+    // 3. one row at a time: unpack once, reduce, scale, rotate the lane's pair, store
 #pragma unroll
     for (int i = 0; i < RPW; ++i) {
         if (row0 + i >= total_rows) break;
-        const int64_t within = static_cast<int64_t>(rem0) + i;
-        const int tok = my_token0 + static_cast<int>(within / p.num_heads);
+        const int tok = static_cast<int>(fast_div(row0 + i, p.heads_mul, p.heads_shift) - first_token);
         if (CHECKED && bad_token[tok]) continue;
-        uint8_t* row = p.q + (row0 + i) * kRowBytes;
-        st_stream16(row + 16 * lane, scale8(a[i], r[i]));
-        uint4 out_b;
-        if (lane >= kFirstRopeLane) {
-            const float4 c = *reinterpret_cast<const float4*>(&cs_smem[tok][4 * (lane - kFirstRopeLane)]);
-            const float4 s = *reinterpret_cast<const float4*>(&cs_smem[tok][32 + 4 * (lane - kFirstRopeLane)]);
-            out_b = scale_rotate8(b[i], r[i], c, s);
-        } else {
-            out_b = scale8(b[i], r[i]);
-        }
-        st_stream16(row + 512 + 16 * lane, out_b);
+        float xa[8], xb[8];
+        unpack8(a[i], xa), unpack8(b[i], xb);
+        const float r = row_inv_rms(xa, xb, tail[i], p.eps);
+        scale8(xa, r), scale8(xb, r);
+        uint8_t* row = p.q + static_cast<uint64_t>(row0 + i) * kRowBytes;
+        st_stream16(row + 16 * lane, pack8(xa));
+        if (lane < kFirstRopeLane) st_stream16(row + 512 + 16 * lane, pack8(xb));
+        st_stream4(row + 2 * kNopeDim + 4 * lane,
+                   scale_rotate_pair(tail[i], r, cs_smem[tok][lane], cs_smem[tok][32 + lane]));
     }
 }
 
@@ -148,7 +137,8 @@ cudaError_t launch_prologue_rows(const PrologueParams& p, bool checked, cudaStre
 #ifdef DSV4_ROWS_RPW
     return launch<DSV4_ROWS_RPW, DSV4_ROWS_WARPS, DSV4_ROWS_MIN_CTAS>(p, checked, stream);
 #else
-    return launch<2, 8, 5>(p, checked, stream);
+    // 2 rows per warp, 4 warps, 10 CTAs per SM (48 registers): the fastest of the swept shapes on B200
+    return launch<2, 4, 10>(p, checked, stream);
 #endif
 }
 

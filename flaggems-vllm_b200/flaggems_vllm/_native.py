@@ -16,6 +16,8 @@ EXPORTS = (
     "dsv4_qnorm_rope_kv_insert",
     "dsv4_qnorm_rope_kv_insert_checked",
     "dsv4_gather_dequant_k_cache",
+    "dsv4_hbm_probe",
+    "dsv4_device_error",
     "dsv4_set_variant",
     "dsv4_get_variant",
     "dsv4_launch_count",
@@ -57,6 +59,10 @@ def lib() -> ctypes.CDLL:
     L.dsv4_qnorm_rope_kv_insert_checked.restype = i32
     L.dsv4_gather_dequant_k_cache.argtypes = [vp, vp, i64, vp, i64, i64, i64, vp]
     L.dsv4_gather_dequant_k_cache.restype = i32
+    L.dsv4_hbm_probe.argtypes = [i32, vp, i64, vp]
+    L.dsv4_hbm_probe.restype = i32
+    L.dsv4_device_error.argtypes = [vp]
+    L.dsv4_device_error.restype = i32
     L.dsv4_set_variant.argtypes = [i32]
     L.dsv4_set_variant.restype = i32
     L.dsv4_get_variant.restype = i32
@@ -71,6 +77,13 @@ def lib() -> ctypes.CDLL:
 def check(code: int) -> None:
     if code != 0:
         raise Dsv4Error(code, lib().dsv4_error_string(code).decode())
+
+
+def device_error() -> int:
+    """Read and clear the current device's kernel error word (synchronises); 0 = healthy."""
+    v = ctypes.c_int32(0)
+    check(lib().dsv4_device_error(ctypes.byref(v)))
+    return int(v.value)
 
 
 def launch_count() -> int:

@@ -1,2 +1,2 @@
 """Test helpers shipped with the package: seeded workloads and the parity comparators."""
-from . import compare, workloads  # noqa: F401
+from . import compare, sharding, workloads  # noqa: F401

@@ -92,6 +92,22 @@ int dsv4_gather_dequant_k_cache(const void* k_cache, const int64_t* slots, int64
                                 int64_t out_row_stride, int64_t cache_block_size,
                                 int64_t kv_block_stride_bytes, void* cuda_stream);
 
+/*
+ * Bandwidth probe with the prologue's q access pattern and no arithmetic, over `rows` rows of
+ * 1 KiB starting at `buffer` (16-byte aligned): mode 0 reads every row and writes it back in
+ * place, mode 1 only reads, mode 2 only writes (the buffer's contents are overwritten).  Used by
+ * bench.py to measure, on the GPU at hand, the ceiling the fused kernel is compared with.
+ * No counterpart in the reference.
+ */
+int dsv4_hbm_probe(int mode, void* buffer, int64_t rows, void* cuda_stream);
+
+/*
+ * Reads into *value_host, and clears, the error word the kernels of the current device keep:
+ * bit 0 = a bounded wait inside the DSV4_VARIANT_BULK kernel ran out (its result is then
+ * incomplete).  Synchronises the device.  0 after every healthy run.
+ */
+int dsv4_device_error(int32_t* value_host);
+
 /* Process-wide kernel variant (DSV4_VARIANT_*); also read once from the environment
  * variable DSV4_VARIANT.  Returns the previous value or DSV4_ERR_BAD_VARIANT. */
 int dsv4_set_variant(int variant);

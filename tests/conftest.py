@@ -19,6 +19,10 @@ SMALL_GOLDEN_CASES = ("q_path", "kv_path_bs16", "kv_path_bs64", "dp_padding", "m
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")
+    # rebuild the CUDA library when a source is newer than it (no-op otherwise; nvcc cross-compiles)
+    from flaggems_vllm import build as native_build
+
+    native_build.build()
 
 
 def pytest_collection_modifyitems(config, items):

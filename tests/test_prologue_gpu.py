@@ -55,6 +55,7 @@ def run_and_check(q, kv, k_cache, slots, pos, cs, eps, bs, *, q_ref=None, kc_ref
     op(q, kv, k_cache, slots, pos, cs, eps, bs)
     torch.cuda.synchronize()
     assert _native.launch_count() == launches + 1, "the operator is one kernel launch"
+    assert _native.device_error() == 0, "a bounded wait inside the kernel ran out"
     assert torch.equal(kv, kv_before), "kv must not be written"
     compare.assert_untouched(k_cache, kc_before, slots, bs)
     kc_host = k_cache.cpu()
@@ -343,3 +344,20 @@ def test_full_size_properties_determinism_and_slot_invariance(variant):
     op(w.q, w.kv, w.k_cache, other, w.position_ids, w.cos_sin_cache, w.eps, 64)
     d2, s2 = compare.gather_rows(w.k_cache, other, 64)
     assert torch.equal(d1, d2) and torch.equal(s1, s2)
+
+
+def test_hbm_probe_modes_leave_or_fill_the_buffer():
+    """The ceiling probe: in-place and read-only modes leave the buffer unchanged, write-only fills
+    every byte of the requested rows and nothing after them."""
+    rows = 1000
+    buf = torch.randint(0, 256, ((rows + 8) * 1024,), dtype=torch.uint8, device=DEV)
+    before = buf.clone()
+    lib, stream = _native.lib(), torch.cuda.current_stream().cuda_stream
+    for mode in (0, 1):
+        _native.check(lib.dsv4_hbm_probe(mode, buf.data_ptr(), rows, stream))
+        torch.cuda.synchronize()
+        assert torch.equal(buf, before)
+    _native.check(lib.dsv4_hbm_probe(2, buf.data_ptr(), rows, stream))
+    torch.cuda.synchronize()
+    assert torch.equal(buf[rows * 1024 :], before[rows * 1024 :])
+    assert not torch.equal(buf[: rows * 1024], before[: rows * 1024])
