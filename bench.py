@@ -43,8 +43,8 @@ NCU_DRAM_BYTES_PER_TOKEN = 257123  # (1.084464 + 1.021883) GB over 8192 tokens x
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--workload", default=None, help="override the N=1 workload (decode, prefill, long_prefill)")
     ap.add_argument("--variant", type=int, default=None, help="kernel variant id (default: library's choice)")
@@ -80,7 +80,7 @@ class ClockSampler:
         try:
             uuid = torch.cuda.get_device_properties(index).uuid
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id=GPU-{uuid}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                ["nvidia-smi", f"--id=GPU-{uuid}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "20"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except Exception:
             self.proc = None
@@ -88,7 +88,7 @@ class ClockSampler:
     def stop(self) -> dict:
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
+        time.sleep(0.05)
         self.proc.terminate()
         try:
             out, _ = self.proc.communicate(timeout=5)
@@ -286,6 +286,8 @@ def main():
 
     # ---- device-resident throughput ("value") and the roofline of the kernel
     sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        time.sleep(0.3)  # let nvidia-smi start polling before the (short) timed region
     launches0 = _native.launch_count()
     secs = time_steps(step, args.steps, args.warmup, stream, sync_all)
     launches = _native.launch_count() - launches0 - args.warmup

@@ -125,6 +125,26 @@ int dsv4_gather_dequant_k_cache(const void* k_cache, const int64_t* slots, int64
                                                   kv_block_stride_bytes, static_cast<cudaStream_t>(cuda_stream)));
 }
 
+int dsv4_dequantize_and_gather_k_cache(void* out, int64_t out_stride0, int64_t out_stride1, int64_t out_tokens,
+                                       const void* k_cache, const void* seq_lens, const void* gather_lens,
+                                       const void* block_table, int64_t num_reqs, int64_t max_blocks_per_seq,
+                                       int64_t cache_block_size, int64_t kv_block_stride_bytes, int64_t offset,
+                                       int32_t nope_dim, int32_t rope_dim, int32_t scale_slots, int32_t index_is_int64,
+                                       void* cuda_stream) {
+    if (num_reqs < 0 || out_tokens < 0 || offset < 0 || nope_dim < 0 || rope_dim < 0 || scale_slots < 0)
+        return DSV4_ERR_BAD_SIZE;
+    if (num_reqs == 0 || out_tokens == 0) return DSV4_OK;
+    if (!out || !k_cache || !seq_lens || !block_table) return DSV4_ERR_NULL_POINTER;
+    if (cache_block_size <= 0 || max_blocks_per_seq <= 0 || scale_slots * 64 < nope_dim) return DSV4_ERR_BAD_SIZE;
+    if (kv_block_stride_bytes < cache_block_size * (nope_dim + 2 * rope_dim + scale_slots)) return DSV4_ERR_BAD_SIZE;
+    if (num_reqs > 65535) return DSV4_ERR_TOO_LARGE;
+    if ((reinterpret_cast<uintptr_t>(out) & 1u) != 0) return DSV4_ERR_MISALIGNED;
+    return static_cast<int>(launch_gather_dequant_requests(
+        static_cast<uint8_t*>(out), out_stride0, out_stride1, static_cast<const uint8_t*>(k_cache), seq_lens, gather_lens,
+        block_table, num_reqs, max_blocks_per_seq, cache_block_size, kv_block_stride_bytes, offset, nope_dim, rope_dim,
+        scale_slots, index_is_int64 ? 1 : 0, out_tokens, static_cast<cudaStream_t>(cuda_stream)));
+}
+
 int dsv4_hbm_probe(int mode, void* buffer, int64_t rows, void* cuda_stream) {
     if (mode < 0 || mode > 2) return DSV4_ERR_BAD_VARIANT;
     if (rows < 0 || rows >= (1LL << 31)) return DSV4_ERR_BAD_SIZE;

@@ -327,6 +327,11 @@ cudaError_t launch_prologue_bulk(const PrologueParams& p, cudaStream_t stream);
 cudaError_t launch_gather_dequant(const uint8_t* k_cache, const int64_t* slots, int64_t num_slots, uint8_t* out,
                                   int64_t out_row_stride, int64_t block_size, int64_t block_stride,
                                   cudaStream_t stream);
+cudaError_t launch_gather_dequant_requests(uint8_t* out, int64_t out_stride0, int64_t out_stride1, const uint8_t* k_cache,
+                                           const void* seq_lens, const void* gather_lens, const void* block_table,
+                                           int64_t num_reqs, int64_t max_blocks_per_seq, int64_t block_size,
+                                           int64_t block_stride, int64_t offset, int nope_dim, int rope_dim, int scale_slots,
+                                           int index64, int64_t tokens_hint, cudaStream_t stream);
 cudaError_t launch_hbm_probe(int mode, uint8_t* buf, int64_t rows, uint32_t* sink, cudaStream_t stream);
 void count_launch();
 cudaError_t read_device_error(int* value);

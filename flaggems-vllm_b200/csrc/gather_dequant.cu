@@ -71,6 +71,73 @@ gather_dequant_kernel(const uint8_t* __restrict__ k_cache, const int64_t* __rest
     *reinterpret_cast<uint4*>(row + 512 + 16 * lane) = b;
 }
 
+// ---- request / block-table form (the reference operator's own addressing) -------------------------
+//
+// out[r, offset + i, :] = token at position seq_len[r] - gather_len[r] + i of request r, found through
+// block_table[r, pos / block_size].  grid = (CTAs per request, requests); the warps of a request stride
+// over its gathered positions.  FAST = DeepSeek-V4 layout (448 e4m3 + 64 bf16, 8 scale bytes) with
+// 16-byte aligned rows on both sides; otherwise any nope/rope/scale_slots with scalar accesses.
+struct GatherParams {
+    uint8_t* out;            // bf16, element strides below, unit stride in the last dimension
+    int64_t out_stride0, out_stride1;
+    const uint8_t* k_cache;
+    const void* seq_lens;
+    const void* gather_lens;  // may be null: gather the whole sequence
+    const void* block_table;
+    int64_t max_blocks_per_seq;
+    int64_t block_size, block_stride;
+    int64_t offset;
+    int32_t nope_dim, rope_dim, scale_slots;
+    int32_t index64;          // 1: seq_lens / gather_lens / block_table are int64, 0: int32
+};
+
+__device__ __forceinline__ int64_t load_index(const void* p, int64_t i, int is64) {
+    return is64 ? static_cast<const int64_t*>(p)[i] : static_cast<int64_t>(static_cast<const int32_t*>(p)[i]);
+}
+
+template <int WARPS, bool FAST>
+__global__ void __launch_bounds__(WARPS * 32) gather_dequant_requests_kernel(const GatherParams g) {
+    const int lane = threadIdx.x & 31;
+    const int64_t req = blockIdx.y;
+    const int64_t seq_len = load_index(g.seq_lens, req, g.index64);
+    const int64_t gather_len = g.gather_lens ? load_index(g.gather_lens, req, g.index64) : seq_len;
+    const int64_t start = seq_len - gather_len;
+    const int64_t token_data = g.nope_dim + 2 * g.rope_dim;
+    const int64_t warps_per_req = static_cast<int64_t>(gridDim.x) * WARPS;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * WARPS + (threadIdx.x >> 5); i < gather_len; i += warps_per_req) {
+        const int64_t pos = start + i;
+        const int64_t block_in_seq = pos / g.block_size, in_block = pos - block_in_seq * g.block_size;
+        const int64_t block = load_index(g.block_table, req * g.max_blocks_per_seq + block_in_seq, g.index64);
+        const uint8_t* base = g.k_cache + block * g.block_stride;
+        const uint8_t* data = base + in_block * token_data;
+        const uint8_t* scales = base + g.block_size * token_data + in_block * g.scale_slots;
+        uint8_t* row = g.out + (req * g.out_stride0 + (g.offset + i) * g.out_stride1) * 2;
+        if (FAST) {
+            const uint2 codes = *reinterpret_cast<const uint2*>(scales);
+            const float scale_a = ue8m0_to_float((codes.x >> (8 * (lane >> 3))) & 0xffu);
+            *reinterpret_cast<uint4*>(row + 16 * lane) = dequant8(*reinterpret_cast<const uint2*>(data + 8 * lane), scale_a);
+            uint4 b;
+            if (lane >= kFirstRopeLane) {
+                b = *reinterpret_cast<const uint4*>(data + kNopeDim + 16 * (lane - kFirstRopeLane));
+            } else {
+                const float scale_b = ue8m0_to_float((codes.y >> (8 * (lane >> 3))) & 0xffu);
+                b = dequant8(*reinterpret_cast<const uint2*>(data + 256 + 8 * lane), scale_b);
+            }
+            *reinterpret_cast<uint4*>(row + 512 + 16 * lane) = b;
+        } else {
+            uint16_t* out16 = reinterpret_cast<uint16_t*>(row);
+            for (int j = lane; j < g.nope_dim; j += 32) {
+                const float scale = ue8m0_to_float(scales[j >> 6]);
+                const float v = unpack_e4m3x2(static_cast<uint16_t>(data[j])).x;
+                out16[j] = static_cast<uint16_t>(pack_bf16x2(__fmul_rn(v, scale), 0.0f) & 0xffffu);
+            }
+            for (int j = lane; j < g.rope_dim; j += 32)
+                out16[g.nope_dim + j] = static_cast<uint16_t>(data[g.nope_dim + 2 * j]) |
+                                        (static_cast<uint16_t>(data[g.nope_dim + 2 * j + 1]) << 8);
+        }
+    }
+}
+
 }  // namespace
 
 cudaError_t launch_gather_dequant(const uint8_t* k_cache, const int64_t* slots, int64_t num_slots, uint8_t* out,
@@ -83,6 +150,34 @@ cudaError_t launch_gather_dequant(const uint8_t* k_cache, const int64_t* slots, 
     const int aligned16 = ((reinterpret_cast<uintptr_t>(k_cache) | static_cast<uintptr_t>(block_stride)) & 15u) == 0;
     gather_dequant_kernel<WARPS><<<static_cast<unsigned>(grid), WARPS * 32, 0, stream>>>(
         k_cache, slots, num_slots, out, out_row_stride * 2, block_size, block_stride, aligned16);
+    count_launch();
+    return cudaGetLastError();
+}
+
+cudaError_t launch_gather_dequant_requests(uint8_t* out, int64_t out_stride0, int64_t out_stride1, const uint8_t* k_cache,
+                                           const void* seq_lens, const void* gather_lens, const void* block_table,
+                                           int64_t num_reqs, int64_t max_blocks_per_seq, int64_t block_size,
+                                           int64_t block_stride, int64_t offset, int nope_dim, int rope_dim, int scale_slots,
+                                           int index64, int64_t tokens_hint, cudaStream_t stream) {
+    constexpr int WARPS = 8;
+    if (num_reqs == 0) return cudaSuccess;
+    if (num_reqs > 65535) return cudaErrorInvalidConfiguration;
+    GatherParams g{};
+    g.out = out, g.out_stride0 = out_stride0, g.out_stride1 = out_stride1, g.k_cache = k_cache;
+    g.seq_lens = seq_lens, g.gather_lens = gather_lens, g.block_table = block_table;
+    g.max_blocks_per_seq = max_blocks_per_seq, g.block_size = block_size, g.block_stride = block_stride, g.offset = offset;
+    g.nope_dim = nope_dim, g.rope_dim = rope_dim, g.scale_slots = scale_slots, g.index64 = index64;
+    // gather lengths live on the device; size the grid from the room the output has per request
+    int64_t ctas = (tokens_hint + WARPS - 1) / WARPS;
+    if (ctas < 1) ctas = 1;
+    if (ctas > 256) ctas = 256;
+    const auto addr = [](const void* p) { return reinterpret_cast<uintptr_t>(p); };
+    const bool fast = nope_dim == kNopeDim && rope_dim == kRopeDim && scale_slots == kScaleBytes &&
+                      ((addr(k_cache) | static_cast<uintptr_t>(block_stride)) & 15u) == 0 && (addr(out) & 15u) == 0 &&
+                      out_stride0 % 8 == 0 && out_stride1 % 8 == 0 && (block_size * kTokenDataBytes) % 8 == 0;
+    const dim3 grid(static_cast<unsigned>(ctas), static_cast<unsigned>(num_reqs));
+    if (fast) gather_dequant_requests_kernel<WARPS, true><<<grid, WARPS * 32, 0, stream>>>(g);
+    else gather_dequant_requests_kernel<WARPS, false><<<grid, WARPS * 32, 0, stream>>>(g);
     count_launch();
     return cudaGetLastError();
 }

@@ -16,6 +16,7 @@ EXPORTS = (
     "dsv4_qnorm_rope_kv_insert",
     "dsv4_qnorm_rope_kv_insert_checked",
     "dsv4_gather_dequant_k_cache",
+    "dsv4_dequantize_and_gather_k_cache",
     "dsv4_hbm_probe",
     "dsv4_device_error",
     "dsv4_set_variant",
@@ -59,6 +60,9 @@ def lib() -> ctypes.CDLL:
     L.dsv4_qnorm_rope_kv_insert_checked.restype = i32
     L.dsv4_gather_dequant_k_cache.argtypes = [vp, vp, i64, vp, i64, i64, i64, vp]
     L.dsv4_gather_dequant_k_cache.restype = i32
+    L.dsv4_dequantize_and_gather_k_cache.argtypes = [vp, i64, i64, i64, vp, vp, vp, vp, i64, i64, i64, i64, i64,
+                                                     i32, i32, i32, i32, vp]
+    L.dsv4_dequantize_and_gather_k_cache.restype = i32
     L.dsv4_hbm_probe.argtypes = [i32, vp, i64, vp]
     L.dsv4_hbm_probe.restype = i32
     L.dsv4_device_error.argtypes = [vp]

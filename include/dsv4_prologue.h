@@ -93,6 +93,30 @@ int dsv4_gather_dequant_k_cache(const void* k_cache, const int64_t* slots, int64
                                 int64_t kv_block_stride_bytes, void* cuda_stream);
 
 /*
+ * The reference operator
+ *   dequantize_and_gather_k_cache(out, k_cache, seq_lens, gather_lens, block_table, block_size, offset,
+ *                                 rope_dim, nope_dim, scale_slots)
+ * (src/flaggems_vllm/ops/deepseek_v4_attention_dequantize_and_gather_k_cache.py:123-172, kernel :38-120):
+ * for request r and i < gather_lens[r] (all of seq_lens[r] when gather_lens is NULL),
+ *   out[r, offset + i, 0 : nope_dim + rope_dim]
+ * is the cached token at position seq_lens[r] - gather_lens[r] + i, located through
+ * block_table[r, position / cache_block_size]; nope_dim e4m3 values times 2^(code - 127) per group of 64,
+ * rounded to bf16, then rope_dim cached bf16 values.  A cached token is nope_dim + 2*rope_dim data bytes;
+ * a block holds cache_block_size of them, then cache_block_size * scale_slots scale bytes.
+ * out is bf16 with element strides out_stride0 / out_stride1 and unit stride in the last dimension;
+ * out_tokens (its second extent) only sizes the grid.  seq_lens, gather_lens and block_table
+ * ([num_reqs, max_blocks_per_seq], contiguous) are int32, or int64 when index_is_int64 != 0.
+ * num_reqs <= 65535.  The DeepSeek-V4 layout (448 / 64 / 8) with 16-byte aligned rows takes a
+ * vectorised path; anything else a scalar one.
+ */
+int dsv4_dequantize_and_gather_k_cache(void* out, int64_t out_stride0, int64_t out_stride1, int64_t out_tokens,
+                                       const void* k_cache, const void* seq_lens, const void* gather_lens,
+                                       const void* block_table, int64_t num_reqs, int64_t max_blocks_per_seq,
+                                       int64_t cache_block_size, int64_t kv_block_stride_bytes, int64_t offset,
+                                       int32_t nope_dim, int32_t rope_dim, int32_t scale_slots, int32_t index_is_int64,
+                                       void* cuda_stream);
+
+/*
  * Bandwidth probe with the prologue's q access pattern and no arithmetic, over `rows` rows of
  * 1 KiB starting at `buffer` (16-byte aligned): mode 0 reads every row and writes it back in
  * place, mode 1 only reads, mode 2 only writes (the buffer's contents are overwritten).  Used by

@@ -40,6 +40,8 @@ def lib() -> ctypes.CDLL:
             getattr(L, name).restype = None
         L.dsv4_oracle_ue8m0_codes.argtypes = [vp, vp, vp, i64]
         L.dsv4_oracle_ue8m0_codes.restype = None
+        L.dsv4_oracle_dequantize_and_gather.argtypes = [vp, i64, i64, vp, vp, vp, vp, i64, i64, i64, i64, i64, i32, i32, i32]
+        L.dsv4_oracle_dequantize_and_gather.restype = i32
         L.dsv4_oracle_version.restype = ctypes.c_char_p
         _lib = L
     return _lib
@@ -76,6 +78,22 @@ def gather_dequant(k_cache, slots, cache_block_size, threads=0) -> torch.Tensor:
     if rc != 0:
         raise ValueError(f"dsv4_oracle_gather_dequant rejected its arguments (rc={rc})")
     return out
+
+
+def dequantize_and_gather(out, k_cache, seq_lens, gather_lens, block_table, block_size, offset=0, rope_dim=64,
+                          nope_dim=None, scale_slots=None) -> None:
+    """Same arguments as the reference operator, on CPU tensors (int32 index tensors); fills `out`."""
+    _cpu(k_cache, torch.uint8), _cpu(seq_lens, torch.int32), _cpu(block_table, torch.int32)
+    assert out.dtype == torch.bfloat16 and out.dim() == 3 and out.stride(2) == 1 and k_cache.dim() == 2
+    nope_dim = out.shape[-1] - rope_dim if nope_dim is None else nope_dim
+    scale_slots = (nope_dim + 63) // 64 + (1 if nope_dim % 64 == 0 else 0) if scale_slots is None else scale_slots
+    gl = None if gather_lens is None else _cpu(gather_lens, torch.int32).data_ptr()
+    rc = lib().dsv4_oracle_dequantize_and_gather(
+        out.data_ptr(), out.stride(0), out.stride(1), k_cache.data_ptr(), seq_lens.data_ptr(), gl, block_table.data_ptr(),
+        seq_lens.shape[0], block_table.shape[1], int(block_size), k_cache.stride(0), int(offset), int(nope_dim),
+        int(rope_dim), int(scale_slots))
+    if rc != 0:
+        raise ValueError("dsv4_oracle_dequantize_and_gather rejected its arguments")
 
 
 def e4m3_from_f32(x: torch.Tensor) -> torch.Tensor:

@@ -291,4 +291,33 @@ int dsv4_oracle_gather_dequant(const uint8_t* k_cache, const int64_t* slots, int
     return 0;
 }
 
+/*
+ * The request / block-table form of the reader, any nope / rope / scale_slots:
+ * src/flaggems_vllm/ops/deepseek_v4_attention_dequantize_and_gather_k_cache.py:61-120.
+ * out[r, offset+i, :] for i < gather_lens[r] (seq_lens[r] when gather_lens is NULL) is the token at
+ * position seq_lens[r]-gather_len+i of request r; int32 index arrays; out strides in elements.
+ */
+int dsv4_oracle_dequantize_and_gather(uint16_t* out, int64_t stride0, int64_t stride1, const uint8_t* k_cache,
+                                      const int32_t* seq_lens, const int32_t* gather_lens, const int32_t* block_table,
+                                      int64_t num_reqs, int64_t max_blocks_per_seq, int64_t block_size,
+                                      int64_t block_stride, int64_t offset, int nope_dim, int rope_dim, int scale_slots) {
+    if (num_reqs < 0 || nope_dim < 0 || rope_dim < 0) return -1;
+    const int64_t token_data = nope_dim + 2 * rope_dim;
+    for (int64_t r = 0; r < num_reqs; ++r) {
+        int64_t seq_len = seq_lens[r], gather_len = gather_lens ? gather_lens[r] : seq_len;
+        for (int64_t i = 0; i < gather_len; ++i) {
+            int64_t pos = seq_len - gather_len + i;
+            int64_t block = block_table[r * max_blocks_per_seq + pos / block_size], in_block = pos % block_size;
+            const uint8_t* base = k_cache + block * block_stride;
+            const uint8_t* data = base + in_block * token_data;
+            const uint8_t* scales = base + block_size * token_data + in_block * scale_slots;
+            uint16_t* row = out + r * stride0 + (offset + i) * stride1;
+            for (int j = 0; j < nope_dim; ++j)
+                row[j] = f32_to_bf16_bits(e4m3_bits_to_f32(data[j]) * exp2f((float)scales[j / 64] - 127.0f));
+            memcpy(row + nope_dim, data + nope_dim, (size_t)rope_dim * 2);
+        }
+    }
+    return 0;
+}
+
 const char* dsv4_oracle_version(void) { return "dsv4-oracle 1"; }

@@ -65,3 +65,45 @@ def load_upstream_test_module():
             del sys.modules[k]
         sys.modules.update({k: v for k, v in saved.items() if v is not None})
     return module
+
+
+def load_upstream_helper_test(test_file: str, op_module: str, op_names: tuple[str, ...]):
+    """Execute another upstream test file (e.g. tests/test_deepseek_v4_attention_*.py) with stand-ins for
+    the package names it imports, to reach the pure-torch helpers it defines (expected-value builders,
+    reference functions).  `op_module` is the dotted module the test imports its operator from."""
+    root = upstream_root()
+    if root is None or not (root / "tests" / test_file).exists():
+        raise FileNotFoundError("upstream tree not present")
+    saved = {k: sys.modules.get(k) for k in list(sys.modules) if k == "flaggems_vllm" or k.startswith("flaggems_vllm.")}
+    for k in saved:
+        del sys.modules[k]
+
+    def mod(name, **attrs):
+        m = types.ModuleType(name)
+        m.__dict__.update(attrs)
+        sys.modules[name] = m
+        return m
+
+    def _unbound(*_a, **_k):
+        raise RuntimeError("stand-in: the operator is not bound in the reference loader")
+
+    import torch
+
+    testing = mod("flaggems_vllm.testing", assert_close=lambda a, b, dtype=None, equal_nan=False, **k: torch.testing.assert_close(a, b, equal_nan=equal_nan))
+    pkg = mod("flaggems_vllm", device="cpu", vendor_name="nvidia", testing=testing, __path__=[])
+    mod("flaggems_vllm.ops", __path__=[])
+    mod(op_module, **{n: _unbound for n in op_names})
+    mod("flaggems_vllm.utils", __path__=[])
+    mod("flaggems_vllm.utils.device_info", get_device_capability=lambda: (10, 0))
+    mod("_dsv4_upstream_tests", __path__=[])
+    mod("_dsv4_upstream_tests.conftest", QUICK_MODE=True)
+    try:
+        spec = importlib.util.spec_from_file_location(f"_dsv4_upstream_tests.{Path(test_file).stem}", root / "tests" / test_file)
+        module = importlib.util.module_from_spec(spec)
+        sys.modules[spec.name] = module
+        spec.loader.exec_module(module)
+    finally:
+        for k in [k for k in sys.modules if k == "flaggems_vllm" or k.startswith("flaggems_vllm.")]:
+            del sys.modules[k]
+        sys.modules.update({k: v for k, v in saved.items() if v is not None})
+    return module

@@ -134,5 +134,39 @@ def main() -> None:
     print("cpu_ref ok")
 
 
+def gather_cases() -> None:
+    """Known-answer vectors of the cache reader, built with the upstream test's own `_fill_cache`
+    (tests/test_deepseek_v4_attention_dequantize_and_gather_k_cache.py:42-63) and the parameter sets of
+    its accuracy test (:66-119): hand-made cache rows and the rows they must de-quantise to."""
+    G = ref_loader.load_upstream_helper_test(
+        "test_deepseek_v4_attention_dequantize_and_gather_k_cache.py",
+        "flaggems_vllm.ops.deepseek_v4_attention_dequantize_and_gather_k_cache", ("dequantize_and_gather_k_cache",))
+    for batch, seq_len, gather_len, block_size, nope_dim, rope_dim in ((1, 6, 3, 4, 64, 16), (2, 12, 5, 64, 448, 64),
+                                                                        (3, 150, 70, 64, 448, 64)):
+        scale_slots = (nope_dim + 63) // 64 + (1 if nope_dim % 64 == 0 else 0)
+        token_data = nope_dim + rope_dim * 2
+        blocks_per_seq = (seq_len + block_size - 1) // block_size
+        num_blocks = batch * blocks_per_seq
+        k_cache = torch.zeros(num_blocks, block_size * (token_data + scale_slots), dtype=torch.uint8)
+        expected = torch.zeros(batch, gather_len, nope_dim + rope_dim, dtype=torch.bfloat16)
+        rows = {}
+        for req in range(batch):
+            for i in range(gather_len):
+                pos = seq_len - gather_len + i
+                slot = (req * blocks_per_seq + pos // block_size) * block_size + pos % block_size
+                rows[slot] = expected[req : req + 1, i : i + 1, :]
+        G._fill_cache(k_cache, rows, block_size, nope_dim, rope_dim, scale_slots)
+        np.savez_compressed(
+            HERE / f"gather_b{batch}_s{seq_len}_g{gather_len}_bs{block_size}_n{nope_dim}_r{rope_dim}.npz",
+            k_cache=k_cache.numpy(), expected=u16(expected), seq_lens=np.full(batch, seq_len, np.int32),
+            gather_lens=np.full(batch, gather_len, np.int32),
+            block_table=np.arange(num_blocks, dtype=np.int32).reshape(batch, blocks_per_seq), block_size=block_size,
+            nope_dim=nope_dim, rope_dim=rope_dim, scale_slots=scale_slots)
+        print("gather", batch, seq_len, gather_len, block_size, nope_dim, rope_dim, "ok")
+
+
 if __name__ == "__main__":
-    main()
+    if len(sys.argv) < 2 or sys.argv[1] == "prologue":
+        main()
+    if len(sys.argv) < 2 or sys.argv[1] == "gather":
+        gather_cases()
