@@ -145,6 +145,21 @@ int dsv4_dequantize_and_gather_k_cache(void* out, int64_t out_stride0, int64_t o
         scale_slots, index_is_int64 ? 1 : 0, out_tokens, static_cast<cudaStream_t>(cuda_stream)));
 }
 
+int dsv4_fused_q_kv_rmsnorm(const void* qr, void* qr_out, const void* q_weight, int64_t q_in_stride,
+                            int64_t q_out_stride, int64_t q_size, const void* kv, void* kv_out, const void* kv_weight,
+                            int64_t kv_in_stride, int64_t kv_out_stride, int64_t kv_size, int64_t num_tokens, float eps,
+                            void* cuda_stream) {
+    if (num_tokens < 0 || q_size <= 0 || kv_size <= 0 || q_size >= (1LL << 31) || kv_size >= (1LL << 31))
+        return DSV4_ERR_BAD_SIZE;
+    if (num_tokens == 0) return DSV4_OK;
+    if (!qr || !qr_out || !q_weight || !kv || !kv_out || !kv_weight) return DSV4_ERR_NULL_POINTER;
+    const auto odd = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 1u) != 0; };
+    if (odd(qr) || odd(qr_out) || odd(q_weight) || odd(kv) || odd(kv_out) || odd(kv_weight)) return DSV4_ERR_MISALIGNED;
+    return static_cast<int>(launch_q_kv_rmsnorm(qr, qr_out, q_weight, q_in_stride, q_out_stride, q_size, kv, kv_out,
+                                                kv_weight, kv_in_stride, kv_out_stride, kv_size, num_tokens, eps,
+                                                static_cast<cudaStream_t>(cuda_stream)));
+}
+
 int dsv4_hbm_probe(int mode, void* buffer, int64_t rows, void* cuda_stream) {
     if (mode < 0 || mode > 2) return DSV4_ERR_BAD_VARIANT;
     if (rows < 0 || rows >= (1LL << 31)) return DSV4_ERR_BAD_SIZE;

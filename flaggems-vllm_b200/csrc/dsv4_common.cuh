@@ -332,6 +332,9 @@ cudaError_t launch_gather_dequant_requests(uint8_t* out, int64_t out_stride0, in
                                            int64_t num_reqs, int64_t max_blocks_per_seq, int64_t block_size,
                                            int64_t block_stride, int64_t offset, int nope_dim, int rope_dim, int scale_slots,
                                            int index64, int64_t tokens_hint, cudaStream_t stream);
+cudaError_t launch_q_kv_rmsnorm(const void* q, void* q_out, const void* q_weight, int64_t q_in_stride, int64_t q_out_stride,
+                                int64_t q_size, const void* kv, void* kv_out, const void* kv_weight, int64_t kv_in_stride,
+                                int64_t kv_out_stride, int64_t kv_size, int64_t num_tokens, float eps, cudaStream_t stream);
 cudaError_t launch_hbm_probe(int mode, uint8_t* buf, int64_t rows, uint32_t* sink, cudaStream_t stream);
 void count_launch();
 cudaError_t read_device_error(int* value);

@@ -1,0 +1,119 @@
+// fused_q_kv_rmsnorm: the step before the prologue - weighted RMSNorm of the q low-rank
+// activations [N, Q] and of the latent KV [N, KV] in one launch.
+// Reference: src/flaggems_vllm/ops/deepseek_v4_attention_fused_q_kv_rmsnorm.py:24-103
+//   y = (x * rsqrt(mean(x^2) + eps)) * w, fp32 arithmetic, bf16 in and out.
+// One warp per row; a row of up to 2048 elements stays in registers between the reduction and
+// the scaling (one read, one write per element); longer or unaligned rows take a two-pass
+// scalar path.  Rows [0, N) are q rows, rows [N, 2N) are kv rows.
+#include "dsv4_common.cuh"
+
+namespace dsv4 {
+namespace {
+
+struct NormRows {
+    const uint8_t* in;
+    uint8_t* out;
+    const uint8_t* weight;
+    int64_t in_stride, out_stride;  // elements
+    int32_t size;
+    int32_t vec_ok;                 // 16-byte path usable for this tensor
+};
+
+constexpr int kMaxChunks = 8;  // 16-byte chunks per lane held in registers: 8 * 32 * 8 = 2048 elements
+
+__device__ __forceinline__ float inv_rms_of(float sum, int size, float eps) {
+    const float v = __fadd_rn(__fdiv_rn(sum, static_cast<float>(size)), eps);
+    const float r0 = rsqrtf(v);
+    return fmaf(r0, fmaf(-0.5f * v * r0, r0, 0.5f), r0);
+}
+
+template <int WARPS>
+__global__ void __launch_bounds__(WARPS * 32) q_kv_rmsnorm_kernel(const NormRows q, const NormRows kv, int64_t num_tokens,
+                                                                 float eps) {
+    const int lane = threadIdx.x & 31;
+    const int64_t r = static_cast<int64_t>(blockIdx.x) * WARPS + (threadIdx.x >> 5);
+    if (r >= 2 * num_tokens) return;
+    const bool is_q = r < num_tokens;
+    const NormRows& t = is_q ? q : kv;
+    const int64_t token = is_q ? r : r - num_tokens;
+    const uint8_t* in = t.in + token * t.in_stride * 2;
+    uint8_t* out = t.out + token * t.out_stride * 2;
+    const int size = t.size;
+    if (t.vec_ok) {
+        const int chunks = size >> 3;
+        uint4 x[kMaxChunks];
+        float acc = 0.0f;
+#pragma unroll
+        for (int j = 0; j < kMaxChunks; ++j) {
+            const int c = lane + 32 * j;
+            x[j] = make_uint4(0u, 0u, 0u, 0u);
+            if (c < chunks) x[j] = ld_stream16(in + 16 * c);
+        }
+#pragma unroll
+        for (int j = 0; j < kMaxChunks; ++j) {
+            float f[8];
+            unpack8(x[j], f);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc = fmaf(f[i], f[i], acc);
+        }
+#pragma unroll
+        for (int m = 16; m > 0; m >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, m);
+        const float rr = inv_rms_of(acc, size, eps);
+#pragma unroll
+        for (int j = 0; j < kMaxChunks; ++j) {
+            const int c = lane + 32 * j;
+            if (c < chunks) {
+                float f[8], w[8];
+                unpack8(x[j], f);
+                unpack8(__ldg(reinterpret_cast<const uint4*>(t.weight + 16 * c)), w);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) f[i] = __fmul_rn(__fmul_rn(f[i], rr), w[i]);
+                st_stream16(out + 16 * c, pack8(f));
+            }
+        }
+    } else {
+        const uint16_t* in16 = reinterpret_cast<const uint16_t*>(in);
+        const uint16_t* w16 = reinterpret_cast<const uint16_t*>(t.weight);
+        uint16_t* out16 = reinterpret_cast<uint16_t*>(out);
+        float acc = 0.0f;
+        for (int i = lane; i < size; i += 32) {
+            const float f = bf16_lo(in16[i]);
+            acc = fmaf(f, f, acc);
+        }
+#pragma unroll
+        for (int m = 16; m > 0; m >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, m);
+        const float rr = inv_rms_of(acc, size, eps);
+        for (int i = lane; i < size; i += 32) {
+            const float y = __fmul_rn(__fmul_rn(bf16_lo(in16[i]), rr), bf16_lo(w16[i]));
+            out16[i] = static_cast<uint16_t>(pack_bf16x2(y, 0.0f) & 0xffffu);
+        }
+    }
+}
+
+bool vec_ok(const void* in, const void* out, const void* w, int64_t in_stride, int64_t out_stride, int64_t size) {
+    const auto a = [](const void* p) { return reinterpret_cast<uintptr_t>(p) & 15u; };
+    return a(in) == 0 && a(out) == 0 && a(w) == 0 && in_stride % 8 == 0 && out_stride % 8 == 0 && size % 8 == 0 &&
+           size <= kMaxChunks * 256;
+}
+
+}  // namespace
+
+cudaError_t launch_q_kv_rmsnorm(const void* q, void* q_out, const void* q_weight, int64_t q_in_stride, int64_t q_out_stride,
+                                int64_t q_size, const void* kv, void* kv_out, const void* kv_weight, int64_t kv_in_stride,
+                                int64_t kv_out_stride, int64_t kv_size, int64_t num_tokens, float eps, cudaStream_t stream) {
+    constexpr int WARPS = 4;
+    if (num_tokens == 0) return cudaSuccess;
+    NormRows a{static_cast<const uint8_t*>(q), static_cast<uint8_t*>(q_out), static_cast<const uint8_t*>(q_weight),
+               q_in_stride, q_out_stride, static_cast<int32_t>(q_size),
+               vec_ok(q, q_out, q_weight, q_in_stride, q_out_stride, q_size) ? 1 : 0};
+    NormRows b{static_cast<const uint8_t*>(kv), static_cast<uint8_t*>(kv_out), static_cast<const uint8_t*>(kv_weight),
+               kv_in_stride, kv_out_stride, static_cast<int32_t>(kv_size),
+               vec_ok(kv, kv_out, kv_weight, kv_in_stride, kv_out_stride, kv_size) ? 1 : 0};
+    const int64_t grid = (2 * num_tokens + WARPS - 1) / WARPS;
+    if (grid > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
+    q_kv_rmsnorm_kernel<WARPS><<<static_cast<unsigned>(grid), WARPS * 32, 0, stream>>>(a, b, num_tokens, eps);
+    count_launch();
+    return cudaGetLastError();
+}
+
+}  // namespace dsv4

@@ -17,6 +17,7 @@ EXPORTS = (
     "dsv4_qnorm_rope_kv_insert_checked",
     "dsv4_gather_dequant_k_cache",
     "dsv4_dequantize_and_gather_k_cache",
+    "dsv4_fused_q_kv_rmsnorm",
     "dsv4_hbm_probe",
     "dsv4_device_error",
     "dsv4_set_variant",
@@ -63,6 +64,8 @@ def lib() -> ctypes.CDLL:
     L.dsv4_dequantize_and_gather_k_cache.argtypes = [vp, i64, i64, i64, vp, vp, vp, vp, i64, i64, i64, i64, i64,
                                                      i32, i32, i32, i32, vp]
     L.dsv4_dequantize_and_gather_k_cache.restype = i32
+    L.dsv4_fused_q_kv_rmsnorm.argtypes = [vp, vp, vp, i64, i64, i64, vp, vp, vp, i64, i64, i64, i64, f32, vp]
+    L.dsv4_fused_q_kv_rmsnorm.restype = i32
     L.dsv4_hbm_probe.argtypes = [i32, vp, i64, vp]
     L.dsv4_hbm_probe.restype = i32
     L.dsv4_device_error.argtypes = [vp]

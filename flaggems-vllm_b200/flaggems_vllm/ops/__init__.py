@@ -1,5 +1,6 @@
 """Operators of this package (reference: src/flaggems_vllm/ops/__init__.py:61-63,191)."""
 from .deepseek_v4_attention_dequantize_and_gather_k_cache import dequantize_and_gather_k_cache
+from .deepseek_v4_attention_fused_q_kv_rmsnorm import fused_q_kv_rmsnorm
 from .fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert import (
     fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert,
     fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert_checked,
@@ -8,6 +9,7 @@ from .gather_dequant_k_cache import gather_dequant_k_cache_slots
 from .host_staged import HostStagedPrologue
 
 __all__ = [
+    "fused_q_kv_rmsnorm",
     "dequantize_and_gather_k_cache",
     "fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert",
     "fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert_checked",

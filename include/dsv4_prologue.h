@@ -117,6 +117,21 @@ int dsv4_dequantize_and_gather_k_cache(void* out, int64_t out_stride0, int64_t o
                                        void* cuda_stream);
 
 /*
+ * The step before the prologue.  Replaces the reference operator
+ *   fused_q_kv_rmsnorm(qr, kv, q_weight, kv_weight, eps) -> (qr_out, kv_out)
+ * (src/flaggems_vllm/ops/deepseek_v4_attention_fused_q_kv_rmsnorm.py:65-103, kernel :24-62):
+ * out = (x * rsqrt(mean(x^2) + eps)) * weight per row, fp32 arithmetic, for the q low-rank
+ * activations [num_tokens, q_size] and the latent KV [num_tokens, kv_size] in one launch.  All six
+ * tensors bf16 with unit stride in the last dimension; row strides in elements; outputs are
+ * caller-allocated.  Rows of up to 2048 elements with 16-byte aligned bases and strides stay in
+ * registers (one read, one write); others take a two-pass scalar path.
+ */
+int dsv4_fused_q_kv_rmsnorm(const void* qr, void* qr_out, const void* q_weight, int64_t q_in_stride,
+                            int64_t q_out_stride, int64_t q_size, const void* kv, void* kv_out, const void* kv_weight,
+                            int64_t kv_in_stride, int64_t kv_out_stride, int64_t kv_size, int64_t num_tokens, float eps,
+                            void* cuda_stream);
+
+/*
  * Bandwidth probe with the prologue's q access pattern and no arithmetic, over `rows` rows of
  * 1 KiB starting at `buffer` (16-byte aligned): mode 0 reads every row and writes it back in
  * place, mode 1 only reads, mode 2 only writes (the buffer's contents are overwritten).  Used by

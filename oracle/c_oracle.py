@@ -42,6 +42,8 @@ def lib() -> ctypes.CDLL:
         L.dsv4_oracle_ue8m0_codes.restype = None
         L.dsv4_oracle_dequantize_and_gather.argtypes = [vp, i64, i64, vp, vp, vp, vp, i64, i64, i64, i64, i64, i32, i32, i32]
         L.dsv4_oracle_dequantize_and_gather.restype = i32
+        L.dsv4_oracle_weighted_rmsnorm.argtypes = [vp, vp, vp, i64, i64, i64, i64, f32]
+        L.dsv4_oracle_weighted_rmsnorm.restype = i32
         L.dsv4_oracle_version.restype = ctypes.c_char_p
         _lib = L
     return _lib
@@ -94,6 +96,18 @@ def dequantize_and_gather(out, k_cache, seq_lens, gather_lens, block_table, bloc
         int(rope_dim), int(scale_slots))
     if rc != 0:
         raise ValueError("dsv4_oracle_dequantize_and_gather rejected its arguments")
+
+
+def weighted_rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """bf16 [rows, size] -> (x * rsqrt(mean(x^2) + eps)) * weight, fp32 arithmetic."""
+    assert x.dtype == torch.bfloat16 and x.dim() == 2 and x.stride(1) == 1 and x.device.type == "cpu"
+    _cpu(weight, torch.bfloat16)
+    out = torch.empty(x.shape, dtype=torch.bfloat16)
+    rc = lib().dsv4_oracle_weighted_rmsnorm(x.data_ptr(), weight.data_ptr(), out.data_ptr(), x.shape[0], x.shape[1],
+                                            x.stride(0), out.stride(0), float(eps))
+    if rc != 0:
+        raise ValueError("dsv4_oracle_weighted_rmsnorm rejected its arguments")
+    return out
 
 
 def e4m3_from_f32(x: torch.Tensor) -> torch.Tensor:

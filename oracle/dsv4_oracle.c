@@ -320,4 +320,29 @@ int dsv4_oracle_dequantize_and_gather(uint16_t* out, int64_t stride0, int64_t st
     return 0;
 }
 
+/*
+ * Weighted RMSNorm of `rows` rows of `size` bf16 values: out = (x * rsqrt(mean(x^2) + eps)) * w, the
+ * statement of tests/test_deepseek_v4_attention_fused_q_kv_rmsnorm.py:40-44 (`_rmsnorm_ref`) and of
+ * src/flaggems_vllm/ops/deepseek_v4_attention_fused_q_kv_rmsnorm.py:55-61.  Strides in elements.
+ */
+int dsv4_oracle_weighted_rmsnorm(const uint16_t* x, const uint16_t* w, uint16_t* out, int64_t rows, int64_t size,
+                                 int64_t in_stride, int64_t out_stride, float eps) {
+    if (rows < 0 || size <= 0) return -1;
+    for (int64_t r = 0; r < rows; ++r) {
+        const uint16_t* xi = x + r * in_stride;
+        double acc = 0.0;
+        for (int64_t i = 0; i < size; ++i) {
+            double v = bf16_bits_to_f32(xi[i]);
+            acc += v * v;
+        }
+        float variance = (float)acc / (float)size;
+        float rr = 1.0f / sqrtf(variance + eps);
+        for (int64_t i = 0; i < size; ++i) {
+            float y = bf16_bits_to_f32(xi[i]) * rr;
+            out[r * out_stride + i] = f32_to_bf16_bits(y * bf16_bits_to_f32(w[i]));
+        }
+    }
+    return 0;
+}
+
 const char* dsv4_oracle_version(void) { return "dsv4-oracle 1"; }

@@ -165,7 +165,29 @@ def gather_cases() -> None:
         print("gather", batch, seq_len, gather_len, block_size, nope_dim, rope_dim, "ok")
 
 
+def rmsnorm_cases() -> None:
+    """Seeded inputs through the upstream test's own torch reference `_rmsnorm_ref`
+    (tests/test_deepseek_v4_attention_fused_q_kv_rmsnorm.py:40-44), at its two shapes (:47-53) plus one
+    with row strides and values of mixed magnitude."""
+    R = ref_loader.load_upstream_helper_test(
+        "test_deepseek_v4_attention_fused_q_kv_rmsnorm.py", "flaggems_vllm.ops.deepseek_v4_attention_fused_q_kv_rmsnorm",
+        ("fused_q_kv_rmsnorm",))
+    for idx, (tokens, qdim, kvdim) in enumerate(((4, 256, 128), (8, 1536, 512), (33, 1536, 512))):
+        g = torch.Generator().manual_seed(100 + idx)
+        rn = lambda *s: torch.randn(*s, generator=g).to(torch.bfloat16)  # noqa: E731
+        qr, kv, qw, kw = rn(tokens, qdim), rn(tokens, kvdim), rn(qdim), rn(kvdim)
+        if idx == 2:
+            qr = (qr.float() * torch.logspace(-3, 3, tokens)[:, None]).to(torch.bfloat16)
+            kv[0] = 0
+        np.savez_compressed(HERE / f"rmsnorm_t{tokens}_q{qdim}_kv{kvdim}.npz", qr=u16(qr), kv=u16(kv), q_weight=u16(qw),
+                            kv_weight=u16(kw), eps=1e-6, q_out=u16(R._rmsnorm_ref(qr, qw, 1e-6)),
+                            kv_out=u16(R._rmsnorm_ref(kv, kw, 1e-6)))
+        print("rmsnorm", tokens, qdim, kvdim, "ok")
+
+
 if __name__ == "__main__":
+    if len(sys.argv) < 2 or sys.argv[1] == "rmsnorm":
+        rmsnorm_cases()
     if len(sys.argv) < 2 or sys.argv[1] == "prologue":
         main()
     if len(sys.argv) < 2 or sys.argv[1] == "gather":
