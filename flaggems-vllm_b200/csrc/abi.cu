@@ -160,6 +160,26 @@ int dsv4_fused_q_kv_rmsnorm(const void* qr, void* qr_out, const void* q_weight, 
                                                 static_cast<cudaStream_t>(cuda_stream)));
 }
 
+int dsv4_fused_inv_rope_fp8_quant(const void* o, int64_t o_stride_token, int64_t o_stride_head, const int64_t* positions,
+                                  const float* cos_sin_cache, int64_t cos_sin_stride, void* fp8_out, void* scale_out,
+                                  int64_t scale_stride_group, int64_t num_tokens, int64_t padded_tokens, int64_t n_groups,
+                                  int64_t heads_per_group, float eps, int32_t packed_ue8m0_scales, void* cuda_stream) {
+    if (num_tokens < 0 || padded_tokens < num_tokens || padded_tokens % 4 != 0 || n_groups <= 0 || heads_per_group <= 0 ||
+        n_groups * heads_per_group >= (1LL << 31))
+        return DSV4_ERR_BAD_SIZE;
+    if (num_tokens == 0) return DSV4_OK;
+    if (!o || !positions || !cos_sin_cache || !fp8_out || !scale_out) return DSV4_ERR_NULL_POINTER;
+    if (!aligned16(o) || !aligned16(cos_sin_cache) || o_stride_token % 8 != 0 || o_stride_head % 8 != 0 ||
+        cos_sin_stride % 4 != 0 || (reinterpret_cast<uintptr_t>(fp8_out) & 7u) != 0 ||
+        (reinterpret_cast<uintptr_t>(scale_out) & 3u) != 0)
+        return DSV4_ERR_MISALIGNED;
+    return static_cast<int>(launch_inv_rope_fp8_quant(o, o_stride_token, o_stride_head, positions, cos_sin_cache, cos_sin_stride,
+                                                      fp8_out, scale_out, scale_stride_group, num_tokens, padded_tokens,
+                                                      static_cast<int>(n_groups * heads_per_group),
+                                                      static_cast<int>(heads_per_group), eps, packed_ue8m0_scales ? 1 : 0,
+                                                      static_cast<cudaStream_t>(cuda_stream)));
+}
+
 int dsv4_hbm_probe(int mode, void* buffer, int64_t rows, void* cuda_stream) {
     if (mode < 0 || mode > 2) return DSV4_ERR_BAD_VARIANT;
     if (rows < 0 || rows >= (1LL << 31)) return DSV4_ERR_BAD_SIZE;

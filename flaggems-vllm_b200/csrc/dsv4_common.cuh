@@ -335,6 +335,10 @@ cudaError_t launch_gather_dequant_requests(uint8_t* out, int64_t out_stride0, in
 cudaError_t launch_q_kv_rmsnorm(const void* q, void* q_out, const void* q_weight, int64_t q_in_stride, int64_t q_out_stride,
                                 int64_t q_size, const void* kv, void* kv_out, const void* kv_weight, int64_t kv_in_stride,
                                 int64_t kv_out_stride, int64_t kv_size, int64_t num_tokens, float eps, cudaStream_t stream);
+cudaError_t launch_inv_rope_fp8_quant(const void* o, int64_t o_stride_token, int64_t o_stride_head, const int64_t* positions,
+                                      const float* cos_sin, int64_t cos_sin_stride, void* fp8, void* scale,
+                                      int64_t scale_stride_group, int64_t num_tokens, int64_t padded_tokens, int num_heads,
+                                      int heads_per_group, float eps, int packed, cudaStream_t stream);
 cudaError_t launch_hbm_probe(int mode, uint8_t* buf, int64_t rows, uint32_t* sink, cudaStream_t stream);
 void count_launch();
 cudaError_t read_device_error(int* value);

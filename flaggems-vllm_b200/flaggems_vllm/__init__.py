@@ -13,5 +13,7 @@ vendor_name = runtime.device.vendor_name
 
 # compatibility alias kept by the reference (src/flaggems_vllm/__init__.py:37-46)
 ops_deepseek_v4_qnorm_rope_kv_rope_quant_insert = _prologue
+ops_inv_rope_fp8_quant = ops.fused_inv_rope_fp8_quant
+SUPPORTED_FP8_DTYPE = ops.fused_inv_rope_fp8_quant.__globals__["SUPPORTED_FP8_DTYPE"]
 
 __version__ = "0.1.0"

@@ -18,6 +18,7 @@ EXPORTS = (
     "dsv4_gather_dequant_k_cache",
     "dsv4_dequantize_and_gather_k_cache",
     "dsv4_fused_q_kv_rmsnorm",
+    "dsv4_fused_inv_rope_fp8_quant",
     "dsv4_hbm_probe",
     "dsv4_device_error",
     "dsv4_set_variant",
@@ -66,6 +67,8 @@ def lib() -> ctypes.CDLL:
     L.dsv4_dequantize_and_gather_k_cache.restype = i32
     L.dsv4_fused_q_kv_rmsnorm.argtypes = [vp, vp, vp, i64, i64, i64, vp, vp, vp, i64, i64, i64, i64, f32, vp]
     L.dsv4_fused_q_kv_rmsnorm.restype = i32
+    L.dsv4_fused_inv_rope_fp8_quant.argtypes = [vp, i64, i64, vp, vp, i64, vp, vp, i64, i64, i64, i64, i64, f32, i32, vp]
+    L.dsv4_fused_inv_rope_fp8_quant.restype = i32
     L.dsv4_hbm_probe.argtypes = [i32, vp, i64, vp]
     L.dsv4_hbm_probe.restype = i32
     L.dsv4_device_error.argtypes = [vp]

@@ -5,10 +5,12 @@ from .fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert import (
     fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert,
     fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert_checked,
 )
+from .fused_inv_rope_fp8_quant import fused_inv_rope_fp8_quant
 from .gather_dequant_k_cache import gather_dequant_k_cache_slots
 from .host_staged import HostStagedPrologue
 
 __all__ = [
+    "fused_inv_rope_fp8_quant",
     "fused_q_kv_rmsnorm",
     "dequantize_and_gather_k_cache",
     "fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert",

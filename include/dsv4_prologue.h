@@ -132,6 +132,27 @@ int dsv4_fused_q_kv_rmsnorm(const void* qr, void* qr_out, const void* q_weight, 
                             void* cuda_stream);
 
 /*
+ * The attention epilogue that mirrors the prologue.  Replaces the reference operator
+ *   fused_inv_rope_fp8_quant(o, positions, cos_sin_cache, n_groups, heads_per_group, nope_dim=448,
+ *                            rope_dim=64, quant_group_size=128, eps, dtype, tma_aligned_scales)
+ * (src/flaggems_vllm/ops/fused_inv_rope_fp8_quant.py:155-256, kernel :37-152) for head_dim 512 = 448 + 64
+ * and groups of 128: inverse GPT-J RoPE on o[..., 448:512] (rounded to bf16, as the reference's torch
+ * statement tests/test_fused_inv_rope_fp8_quant.py:150-198 does), then per group of 128 values
+ * scale = max(amax, eps)/448 (power of two >= that when packed_ue8m0_scales) and e4m3(x / scale).
+ *   o          bf16 [num_tokens, n_groups*heads_per_group, 512], element strides given, 16-byte aligned rows
+ *   positions  int64 [num_tokens]; cos_sin_cache fp32 rows of 64 (32 cos | 32 sin), row stride in elements
+ *   fp8_out    e4m3 bytes, contiguous [n_groups, num_tokens, heads_per_group*512]
+ *   scale_out  element (g, t, k) at g*scale_stride_group + t + k*padded_tokens (4-byte elements):
+ *              fp32 with k < heads_per_group*4, or int32 with k < heads_per_group holding the head's four
+ *              UE8M0 exponent bytes (group j in byte j); columns t in [num_tokens, padded_tokens) are zeroed.
+ *              padded_tokens = num_tokens rounded up to a multiple of 4.
+ */
+int dsv4_fused_inv_rope_fp8_quant(const void* o, int64_t o_stride_token, int64_t o_stride_head, const int64_t* positions,
+                                  const float* cos_sin_cache, int64_t cos_sin_stride, void* fp8_out, void* scale_out,
+                                  int64_t scale_stride_group, int64_t num_tokens, int64_t padded_tokens, int64_t n_groups,
+                                  int64_t heads_per_group, float eps, int32_t packed_ue8m0_scales, void* cuda_stream);
+
+/*
  * Bandwidth probe with the prologue's q access pattern and no arithmetic, over `rows` rows of
  * 1 KiB starting at `buffer` (16-byte aligned): mode 0 reads every row and writes it back in
  * place, mode 1 only reads, mode 2 only writes (the buffer's contents are overwritten).  Used by

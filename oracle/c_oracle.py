@@ -44,6 +44,8 @@ def lib() -> ctypes.CDLL:
         L.dsv4_oracle_dequantize_and_gather.restype = i32
         L.dsv4_oracle_weighted_rmsnorm.argtypes = [vp, vp, vp, i64, i64, i64, i64, f32]
         L.dsv4_oracle_weighted_rmsnorm.restype = i32
+        L.dsv4_oracle_inv_rope_fp8_quant.argtypes = [vp, i64, i64, vp, vp, i64, vp, vp, i64, i64, i64, f32, i32]
+        L.dsv4_oracle_inv_rope_fp8_quant.restype = i32
         L.dsv4_oracle_version.restype = ctypes.c_char_p
         _lib = L
     return _lib
@@ -108,6 +110,22 @@ def weighted_rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch
     if rc != 0:
         raise ValueError("dsv4_oracle_weighted_rmsnorm rejected its arguments")
     return out
+
+
+def inv_rope_fp8_quant(o, positions, cos_sin_cache, n_groups, heads_per_group, eps=1e-10, packed=False):
+    """(fp8 bytes uint8 [N, G, hpg*512], scales [N, G, hpg*4] fp32 or [N, G, hpg] int32) on CPU tensors."""
+    assert o.dtype == torch.bfloat16 and o.dim() == 3 and o.shape[2] == 512 and o.stride(2) == 1 and o.device.type == "cpu"
+    _cpu(positions, torch.int64), _cpu(cos_sin_cache, torch.float32)
+    n = o.shape[0]
+    assert o.shape[1] == n_groups * heads_per_group
+    fp8 = torch.empty(n, n_groups, heads_per_group * 512, dtype=torch.uint8)
+    scales = torch.empty(n, n_groups, heads_per_group * (1 if packed else 4), dtype=torch.int32 if packed else torch.float32)
+    rc = lib().dsv4_oracle_inv_rope_fp8_quant(o.data_ptr(), o.stride(0), o.stride(1), positions.data_ptr(),
+                                              cos_sin_cache.data_ptr(), cos_sin_cache.stride(0), fp8.data_ptr(),
+                                              scales.data_ptr(), n, n_groups, heads_per_group, float(eps), 1 if packed else 0)
+    if rc != 0:
+        raise ValueError("dsv4_oracle_inv_rope_fp8_quant rejected its arguments")
+    return fp8, scales
 
 
 def e4m3_from_f32(x: torch.Tensor) -> torch.Tensor:

@@ -185,7 +185,43 @@ def rmsnorm_cases() -> None:
         print("rmsnorm", tokens, qdim, kvdim, "ok")
 
 
+def inv_rope_cases() -> None:
+    """Seeded inputs through the upstream test's torch statement `native_fused_inv_rope_fp8_quant`
+    (tests/test_fused_inv_rope_fp8_quant.py:150-198), both scale formats, its head/group shapes (:104-115),
+    a x1000 saturation case (:430-442) and rows built to hit exact powers of two."""
+    shapes = {"NUM_TOKENS": [7], "NUM_HEADS_AND_GROUPS": [(64, 8)], "OUTPUT_LAYOUT_NUM_TOKENS": [7],
+              "OUTPUT_LAYOUT_NUM_HEADS_AND_GROUPS": [(64, 8)], "PER_GROUP_CONTIGUITY_NUM_TOKENS": [7],
+              "REAL_ROPE_NUM_TOKENS": [32], "TMA_ALIGNED_SCALES": [False, True], "SEEDS": [0, 42]}
+    M = ref_loader.load_upstream_helper_test(
+        "test_fused_inv_rope_fp8_quant.py", "flaggems_vllm.ops", ("per_token_group_quant_fp8", "fused_inv_rope_fp8_quant"),
+        package_attrs={"SUPPORTED_FP8_DTYPE": torch.float8_e4m3fn},
+        sibling_modules={"accuracy_utils": {"FUSED_INV_ROPE_FP8_QUANT_SHAPES": shapes}})
+    cs = M._make_cos_sin_cache(4096, 64, "cpu")
+    for idx, (tokens, heads, groups, scale) in enumerate(((3, 64, 8, 1.0), (1, 32, 4, 1.0), (5, 16, 2, 1000.0), (6, 8, 8, 1.0))):
+        g = torch.Generator().manual_seed(200 + idx)
+        o = (scale * torch.randn(tokens, heads, 512, generator=g)).to(torch.bfloat16)
+        if idx == 3:  # exact powers of two, zero groups, tiny groups
+            of = o.float()
+            of[0, 0, :128] = 0.0
+            of[0, 1, :128] *= 1e-12
+            for k in range(2, 8):
+                of[0, k, :128] = of[0, k, :128].clamp(-1, 1)
+                of[0, k, 5] = 1.75 * 2.0 ** (k - 4)
+            o = of.to(torch.bfloat16)
+        pos = torch.randint(0, 4096, (tokens,), generator=g)
+        out = {}
+        for packed in (False, True):
+            f8, sc = M.native_fused_inv_rope_fp8_quant(o, pos, cs, groups, heads // groups, tma_aligned_scales=packed)
+            out[f"fp8_{int(packed)}"] = f8.view(torch.uint8).numpy()
+            out[f"scale_{int(packed)}"] = sc.numpy()
+        np.savez_compressed(HERE / f"inv_rope_t{tokens}_h{heads}_g{groups}.npz", o=u16(o), positions=pos.numpy(), n_groups=groups,
+                            heads_per_group=heads // groups, **out)
+        print("inv_rope", tokens, heads, groups, "ok")
+
+
 if __name__ == "__main__":
+    if len(sys.argv) < 2 or sys.argv[1] == "inv_rope":
+        inv_rope_cases()
     if len(sys.argv) < 2 or sys.argv[1] == "rmsnorm":
         rmsnorm_cases()
     if len(sys.argv) < 2 or sys.argv[1] == "prologue":
