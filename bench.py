@@ -211,6 +211,98 @@ def hbm_ceiling(native, nbytes: int, stream):
     return out
 
 
+def sibling_ops(steps, warmup):
+    """The operators either side of the prologue, 8192 tokens x 128 heads,
+    device-resident inputs larger than L2, CUDA-event time; GB/s = algorithmic bytes / time."""
+    import flaggems_vllm
+
+    dev, n, h = "cuda", 8192, 128
+    stream = torch.cuda.current_stream()
+    g = torch.Generator(device=dev).manual_seed(0)
+    out = {}
+    # epilogue: read 1 KiB, write 512 B + 4 fp32 scales per (token, head) row
+    o = torch.randn(n, h, 512, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+    pos = torch.randint(0, 65536, (n,), generator=g, device=dev, dtype=torch.int64)
+    from flaggems_vllm.testing.workloads import cos_sin_table
+
+    cs = cos_sin_table(65536, device=dev)
+    for packed, key, scale_bytes in ((True, "fused_inv_rope_fp8_quant[ue8m0 scales]", 4), (False, "fused_inv_rope_fp8_quant[fp32 scales]", 16)):
+        secs = time_steps(lambda: flaggems_vllm.fused_inv_rope_fp8_quant(o, pos, cs, 8, 16, tma_aligned_scales=packed), steps,
+                          warmup, stream, torch.cuda.synchronize)
+        nbytes = n * h * (1024 + 512 + scale_bytes) + n * 264
+        out[key] = {"rows": n * h, "us_per_launch": secs / steps * 1e6, "hbm_gbs": nbytes * steps / secs / 1e9,
+                    "note": "includes torch.empty of the two outputs per call"}
+    del o
+    # step before: weighted RMSNorm of [N,1536] and [N,512]; 64 Ki tokens so the working set exceeds L2
+    nt = 65536
+    qr = torch.randn(nt, 1536, generator=g, device=dev).to(torch.bfloat16)
+    kv = torch.randn(nt, 512, generator=g, device=dev).to(torch.bfloat16)
+    qw, kw = torch.ones(1536, device=dev, dtype=torch.bfloat16), torch.ones(512, device=dev, dtype=torch.bfloat16)
+    secs = time_steps(lambda: flaggems_vllm.fused_q_kv_rmsnorm(qr, kv, qw, kw, 1e-6), steps, warmup, stream, torch.cuda.synchronize)
+    out["fused_q_kv_rmsnorm"] = {"tokens": nt, "us_per_launch": secs / steps * 1e6,
+                                 "hbm_gbs": nt * 2048 * 2 * 2 * steps / secs / 1e9,
+                                 "note": "includes torch.empty_like of the two outputs per call"}
+    del qr, kv
+    # reader: 16 requests x 16384 tokens gathered through a block table; 584 B read, 1 KiB written per token
+    reqs, seq, bs = 16, 16384, 64
+    blocks = reqs * seq // bs
+    cache = torch.randint(0, 256, (blocks, bs * 584), generator=g, device=dev, dtype=torch.uint8)
+    table = torch.randperm(blocks, generator=g, device=dev).to(torch.int32).view(reqs, seq // bs).contiguous()
+    lens = torch.full((reqs,), seq, device=dev, dtype=torch.int32)
+    dst = torch.empty(reqs, seq, 512, device=dev, dtype=torch.bfloat16)
+    secs = time_steps(lambda: flaggems_vllm.dequantize_and_gather_k_cache(dst, cache, lens, None, table, bs), steps, warmup, stream,
+                      torch.cuda.synchronize)
+    out["dequantize_and_gather_k_cache"] = {"tokens": reqs * seq, "us_per_launch": secs / steps * 1e6,
+                                            "hbm_gbs": reqs * seq * (584 + 1024) * steps / secs / 1e9}
+    return out
+
+
+def measure_e2e(flaggems_vllm, w, args, dev, stream, sync_all, tokens_all_ranks):
+    """The same step through the public host-buffer front end: q/kv/slots/positions start in pinned host
+    memory, the rewritten q ends in pinned host memory (in place), copies inside the timed region."""
+    import torch.distributed as dist
+
+    distributed = dist.is_available() and dist.is_initialized()
+    try:
+        hq = torch.empty(w.q.shape, dtype=w.q.dtype, pin_memory=True)
+    except RuntimeError as e:  # not enough pinnable host memory on this box
+        return {"value": None, "unit": "tokens/s", "unavailable": f"pinned allocation failed: {str(e).splitlines()[0]}"}
+    hq.copy_(w.q)
+    hkv = w.kv.cpu().pin_memory()
+    hslots = w.slot_mapping.cpu().pin_memory()
+    hpos = w.position_ids.cpu().pin_memory()
+    pipe = flaggems_vllm.HostStagedPrologue(w.num_heads, chunk_tokens=2048, device=dev)
+    e2e_steps = max(2, min(args.steps, 5))
+
+    def e2e_step():
+        pipe(hq, hkv, w.k_cache, hslots, hpos, w.cos_sin_cache, w.eps, 64)
+
+    for _ in range(min(args.warmup, 2) or 1):
+        e2e_step()
+    sync_all()
+    # the staged call makes the caller's stream wait for its last copy, so two events on that stream
+    # bracket the host->device copies, the kernels and the device->host copies
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record(stream)
+    for _ in range(e2e_steps):
+        e2e_step()
+    t1.record(stream)
+    sync_all()
+    secs = t0.elapsed_time(t1) * 1e-3 / e2e_steps
+    h2d = hq.numel() * 2 + hkv.numel() * 2 + hslots.numel() * 8 + hpos.numel() * 8
+    d2h = hq.numel() * 2
+    es = torch.tensor([secs, float(h2d), float(d2h)], dtype=torch.float64, device=dev)
+    if distributed and dist.get_world_size() > 1:
+        em, esum = es.clone(), es.clone()
+        dist.all_reduce(em, op=dist.ReduceOp.MAX)
+        dist.all_reduce(esum, op=dist.ReduceOp.SUM)
+        secs, h2d, d2h = float(em[0]), float(esum[1]), float(esum[2])
+    return {"value": tokens_all_ranks / secs, "unit": "tokens/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
+            "ms_per_step": secs * 1e3, "chunk_tokens": 2048, "launches_per_step": pipe.launches,
+            "note": "q/kv/slots/positions from pinned host memory, rewritten q back to the same pinned buffer; "
+                    "K cache and cos/sin table device-resident"}
+
+
 def side_measurement(name, steps, warmup, op, native):
     """decode / prefill configurations, reported beside the headline (N=1, rank 0 only).
     The 256-token decode batch fits in L2, so it rotates over enough independent q/kv sets to
@@ -302,43 +394,7 @@ def main():
     # ---- end to end from pinned host buffers through the public API
     e2e = None
     if not args.no_e2e:
-        pipe = flaggems_vllm.HostStagedPrologue(w.num_heads, chunk_tokens=2048, device=dev)
-        hq = torch.empty(w.q.shape, dtype=w.q.dtype, pin_memory=True)
-        hq.copy_(w.q)
-        hq_out = torch.empty(w.q.shape, dtype=w.q.dtype, pin_memory=True)
-        hkv = w.kv.cpu().pin_memory()
-        hslots = w.slot_mapping.cpu().pin_memory()
-        hpos = w.position_ids.cpu().pin_memory()
-        e2e_steps = max(2, min(args.steps, 5))
-
-        def e2e_step():
-            pipe(hq, hkv, w.k_cache, hslots, hpos, w.cos_sin_cache, w.eps, 64, q_out_host=hq_out)
-
-        for _ in range(min(args.warmup, 2) or 1):
-            e2e_step()
-        sync_all()
-        # the staged call makes the caller's stream wait for its last copy, so two events on that
-        # stream bracket the host->device copies, the kernels and the device->host copies
-        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        t0.record(stream)
-        for _ in range(e2e_steps):
-            e2e_step()
-        t1.record(stream)
-        sync_all()
-        e2e_secs = t0.elapsed_time(t1) * 1e-3 / e2e_steps
-        h2d = hq.numel() * 2 + hkv.numel() * 2 + hslots.numel() * 8 + hpos.numel() * 8
-        d2h = hq_out.numel() * 2
-        es = torch.tensor([e2e_secs, float(h2d), float(d2h)], dtype=torch.float64, device=dev)
-        if distributed:
-            em = es.clone()
-            dist.all_reduce(em, op=dist.ReduceOp.MAX)
-            esum = es.clone()
-            dist.all_reduce(esum, op=dist.ReduceOp.SUM)
-            e2e_secs, h2d, d2h = float(em[0]), float(esum[1]), float(esum[2])
-        e2e = {"value": tokens / e2e_secs, "unit": "tokens/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
-               "ms_per_step": e2e_secs * 1e3, "chunk_tokens": 2048, "launches_per_step": pipe.launches,
-               "note": "q/kv/slots/positions from pinned host memory, rewritten q back to pinned host memory; K cache and cos/sin table device-resident"}
-        del hq, hq_out
+        e2e = measure_e2e(flaggems_vllm, w, args, dev, stream, sync_all, tokens)
 
     if rank != 0:
         if distributed:
@@ -380,6 +436,8 @@ def main():
         line["hbm_ceiling"] = ceiling
         line["other_configs"] = {n: side_measurement(n, max(args.steps, 50), max(args.warmup, 5), op, _native)
                                  for n in ("decode", "prefill")}
+        torch.cuda.empty_cache()
+        line["sibling_ops"] = sibling_ops(20, 5)
     print(json.dumps(line), flush=True)
     if distributed:
         dist.destroy_process_group()

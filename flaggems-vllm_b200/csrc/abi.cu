@@ -180,6 +180,26 @@ int dsv4_fused_inv_rope_fp8_quant(const void* o, int64_t o_stride_token, int64_t
                                                       static_cast<cudaStream_t>(cuda_stream)));
 }
 
+int dsv4_indexer_k_quant_and_cache(const void* k, int64_t k_row_stride, int32_t k_is_fp16, void* kv_cache,
+                                   int64_t cache_block_stride_bytes, const int64_t* slot_mapping, int64_t num_tokens,
+                                   int64_t cache_block_size, int64_t head_dim, int64_t quant_block_size,
+                                   int32_t scale_is_ue8m0, void* cuda_stream) {
+    if (num_tokens < 0 || head_dim <= 0 || quant_block_size <= 0 || head_dim % quant_block_size != 0 ||
+        head_dim >= (1LL << 24) || cache_block_size <= 0)
+        return DSV4_ERR_BAD_SIZE;
+    if (num_tokens == 0) return DSV4_OK;
+    if (!k || !kv_cache || !slot_mapping) return DSV4_ERR_NULL_POINTER;
+    if (cache_block_stride_bytes < cache_block_size * (head_dim + 4 * (head_dim / quant_block_size))) return DSV4_ERR_BAD_SIZE;
+    // the fp32 scale region of every block must be 4-byte aligned
+    if ((reinterpret_cast<uintptr_t>(k) & 1u) != 0 || (reinterpret_cast<uintptr_t>(kv_cache) & 3u) != 0 ||
+        cache_block_stride_bytes % 4 != 0 || (cache_block_size * head_dim) % 4 != 0)
+        return DSV4_ERR_MISALIGNED;
+    return static_cast<int>(launch_indexer_k_quant(k, k_row_stride, k_is_fp16 ? 1 : 0, kv_cache, cache_block_stride_bytes,
+                                                   slot_mapping, num_tokens, cache_block_size, static_cast<int>(head_dim),
+                                                   static_cast<int>(quant_block_size), scale_is_ue8m0 ? 1 : 0,
+                                                   static_cast<cudaStream_t>(cuda_stream)));
+}
+
 int dsv4_hbm_probe(int mode, void* buffer, int64_t rows, void* cuda_stream) {
     if (mode < 0 || mode > 2) return DSV4_ERR_BAD_VARIANT;
     if (rows < 0 || rows >= (1LL << 31)) return DSV4_ERR_BAD_SIZE;

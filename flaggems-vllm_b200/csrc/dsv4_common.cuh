@@ -112,7 +112,8 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     return r;
 }
 
-// Four floats -> four e4m3 bytes (f0 in the lowest byte), round to nearest even, saturating.
+// Four floats -> four e4m3 bytes (f0 in the lowest byte), round to nearest even; `satfinite` clamps to
+// +-448 (what the reference's explicit clamp before the cast does) and keeps NaN as NaN.
 __device__ __forceinline__ uint32_t pack_e4m3x4(float f0, float f1, float f2, float f3) {
     uint16_t lo, hi;
     asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(lo) : "f"(f1), "f"(f0));
@@ -262,7 +263,7 @@ __device__ __forceinline__ uint2 quant8(const uint4& v, uint32_t code) {
     float x[8];
     unpack8(v, x);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) x[i] = fminf(fmaxf(__fdiv_rn(x[i], scale), -448.0f), 448.0f);
+    for (int i = 0; i < 8; ++i) x[i] = __fdiv_rn(x[i], scale);
     return make_uint2(pack_e4m3x4(x[0], x[1], x[2], x[3]), pack_e4m3x4(x[4], x[5], x[6], x[7]));
 }
 
@@ -339,6 +340,9 @@ cudaError_t launch_inv_rope_fp8_quant(const void* o, int64_t o_stride_token, int
                                       const float* cos_sin, int64_t cos_sin_stride, void* fp8, void* scale,
                                       int64_t scale_stride_group, int64_t num_tokens, int64_t padded_tokens, int num_heads,
                                       int heads_per_group, float eps, int packed, cudaStream_t stream);
+cudaError_t launch_indexer_k_quant(const void* k, int64_t k_stride, int is_fp16, void* cache, int64_t block_stride,
+                                   const int64_t* slot_mapping, int64_t num_tokens, int64_t block_size, int head_dim,
+                                   int quant_block, int ue8m0, cudaStream_t stream);
 cudaError_t launch_hbm_probe(int mode, uint8_t* buf, int64_t rows, uint32_t* sink, cudaStream_t stream);
 void count_launch();
 cudaError_t read_device_error(int* value);

@@ -104,7 +104,59 @@ __global__ void __launch_bounds__(WARPS * 32) gather_dequant_requests_kernel(con
     const int64_t start = seq_len - gather_len;
     const int64_t token_data = g.nope_dim + 2 * g.rope_dim;
     const int64_t warps_per_req = static_cast<int64_t>(gridDim.x) * WARPS;
-    for (int64_t i = static_cast<int64_t>(blockIdx.x) * WARPS + (threadIdx.x >> 5); i < gather_len; i += warps_per_req) {
+    const int64_t first = static_cast<int64_t>(blockIdx.x) * WARPS + (threadIdx.x >> 5);
+    if (FAST) {
+        // two tokens per warp and iteration: both block-table lookups, then all cache reads, are in flight
+        // together before anything is converted
+        constexpr int U = 2;
+        for (int64_t i0 = first; i0 < gather_len; i0 += U * warps_per_req) {
+            const uint8_t* data[U];
+            const uint8_t* scales[U];
+            int64_t block[U];
+            bool live[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int64_t i = i0 + u * warps_per_req;
+                live[u] = i < gather_len;
+                const int64_t pos = start + (live[u] ? i : i0);
+                block[u] = load_index(g.block_table, req * g.max_blocks_per_seq + pos / g.block_size, g.index64);
+            }
+            uint2 codes[U], qa[U];
+            uint4 qb[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int64_t pos = start + (live[u] ? i0 + u * warps_per_req : i0);
+                const int64_t in_block = pos % g.block_size;
+                const uint8_t* base = g.k_cache + block[u] * g.block_stride;
+                data[u] = base + in_block * kTokenDataBytes;
+                scales[u] = base + g.block_size * kTokenDataBytes + in_block * kScaleBytes;
+                codes[u] = *reinterpret_cast<const uint2*>(scales[u]);
+                qa[u] = *reinterpret_cast<const uint2*>(data[u] + 8 * lane);
+                if (lane >= kFirstRopeLane) {
+                    qb[u] = *reinterpret_cast<const uint4*>(data[u] + kNopeDim + 16 * (lane - kFirstRopeLane));
+                } else {
+                    const uint2 t = *reinterpret_cast<const uint2*>(data[u] + 256 + 8 * lane);
+                    qb[u] = make_uint4(t.x, t.y, 0u, 0u);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                if (!live[u]) continue;
+                const int64_t i = i0 + u * warps_per_req;
+                uint8_t* row = g.out + (req * g.out_stride0 + (g.offset + i) * g.out_stride1) * 2;
+                const float scale_a = ue8m0_to_float((codes[u].x >> (8 * (lane >> 3))) & 0xffu);
+                *reinterpret_cast<uint4*>(row + 16 * lane) = dequant8(qa[u], scale_a);
+                uint4 b = qb[u];
+                if (lane < kFirstRopeLane) {
+                    const float scale_b = ue8m0_to_float((codes[u].y >> (8 * (lane >> 3))) & 0xffu);
+                    b = dequant8(make_uint2(qb[u].x, qb[u].y), scale_b);
+                }
+                *reinterpret_cast<uint4*>(row + 512 + 16 * lane) = b;
+            }
+        }
+        return;
+    }
+    for (int64_t i = first; i < gather_len; i += warps_per_req) {
         const int64_t pos = start + i;
         const int64_t block_in_seq = pos / g.block_size, in_block = pos - block_in_seq * g.block_size;
         const int64_t block = load_index(g.block_table, req * g.max_blocks_per_seq + block_in_seq, g.index64);
@@ -112,29 +164,15 @@ __global__ void __launch_bounds__(WARPS * 32) gather_dequant_requests_kernel(con
         const uint8_t* data = base + in_block * token_data;
         const uint8_t* scales = base + g.block_size * token_data + in_block * g.scale_slots;
         uint8_t* row = g.out + (req * g.out_stride0 + (g.offset + i) * g.out_stride1) * 2;
-        if (FAST) {
-            const uint2 codes = *reinterpret_cast<const uint2*>(scales);
-            const float scale_a = ue8m0_to_float((codes.x >> (8 * (lane >> 3))) & 0xffu);
-            *reinterpret_cast<uint4*>(row + 16 * lane) = dequant8(*reinterpret_cast<const uint2*>(data + 8 * lane), scale_a);
-            uint4 b;
-            if (lane >= kFirstRopeLane) {
-                b = *reinterpret_cast<const uint4*>(data + kNopeDim + 16 * (lane - kFirstRopeLane));
-            } else {
-                const float scale_b = ue8m0_to_float((codes.y >> (8 * (lane >> 3))) & 0xffu);
-                b = dequant8(*reinterpret_cast<const uint2*>(data + 256 + 8 * lane), scale_b);
-            }
-            *reinterpret_cast<uint4*>(row + 512 + 16 * lane) = b;
-        } else {
-            uint16_t* out16 = reinterpret_cast<uint16_t*>(row);
-            for (int j = lane; j < g.nope_dim; j += 32) {
-                const float scale = ue8m0_to_float(scales[j >> 6]);
-                const float v = unpack_e4m3x2(static_cast<uint16_t>(data[j])).x;
-                out16[j] = static_cast<uint16_t>(pack_bf16x2(__fmul_rn(v, scale), 0.0f) & 0xffffu);
-            }
-            for (int j = lane; j < g.rope_dim; j += 32)
-                out16[g.nope_dim + j] = static_cast<uint16_t>(data[g.nope_dim + 2 * j]) |
-                                        (static_cast<uint16_t>(data[g.nope_dim + 2 * j + 1]) << 8);
+        uint16_t* out16 = reinterpret_cast<uint16_t*>(row);
+        for (int j = lane; j < g.nope_dim; j += 32) {
+            const float scale = ue8m0_to_float(scales[j >> 6]);
+            const float v = unpack_e4m3x2(static_cast<uint16_t>(data[j])).x;
+            out16[j] = static_cast<uint16_t>(pack_bf16x2(__fmul_rn(v, scale), 0.0f) & 0xffffu);
         }
+        for (int j = lane; j < g.rope_dim; j += 32)
+            out16[g.nope_dim + j] = static_cast<uint16_t>(data[g.nope_dim + 2 * j]) |
+                                    (static_cast<uint16_t>(data[g.nope_dim + 2 * j + 1]) << 8);
     }
 }
 

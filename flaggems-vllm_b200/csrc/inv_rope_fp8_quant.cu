@@ -25,7 +25,8 @@ struct InvRopeParams {
     int64_t num_tokens, padded_tokens;
     int32_t num_heads, heads_per_group;
     float eps;
-    int32_t packed;            // 1: power-of-two scales, the 4 UE8M0 bytes of a head packed into one int32
+    uint32_t heads_mul, heads_shift;  // fast division of a row index by num_heads (rows < 2^31)
+    uint32_t hpg_mul, hpg_shift;      // fast division of a head index by heads_per_group
 };
 
 // Power-of-two scale >= s as (exponent byte, value): ceil(log2(max(s, 1e-10))) from the bit pattern.
@@ -37,29 +38,40 @@ __device__ __forceinline__ uint32_t pow2_ceil_code(float s) {
 __device__ __forceinline__ uint2 quant8_by(const float (&x)[8], float scale) {
     float q[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) q[i] = fminf(fmaxf(__fdiv_rn(x[i], scale), -448.0f), 448.0f);
+    for (int i = 0; i < 8; ++i) q[i] = __fdiv_rn(x[i], scale);  // the e4m3 conversion saturates at +-448
     return make_uint2(pack_e4m3x4(q[0], q[1], q[2], q[3]), pack_e4m3x4(q[4], q[5], q[6], q[7]));
 }
 
-template <int WARPS>
+// 8 values times the exact reciprocal of a power-of-two scale (same result as dividing by it).
+__device__ __forceinline__ uint2 quant8_pow2(const float (&x)[8], uint32_t code) {
+    const float inv = __uint_as_float((254u - code) << 23);
+    float q[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) q[i] = __fmul_rn(x[i], inv);
+    return make_uint2(pack_e4m3x4(q[0], q[1], q[2], q[3]), pack_e4m3x4(q[4], q[5], q[6], q[7]));
+}
+
+// PACKED: power-of-two scales, the 4 UE8M0 bytes of a head packed into one int32.
+template <int WARPS, bool PACKED>
 __global__ void __launch_bounds__(WARPS * 32) inv_rope_fp8_quant_kernel(const InvRopeParams p) {
     const int lane = threadIdx.x & 31;
-    const int64_t row = static_cast<int64_t>(blockIdx.x) * WARPS + (threadIdx.x >> 5);
-    if (row >= p.padded_tokens * p.num_heads) return;
-    const int64_t token = row / p.num_heads;
-    const int head = static_cast<int>(row - token * p.num_heads);
-    const int group = head / p.heads_per_group, head_in_group = head - group * p.heads_per_group;
+    const uint32_t row = blockIdx.x * WARPS + (threadIdx.x >> 5);
+    if (row >= static_cast<uint32_t>(p.padded_tokens) * static_cast<uint32_t>(p.num_heads)) return;
+    const uint32_t token = fast_div(row, p.heads_mul, p.heads_shift);
+    const int head = static_cast<int>(row - token * static_cast<uint32_t>(p.num_heads));
+    const int group = static_cast<int>(fast_div(static_cast<uint32_t>(head), p.hpg_mul, p.hpg_shift));
+    const int head_in_group = head - group * p.heads_per_group;
     uint8_t* scale_row = p.scale + (group * p.scale_stride_group + token) * 4;
     if (token >= p.num_tokens) {
         // rows of the token padding (scale columns are padded to a multiple of 4 tokens): zero scales
-        if (p.packed) {
+        if (PACKED) {
             if (lane == 0) *reinterpret_cast<uint32_t*>(scale_row + head_in_group * p.padded_tokens * 4) = 0u;
         } else if (lane < 4) {
             *reinterpret_cast<float*>(scale_row + (head_in_group * 4 + lane) * p.padded_tokens * 4) = 0.0f;
         }
         return;
     }
-    const uint8_t* in = p.o + (token * p.o_stride_token + head * p.o_stride_head) * 2;
+    const uint8_t* in = p.o + (static_cast<int64_t>(token) * p.o_stride_token + head * p.o_stride_head) * 2;
     float xa[8], xb[8];
     unpack8(ld_stream16(in + 16 * lane), xa);
     unpack8(ld_stream16(in + 512 + 16 * lane), xb);
@@ -86,16 +98,18 @@ __global__ void __launch_bounds__(WARPS * 32) inv_rope_fp8_quant_kernel(const In
         mb = fmaxf(mb, __shfl_xor_sync(0xffffffffu, mb, m));
     }
     float sa = __fmul_rn(fmaxf(ma, p.eps), 1.0f / 448.0f), sb = __fmul_rn(fmaxf(mb, p.eps), 1.0f / 448.0f);
-    uint32_t code_a = 0, code_b = 0;
-    if (p.packed) {
-        code_a = pow2_ceil_code(sa), code_b = pow2_ceil_code(sb);
-        sa = __uint_as_float(code_a << 23), sb = __uint_as_float(code_b << 23);
-    }
     uint8_t* out = p.fp8 + (static_cast<int64_t>(group) * p.num_tokens + token) * (static_cast<int64_t>(p.heads_per_group) * kRowBytes / 2) +
                    static_cast<int64_t>(head_in_group) * (kRowBytes / 2);
-    st_global8(out + 8 * lane, quant8_by(xa, sa));
-    st_global8(out + 256 + 8 * lane, quant8_by(xb, sb));
-    if (p.packed) {
+    uint32_t code_a = 0, code_b = 0;
+    if (PACKED) {
+        code_a = pow2_ceil_code(sa), code_b = pow2_ceil_code(sb);
+        st_global8(out + 8 * lane, quant8_pow2(xa, code_a));
+        st_global8(out + 256 + 8 * lane, quant8_pow2(xb, code_b));
+    } else {
+        st_global8(out + 8 * lane, quant8_by(xa, sa));
+        st_global8(out + 256 + 8 * lane, quant8_by(xb, sb));
+    }
+    if (PACKED) {
         // chunk k of the head in byte k: groups 0,1 from register A (lanes 0 / 16), 2,3 from B
         const uint32_t word = (__shfl_sync(0xffffffffu, code_a, 0) & 0xffu) | ((__shfl_sync(0xffffffffu, code_a, 16) & 0xffu) << 8) |
                               ((__shfl_sync(0xffffffffu, code_b, 0) & 0xffu) << 16) |
@@ -124,8 +138,12 @@ cudaError_t launch_inv_rope_fp8_quant(const void* o, int64_t o_stride_token, int
     p.positions = positions, p.cos_sin = cos_sin, p.cos_sin_stride = cos_sin_stride;
     p.fp8 = static_cast<uint8_t*>(fp8), p.scale = static_cast<uint8_t*>(scale), p.scale_stride_group = scale_stride_group;
     p.num_tokens = num_tokens, p.padded_tokens = padded_tokens, p.num_heads = num_heads, p.heads_per_group = heads_per_group;
-    p.eps = eps, p.packed = packed;
-    inv_rope_fp8_quant_kernel<WARPS><<<static_cast<unsigned>(grid), WARPS * 32, 0, stream>>>(p);
+    p.eps = eps;
+    if (rows >= (1LL << 31)) return cudaErrorInvalidConfiguration;
+    make_fast_divisor(static_cast<uint32_t>(num_heads), &p.heads_mul, &p.heads_shift);
+    make_fast_divisor(static_cast<uint32_t>(heads_per_group), &p.hpg_mul, &p.hpg_shift);
+    if (packed) inv_rope_fp8_quant_kernel<WARPS, true><<<static_cast<unsigned>(grid), WARPS * 32, 0, stream>>>(p);
+    else inv_rope_fp8_quant_kernel<WARPS, false><<<static_cast<unsigned>(grid), WARPS * 32, 0, stream>>>(p);
     count_launch();
     return cudaGetLastError();
 }

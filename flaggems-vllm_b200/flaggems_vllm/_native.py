@@ -19,6 +19,7 @@ EXPORTS = (
     "dsv4_dequantize_and_gather_k_cache",
     "dsv4_fused_q_kv_rmsnorm",
     "dsv4_fused_inv_rope_fp8_quant",
+    "dsv4_indexer_k_quant_and_cache",
     "dsv4_hbm_probe",
     "dsv4_device_error",
     "dsv4_set_variant",
@@ -69,6 +70,8 @@ def lib() -> ctypes.CDLL:
     L.dsv4_fused_q_kv_rmsnorm.restype = i32
     L.dsv4_fused_inv_rope_fp8_quant.argtypes = [vp, i64, i64, vp, vp, i64, vp, vp, i64, i64, i64, i64, i64, f32, i32, vp]
     L.dsv4_fused_inv_rope_fp8_quant.restype = i32
+    L.dsv4_indexer_k_quant_and_cache.argtypes = [vp, i64, i32, vp, i64, vp, i64, i64, i64, i64, i32, vp]
+    L.dsv4_indexer_k_quant_and_cache.restype = i32
     L.dsv4_hbm_probe.argtypes = [i32, vp, i64, vp]
     L.dsv4_hbm_probe.restype = i32
     L.dsv4_device_error.argtypes = [vp]

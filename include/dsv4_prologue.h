@@ -153,6 +153,20 @@ int dsv4_fused_inv_rope_fp8_quant(const void* o, int64_t o_stride_token, int64_t
                                   int64_t heads_per_group, float eps, int32_t packed_ue8m0_scales, void* cuda_stream);
 
 /*
+ * The sparse-indexer sibling of the prologue's KV insert.  Replaces the reference operator
+ *   indexer_k_quant_and_cache(k, kv_cache, slot_mapping, quant_block_size, scale_fmt)
+ * (src/flaggems_vllm/ops/indexer_k_quant_and_cache.py:103-132, kernel :44-100): token t of k
+ * [num_tokens, head_dim] (bf16, or fp16 when k_is_fp16) goes to slot_mapping[t] (skipped when negative):
+ * per group of quant_block_size values scale = max(amax, 1e-4)/448 (rounded up to a power of two when
+ * scale_is_ue8m0), bytes = e4m3(x / scale).  Cache block b at b*cache_block_stride_bytes holds
+ * cache_block_size*head_dim value bytes, then cache_block_size*(head_dim/quant_block_size) fp32 scales.
+ */
+int dsv4_indexer_k_quant_and_cache(const void* k, int64_t k_row_stride, int32_t k_is_fp16, void* kv_cache,
+                                   int64_t cache_block_stride_bytes, const int64_t* slot_mapping, int64_t num_tokens,
+                                   int64_t cache_block_size, int64_t head_dim, int64_t quant_block_size,
+                                   int32_t scale_is_ue8m0, void* cuda_stream);
+
+/*
  * Bandwidth probe with the prologue's q access pattern and no arithmetic, over `rows` rows of
  * 1 KiB starting at `buffer` (16-byte aligned): mode 0 reads every row and writes it back in
  * place, mode 1 only reads, mode 2 only writes (the buffer's contents are overwritten).  Used by

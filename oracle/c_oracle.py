@@ -46,6 +46,8 @@ def lib() -> ctypes.CDLL:
         L.dsv4_oracle_weighted_rmsnorm.restype = i32
         L.dsv4_oracle_inv_rope_fp8_quant.argtypes = [vp, i64, i64, vp, vp, i64, vp, vp, i64, i64, i64, f32, i32]
         L.dsv4_oracle_inv_rope_fp8_quant.restype = i32
+        L.dsv4_oracle_indexer_k_quant.argtypes = [vp, i64, i32, vp, i64, vp, i64, i64, i64, i64, i32]
+        L.dsv4_oracle_indexer_k_quant.restype = i32
         L.dsv4_oracle_version.restype = ctypes.c_char_p
         _lib = L
     return _lib
@@ -126,6 +128,17 @@ def inv_rope_fp8_quant(o, positions, cos_sin_cache, n_groups, heads_per_group, e
     if rc != 0:
         raise ValueError("dsv4_oracle_inv_rope_fp8_quant rejected its arguments")
     return fp8, scales
+
+
+def indexer_k_quant_and_cache(k, kv_cache, slot_mapping, quant_block_size, scale_fmt) -> None:
+    """Same arguments as the reference operator, on CPU tensors; kv_cache [blocks, block_size, row] uint8 in place."""
+    assert k.device.type == "cpu" and k.dim() == 2 and k.stride(1) == 1 and k.dtype in (torch.bfloat16, torch.float16)
+    _cpu(kv_cache, torch.uint8), _cpu(slot_mapping, torch.int64)
+    rc = lib().dsv4_oracle_indexer_k_quant(k.data_ptr(), k.stride(0), 1 if k.dtype == torch.float16 else 0, kv_cache.data_ptr(),
+                                           kv_cache.stride(0), slot_mapping.data_ptr(), slot_mapping.shape[0], kv_cache.shape[1],
+                                           k.shape[1], int(quant_block_size), 1 if scale_fmt == "ue8m0" else 0)
+    if rc != 0:
+        raise ValueError("dsv4_oracle_indexer_k_quant rejected its arguments")
 
 
 def e4m3_from_f32(x: torch.Tensor) -> torch.Tensor:

@@ -405,4 +405,53 @@ int dsv4_oracle_inv_rope_fp8_quant(const uint16_t* o, int64_t stride_token, int6
     return 0;
 }
 
+static inline float fp16_bits_to_f32(uint16_t h) {
+    uint32_t sign = (uint32_t)(h & 0x8000u) << 16, e = (h >> 10) & 0x1fu, m = h & 0x3ffu;
+    float v;
+    if (e == 0) v = ldexpf((float)m, -24);
+    else if (e == 31) v = m ? NAN : INFINITY;
+    else v = ldexpf((float)(m | 0x400u), (int)e - 25);
+    uint32_t u;
+    memcpy(&u, &v, 4);
+    u |= sign;
+    memcpy(&v, &u, 4);
+    return v;
+}
+
+/*
+ * Sparse-indexer key quantisation into its paged cache, the torch statement
+ * tests/test_indexer_k_quant_and_cache.py:99-143 of src/flaggems_vllm/ops/indexer_k_quant_and_cache.py:44-100.
+ * k [num_tokens, head_dim] bf16 (fp16 when is_fp16), row stride in elements; cache block b at b*block_stride bytes:
+ * block_size*head_dim e4m3 bytes then block_size*(head_dim/quant_block) fp32 scales.
+ */
+int dsv4_oracle_indexer_k_quant(const uint16_t* k, int64_t k_stride, int is_fp16, uint8_t* cache, int64_t block_stride,
+                                const int64_t* slot_mapping, int64_t num_tokens, int64_t block_size, int64_t head_dim,
+                                int64_t quant_block, int ue8m0) {
+    if (num_tokens < 0 || quant_block <= 0 || head_dim % quant_block != 0) return -1;
+    const int64_t nqb = head_dim / quant_block;
+    for (int64_t t = 0; t < num_tokens; ++t) {
+        int64_t slot = slot_mapping[t];
+        if (slot < 0) continue;
+        int64_t block = slot / block_size, in_block = slot % block_size;
+        uint8_t* base = cache + block * block_stride;
+        for (int64_t g = 0; g < nqb; ++g) {
+            float amax = 0.0f;
+            for (int64_t i = 0; i < quant_block; ++i) {
+                uint16_t h = k[t * k_stride + g * quant_block + i];
+                float a = fabsf(is_fp16 ? fp16_bits_to_f32(h) : bf16_bits_to_f32(h));
+                if (a > amax) amax = a;
+            }
+            float scale = (amax > 1e-4f ? amax : 1e-4f) / 448.0f;
+            if (ue8m0) scale = exp2f(ceilf(log2f(scale)));
+            for (int64_t i = 0; i < quant_block; ++i) {
+                uint16_t h = k[t * k_stride + g * quant_block + i];
+                float x = is_fp16 ? fp16_bits_to_f32(h) : bf16_bits_to_f32(h);
+                base[in_block * head_dim + g * quant_block + i] = f32_to_e4m3_bits(x / scale);
+            }
+            memcpy(base + block_size * head_dim + (in_block * nqb + g) * 4, &scale, 4);
+        }
+    }
+    return 0;
+}
+
 const char* dsv4_oracle_version(void) { return "dsv4-oracle 1"; }

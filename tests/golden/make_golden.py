@@ -219,7 +219,33 @@ def inv_rope_cases() -> None:
         print("inv_rope", tokens, heads, groups, "ok")
 
 
+def indexer_cases() -> None:
+    """Seeded inputs through the upstream test's torch statement `torch_indexer` and its cache builder
+    (tests/test_indexer_k_quant_and_cache.py:99-171), at the test's parameter sets (:174-181) plus fp32-scale ones."""
+    M = ref_loader.load_upstream_helper_test("test_indexer_k_quant_and_cache.py", "flaggems_vllm.ops", ("indexer_k_quant_and_cache",))
+    cases = ((torch.bfloat16, 19, 4, 16, 128, 128, "ue8m0"), (torch.float16, 23, 5, 16, 512, 128, "ue8m0"),
+             (torch.bfloat16, 17, 4, 64, 512, 128, "ue8m0"), (torch.bfloat16, 21, 3, 16, 128, 128, "fp32"),
+             (torch.float16, 9, 2, 8, 256, 64, "fp32"))
+    for idx, (dtype, tokens, blocks, bs, hd, qbs, fmt) in enumerate(cases):
+        torch.manual_seed(300 + idx)
+        k = torch.randn(tokens, hd, dtype=dtype)
+        if idx == 3:
+            k[0] = 0
+            k[1] *= 1e-6
+            k[2, 5] = 1.75 * 4
+        slots = M._make_slot_mapping(tokens, blocks, bs, "cpu")
+        cache = M._make_cache(blocks, bs, hd, qbs, "cpu")
+        out = cache.clone()
+        M.torch_indexer(k, out, slots, qbs, fmt)
+        name = f"indexer_{'f16' if dtype == torch.float16 else 'bf16'}_t{tokens}_b{blocks}x{bs}_d{hd}_q{qbs}_{fmt}"
+        np.savez_compressed(HERE / f"{name}.npz", k=u16(k), is_fp16=int(dtype == torch.float16), slot_mapping=slots.numpy(),
+                            cache=cache.numpy(), cache_out=out.numpy(), quant_block_size=qbs, scale_fmt=fmt)
+        print(name, "ok")
+
+
 if __name__ == "__main__":
+    if len(sys.argv) < 2 or sys.argv[1] == "indexer":
+        indexer_cases()
     if len(sys.argv) < 2 or sys.argv[1] == "inv_rope":
         inv_rope_cases()
     if len(sys.argv) < 2 or sys.argv[1] == "rmsnorm":
