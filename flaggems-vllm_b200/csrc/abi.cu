@@ -200,6 +200,34 @@ int dsv4_indexer_k_quant_and_cache(const void* k, int64_t k_row_stride, int32_t 
                                                    static_cast<cudaStream_t>(cuda_stream)));
 }
 
+int dsv4_fused_indexer_q_rope_quant(const int64_t* positions, const void* index_q, int64_t q_stride0, int64_t q_stride1,
+                                    const void* cos_sin_cache, int64_t cos_sin_stride, int32_t cos_sin_is_bf16, int64_t rot_dim,
+                                    void* q_out, int64_t out_stride0, int64_t out_stride1, void* q_scales_out,
+                                    int64_t scale_stride0, int64_t scale_stride1, const void* weights, int64_t weights_stride,
+                                    int32_t weights_dtype, float* weights_out, int64_t weights_out_stride, float softmax_scale,
+                                    float head_scale, int64_t num_tokens, int64_t num_heads, int64_t head_dim, int32_t use_fp4,
+                                    void* cuda_stream) {
+    if (num_tokens < 0 || num_heads <= 0 || num_heads >= (1LL << 31)) return DSV4_ERR_BAD_SIZE;
+    if (head_dim != 64 && head_dim != 128 && head_dim != 256) return DSV4_ERR_BAD_SIZE;
+    const int64_t lane_elems = head_dim / 32;
+    if (rot_dim < 0 || rot_dim > head_dim || rot_dim % 2 != 0 || (head_dim - rot_dim) % lane_elems != 0) return DSV4_ERR_BAD_SIZE;
+    if (weights_dtype < 0 || weights_dtype > 2) return DSV4_ERR_BAD_SIZE;
+    if (num_tokens == 0) return DSV4_OK;
+    if (!positions || !index_q || !cos_sin_cache || !q_out || !weights || !weights_out || (use_fp4 && !q_scales_out))
+        return DSV4_ERR_NULL_POINTER;
+    const auto addr = [](const void* p) { return reinterpret_cast<uintptr_t>(p); };
+    const int64_t in_bytes = lane_elems * 2, out_bytes = use_fp4 ? lane_elems / 2 : lane_elems;
+    if (addr(index_q) % in_bytes || (q_stride0 * 2) % in_bytes || (q_stride1 * 2) % in_bytes || addr(q_out) % out_bytes ||
+        out_stride0 % out_bytes || out_stride1 % out_bytes || addr(cos_sin_cache) % (cos_sin_is_bf16 ? 2 : 4) ||
+        addr(weights_out) % 4)
+        return DSV4_ERR_MISALIGNED;
+    return static_cast<int>(launch_indexer_q_rope_quant(
+        positions, index_q, q_stride0, q_stride1, cos_sin_cache, cos_sin_stride, cos_sin_is_bf16 ? 1 : 0, static_cast<int>(rot_dim),
+        q_out, out_stride0, out_stride1, q_scales_out, scale_stride0, scale_stride1, weights, weights_stride, weights_dtype,
+        weights_out, weights_out_stride, softmax_scale, head_scale, num_tokens, static_cast<int>(num_heads),
+        static_cast<int>(head_dim), use_fp4 ? 1 : 0, static_cast<cudaStream_t>(cuda_stream)));
+}
+
 int dsv4_hbm_probe(int mode, void* buffer, int64_t rows, void* cuda_stream) {
     if (mode < 0 || mode > 2) return DSV4_ERR_BAD_VARIANT;
     if (rows < 0 || rows >= (1LL << 31)) return DSV4_ERR_BAD_SIZE;

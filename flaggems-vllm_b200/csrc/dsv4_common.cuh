@@ -343,6 +343,12 @@ cudaError_t launch_inv_rope_fp8_quant(const void* o, int64_t o_stride_token, int
 cudaError_t launch_indexer_k_quant(const void* k, int64_t k_stride, int is_fp16, void* cache, int64_t block_stride,
                                    const int64_t* slot_mapping, int64_t num_tokens, int64_t block_size, int head_dim,
                                    int quant_block, int ue8m0, cudaStream_t stream);
+cudaError_t launch_indexer_q_rope_quant(const int64_t* positions, const void* q, int64_t q_stride0, int64_t q_stride1,
+                                        const void* cos_sin, int64_t cos_sin_stride, int cos_sin_bf16, int rot_dim, void* out,
+                                        int64_t out_stride0, int64_t out_stride1, void* scales, int64_t scale_stride0,
+                                        int64_t scale_stride1, const void* weights, int64_t weights_stride, int weights_dtype,
+                                        float* weights_out, int64_t weights_out_stride, float softmax_scale, float head_scale,
+                                        int64_t num_tokens, int num_heads, int head_dim, int fp4, cudaStream_t stream);
 cudaError_t launch_hbm_probe(int mode, uint8_t* buf, int64_t rows, uint32_t* sink, cudaStream_t stream);
 void count_launch();
 cudaError_t read_device_error(int* value);

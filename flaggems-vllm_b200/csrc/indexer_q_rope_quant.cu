@@ -1,0 +1,181 @@
+// fused_indexer_q_rope_quant: the sparse-indexer prologue that runs beside the attention prologue -
+// GPT-J RoPE on the last rot_dim values of every index-q head (rounded to bf16), then either
+//   FP8:   one power-of-two scale per (token, head), e4m3 values, scale folded into the head weight, or
+//   MXFP4: one UE8M0 scale per 32 values, e2m1 values packed two per byte (cvt.rn.satfinite.e2m1x2.f32,
+//          an sm_100 instruction), weights scaled by softmax_scale*head_scale only.
+// Reference: src/flaggems_vllm/ops/fused_indexer_q_rope_quant.py:69-410 and its torch statement
+// tests/test_fused_indexer_q_rope_quant.py:48-113.
+// One warp per (token, head) row; lane l keeps E = head_dim/32 consecutive values (E/2 rotary pairs).
+#include "dsv4_common.cuh"
+
+namespace dsv4 {
+namespace {
+
+struct IndexerQParams {
+    const int64_t* positions;
+    const uint8_t* q;  // bf16 [T, H, D], element strides
+    int64_t q_stride0, q_stride1;
+    const uint8_t* cos_sin;  // [max_pos, rot_dim] fp32 or bf16, row stride in elements
+    int64_t cos_sin_stride;
+    int32_t cos_sin_bf16, rot_dim;
+    uint8_t* out;  // fp8: [T, H, D] bytes; fp4: [T, H, D/2] bytes (strides in bytes)
+    int64_t out_stride0, out_stride1;
+    uint8_t* scales;  // fp4 only: [T, H, D/32] bytes
+    int64_t scale_stride0, scale_stride1;
+    const uint8_t* weights;  // [T, H], row stride in elements; dtype code 0 bf16, 1 fp16, 2 fp32
+    int64_t weights_stride;
+    int32_t weights_dtype;
+    float* weights_out;  // fp32 [T, H], row stride in elements
+    int64_t weights_out_stride;
+    float softmax_scale, head_scale;
+    int64_t num_tokens;
+    int32_t num_heads;
+    uint32_t heads_mul, heads_shift;
+};
+
+__device__ __forceinline__ float load_weight(const uint8_t* base, int64_t idx, int dtype) {
+    if (dtype == 2) return reinterpret_cast<const float*>(base)[idx];
+    const uint16_t h = reinterpret_cast<const uint16_t*>(base)[idx];
+    if (dtype == 0) return bf16_lo(h);
+    float f;
+    asm("{.reg .f16 t; mov.b16 t, %1; cvt.f32.f16 %0, t;}" : "=f"(f) : "h"(h));
+    return f;
+}
+
+// Two floats -> one byte of two e2m1 codes (lo in bits 0-3), round to nearest even, saturating at +-6.
+__device__ __forceinline__ uint32_t pack_e2m1x2(float lo, float hi) {
+    uint32_t r;
+    asm("{.reg .b8 t; cvt.rn.satfinite.e2m1x2.f32 t, %1, %2; cvt.u32.u8 %0, t;}" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+
+template <int E>
+__device__ __forceinline__ void load_row(const uint8_t* p, float (&x)[E]) {
+    if (E == 2) {
+        const uint32_t v = *reinterpret_cast<const uint32_t*>(p);
+        x[0] = bf16_lo(v), x[1] = bf16_hi(v);
+    } else if (E == 4) {
+        const uint2 v = *reinterpret_cast<const uint2*>(p);
+        x[0] = bf16_lo(v.x), x[1] = bf16_hi(v.x), x[2] = bf16_lo(v.y), x[3] = bf16_hi(v.y);
+    } else {
+        const uint4 v = *reinterpret_cast<const uint4*>(p);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) x[2 * i] = bf16_lo(w[i]), x[2 * i + 1] = bf16_hi(w[i]);
+    }
+}
+
+template <int WARPS, int E, bool FP4>
+__global__ void __launch_bounds__(WARPS * 32) indexer_q_rope_quant_kernel(const IndexerQParams p) {
+    constexpr int D = 32 * E;
+    const int lane = threadIdx.x & 31;
+    const uint32_t row = blockIdx.x * WARPS + (threadIdx.x >> 5);
+    if (row >= static_cast<uint32_t>(p.num_tokens) * static_cast<uint32_t>(p.num_heads)) return;
+    const uint32_t t = fast_div(row, p.heads_mul, p.heads_shift);
+    const int h = static_cast<int>(row - t * static_cast<uint32_t>(p.num_heads));
+    float x[E];
+    load_row<E>(p.q + (static_cast<int64_t>(t) * p.q_stride0 + h * p.q_stride1 + lane * E) * 2, x);
+    const int first_rot = lane * E - (D - p.rot_dim);  // index of this lane's first value inside the rotary tail
+    if (first_rot >= 0) {
+        const int64_t pos = p.positions[t];
+        const int half = p.rot_dim >> 1;
+#pragma unroll
+        for (int j = 0; j < E / 2; ++j) {
+            const int pair = (first_rot >> 1) + j;
+            float c, s;
+            if (p.cos_sin_bf16) {
+                const uint16_t* cs = reinterpret_cast<const uint16_t*>(p.cos_sin) + pos * p.cos_sin_stride;
+                c = bf16_lo(cs[pair]), s = bf16_lo(cs[half + pair]);
+            } else {
+                const float* cs = reinterpret_cast<const float*>(p.cos_sin) + pos * p.cos_sin_stride;
+                c = cs[pair], s = cs[half + pair];
+            }
+            const float e = x[2 * j], o = x[2 * j + 1];
+            // separately rounded products, then the bf16 round trip the reference makes before quantising
+            const uint32_t packed = pack_bf16x2(__fsub_rn(__fmul_rn(e, c), __fmul_rn(o, s)),
+                                                __fadd_rn(__fmul_rn(o, c), __fmul_rn(e, s)));
+            x[2 * j] = bf16_lo(packed), x[2 * j + 1] = bf16_hi(packed);
+        }
+    }
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < E; ++i) amax = fmaxf(amax, fabsf(x[i]));
+    uint8_t* out = p.out + static_cast<int64_t>(t) * p.out_stride0 + h * p.out_stride1;
+    float weight_factor = 1.0f;
+    if (FP4) {
+        constexpr int kGroupLanes = 32 / E;  // lanes per block of 32 values
+#pragma unroll
+        for (int m = 1; m < kGroupLanes; m <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
+        // block scale 2^ceil(log2(max(amax, 6*2^-126)/6)), exponent clamped to [-127, 127]
+        const uint32_t u = __float_as_uint(__fdiv_rn(fmaxf(amax, 6.0f * 1.17549435e-38f), 6.0f));
+        uint32_t code = ((u >> 23) & 0xffu) + ((u & 0x7fffffu) ? 1u : 0u);
+        code = code > 254u ? 254u : code;
+        const float inv = __uint_as_float((254u - code) << 23);  // code >= 1 because of the amax floor
+        uint32_t bytes = 0;
+#pragma unroll
+        for (int j = 0; j < E / 2; ++j) bytes |= pack_e2m1x2(__fmul_rn(x[2 * j], inv), __fmul_rn(x[2 * j + 1], inv)) << (8 * j);
+        if (E == 2) out[lane] = static_cast<uint8_t>(bytes);
+        else if (E == 4) *reinterpret_cast<uint16_t*>(out + 2 * lane) = static_cast<uint16_t>(bytes);
+        else *reinterpret_cast<uint32_t*>(out + 4 * lane) = bytes;
+        if ((lane & (kGroupLanes - 1)) == 0)
+            p.scales[static_cast<int64_t>(t) * p.scale_stride0 + h * p.scale_stride1 + lane / kGroupLanes] = static_cast<uint8_t>(code);
+    } else {
+#pragma unroll
+        for (int m = 16; m > 0; m >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
+        const uint32_t code = ue8m0_code(amax);  // 2^ceil(log2(max(amax, 1e-4)/448))
+        const float inv = __uint_as_float((254u - code) << 23);
+        weight_factor = __uint_as_float(code << 23);
+        float y[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int i = 0; i < E; ++i) y[i] = __fmul_rn(x[i], inv);
+        if (E == 2) *reinterpret_cast<uint16_t*>(out + 2 * lane) = static_cast<uint16_t>(pack_e4m3x4(y[0], y[1], 0.f, 0.f));
+        else if (E == 4) *reinterpret_cast<uint32_t*>(out + 4 * lane) = pack_e4m3x4(y[0], y[1], y[2], y[3]);
+        else st_global8(out + 8 * lane, make_uint2(pack_e4m3x4(y[0], y[1], y[2], y[3]), pack_e4m3x4(y[4], y[5], y[6], y[7])));
+    }
+    if (lane == 0) {
+        float w = load_weight(p.weights, static_cast<int64_t>(t) * p.weights_stride + h, p.weights_dtype);
+        if (!FP4) w = __fmul_rn(w, weight_factor);
+        w = __fmul_rn(__fmul_rn(w, p.softmax_scale), p.head_scale);
+        p.weights_out[static_cast<int64_t>(t) * p.weights_out_stride + h] = w;
+    }
+}
+
+template <int E>
+cudaError_t launch_e(const IndexerQParams& p, bool fp4, unsigned grid, cudaStream_t stream) {
+    constexpr int WARPS = 8;
+    if (fp4) indexer_q_rope_quant_kernel<WARPS, E, true><<<grid, WARPS * 32, 0, stream>>>(p);
+    else indexer_q_rope_quant_kernel<WARPS, E, false><<<grid, WARPS * 32, 0, stream>>>(p);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t launch_indexer_q_rope_quant(const int64_t* positions, const void* q, int64_t q_stride0, int64_t q_stride1,
+                                        const void* cos_sin, int64_t cos_sin_stride, int cos_sin_bf16, int rot_dim, void* out,
+                                        int64_t out_stride0, int64_t out_stride1, void* scales, int64_t scale_stride0,
+                                        int64_t scale_stride1, const void* weights, int64_t weights_stride, int weights_dtype,
+                                        float* weights_out, int64_t weights_out_stride, float softmax_scale, float head_scale,
+                                        int64_t num_tokens, int num_heads, int head_dim, int fp4, cudaStream_t stream) {
+    const int64_t rows = num_tokens * num_heads;
+    if (rows == 0) return cudaSuccess;
+    if (rows >= (1LL << 31)) return cudaErrorInvalidConfiguration;
+    IndexerQParams p{};
+    p.positions = positions, p.q = static_cast<const uint8_t*>(q), p.q_stride0 = q_stride0, p.q_stride1 = q_stride1;
+    p.cos_sin = static_cast<const uint8_t*>(cos_sin), p.cos_sin_stride = cos_sin_stride, p.cos_sin_bf16 = cos_sin_bf16;
+    p.rot_dim = rot_dim, p.out = static_cast<uint8_t*>(out), p.out_stride0 = out_stride0, p.out_stride1 = out_stride1;
+    p.scales = static_cast<uint8_t*>(scales), p.scale_stride0 = scale_stride0, p.scale_stride1 = scale_stride1;
+    p.weights = static_cast<const uint8_t*>(weights), p.weights_stride = weights_stride, p.weights_dtype = weights_dtype;
+    p.weights_out = weights_out, p.weights_out_stride = weights_out_stride;
+    p.softmax_scale = softmax_scale, p.head_scale = head_scale, p.num_tokens = num_tokens, p.num_heads = num_heads;
+    make_fast_divisor(static_cast<uint32_t>(num_heads), &p.heads_mul, &p.heads_shift);
+    const unsigned grid = static_cast<unsigned>((rows + 7) / 8);
+    cudaError_t err;
+    if (head_dim == 64) err = launch_e<2>(p, fp4 != 0, grid, stream);
+    else if (head_dim == 128) err = launch_e<4>(p, fp4 != 0, grid, stream);
+    else if (head_dim == 256) err = launch_e<8>(p, fp4 != 0, grid, stream);
+    else return cudaErrorInvalidValue;
+    count_launch();
+    return err;
+}
+
+}  // namespace dsv4

@@ -5,12 +5,14 @@ from .fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert import (
     fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert,
     fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert_checked,
 )
+from .fused_indexer_q_rope_quant import fused_indexer_q_rope_quant
 from .fused_inv_rope_fp8_quant import fused_inv_rope_fp8_quant
 from .gather_dequant_k_cache import gather_dequant_k_cache_slots
 from .host_staged import HostStagedPrologue
 from .indexer_k_quant_and_cache import indexer_k_quant_and_cache
 
 __all__ = [
+    "fused_indexer_q_rope_quant",
     "indexer_k_quant_and_cache",
     "fused_inv_rope_fp8_quant",
     "fused_q_kv_rmsnorm",

@@ -167,6 +167,28 @@ int dsv4_indexer_k_quant_and_cache(const void* k, int64_t k_row_stride, int32_t 
                                    int32_t scale_is_ue8m0, void* cuda_stream);
 
 /*
+ * The sparse-indexer prologue.  Replaces the reference operator
+ *   fused_indexer_q_rope_quant(positions, index_q, index_q_cos_sin_cache, index_weights,
+ *                              index_weights_softmax_scale, index_weights_head_scale, use_fp4)
+ * (src/flaggems_vllm/ops/fused_indexer_q_rope_quant.py:283-410, kernels :69-280): GPT-J RoPE on the last
+ * rot_dim values of each head of index_q (bf16 [T, H, head_dim], element strides), result rounded to bf16, then
+ *   use_fp4 == 0: q_out = e4m3(x / s) bytes [T, H, head_dim] with s = 2^ceil(log2(max(amax_head, 1e-4)/448));
+ *                 weights_out = weights * s * softmax_scale * head_scale
+ *   use_fp4 != 0: per 32 values s = 2^ceil(log2(max(amax, 6*2^-126)/6)); q_out = e2m1(x / s) packed two per
+ *                 byte (even index in the low nibble) [T, H, head_dim/2]; q_scales_out = exponent bytes
+ *                 [T, H, head_dim/32]; weights_out = weights * softmax_scale * head_scale
+ * Output strides in bytes.  cos_sin_cache rows = rot_dim/2 cosines then rot_dim/2 sines, fp32 or bf16.
+ * weights [T, H] of dtype code 0 bf16 / 1 fp16 / 2 fp32; weights_out fp32.  head_dim 64, 128 or 256.
+ */
+int dsv4_fused_indexer_q_rope_quant(const int64_t* positions, const void* index_q, int64_t q_stride0, int64_t q_stride1,
+                                    const void* cos_sin_cache, int64_t cos_sin_stride, int32_t cos_sin_is_bf16, int64_t rot_dim,
+                                    void* q_out, int64_t out_stride0, int64_t out_stride1, void* q_scales_out,
+                                    int64_t scale_stride0, int64_t scale_stride1, const void* weights, int64_t weights_stride,
+                                    int32_t weights_dtype, float* weights_out, int64_t weights_out_stride, float softmax_scale,
+                                    float head_scale, int64_t num_tokens, int64_t num_heads, int64_t head_dim, int32_t use_fp4,
+                                    void* cuda_stream);
+
+/*
  * Bandwidth probe with the prologue's q access pattern and no arithmetic, over `rows` rows of
  * 1 KiB starting at `buffer` (16-byte aligned): mode 0 reads every row and writes it back in
  * place, mode 1 only reads, mode 2 only writes (the buffer's contents are overwritten).  Used by

@@ -48,6 +48,8 @@ def lib() -> ctypes.CDLL:
         L.dsv4_oracle_inv_rope_fp8_quant.restype = i32
         L.dsv4_oracle_indexer_k_quant.argtypes = [vp, i64, i32, vp, i64, vp, i64, i64, i64, i64, i32]
         L.dsv4_oracle_indexer_k_quant.restype = i32
+        L.dsv4_oracle_indexer_q_rope_quant.argtypes = [vp, vp, vp, i64, vp, f32, f32, i64, i64, i64, i32, vp, vp, vp]
+        L.dsv4_oracle_indexer_q_rope_quant.restype = i32
         L.dsv4_oracle_version.restype = ctypes.c_char_p
         _lib = L
     return _lib
@@ -139,6 +141,24 @@ def indexer_k_quant_and_cache(k, kv_cache, slot_mapping, quant_block_size, scale
                                            k.shape[1], int(quant_block_size), 1 if scale_fmt == "ue8m0" else 0)
     if rc != 0:
         raise ValueError("dsv4_oracle_indexer_k_quant rejected its arguments")
+
+
+def indexer_q_rope_quant(positions, index_q, cos_sin_cache, weights, softmax_scale, head_scale, use_fp4=False):
+    """(q bytes uint8, scales uint8 or None, weights_out fp32) on CPU tensors; cos_sin_cache and weights of any float dtype."""
+    _cpu(positions, torch.int64)
+    q = _cpu(index_q.contiguous(), torch.bfloat16)
+    cs = cos_sin_cache.float().contiguous()
+    w = weights.float().contiguous()
+    t, h, d = q.shape
+    out = torch.empty(t, h, d // 2 if use_fp4 else d, dtype=torch.uint8)
+    scales = torch.empty(t, h, d // 32, dtype=torch.uint8) if use_fp4 else None
+    w_out = torch.empty(t, h, dtype=torch.float32)
+    rc = lib().dsv4_oracle_indexer_q_rope_quant(positions.data_ptr(), q.data_ptr(), cs.data_ptr(), cs.shape[1], w.data_ptr(),
+                                                float(softmax_scale), float(head_scale), t, h, d, 1 if use_fp4 else 0,
+                                                out.data_ptr(), scales.data_ptr() if use_fp4 else None, w_out.data_ptr())
+    if rc != 0:
+        raise ValueError("dsv4_oracle_indexer_q_rope_quant rejected its arguments")
+    return out, scales, w_out
 
 
 def e4m3_from_f32(x: torch.Tensor) -> torch.Tensor:

@@ -454,4 +454,75 @@ int dsv4_oracle_indexer_k_quant(const uint16_t* k, int64_t k_stride, int is_fp16
     return 0;
 }
 
+/* e2m1 code of |v| <= 6 with the tie rule of tests/test_fused_indexer_q_rope_quant.py:81-92 (nearest, ties to even). */
+static inline uint8_t e2m1_code(float v) {
+    float a = fabsf(v);
+    uint8_t code = 0;
+    if (a > 0.25f) code = 1;
+    if (a >= 0.75f) code = 2;
+    if (a > 1.25f) code = 3;
+    if (a >= 1.75f) code = 4;
+    if (a > 2.5f) code = 5;
+    if (a >= 3.5f) code = 6;
+    if (a > 5.0f) code = 7;
+    uint32_t u;
+    memcpy(&u, &v, 4);
+    return (uint8_t)(code | ((u >> 31) << 3));
+}
+
+/*
+ * Sparse-indexer q prologue, the torch statement tests/test_fused_indexer_q_rope_quant.py:48-113 of
+ * src/flaggems_vllm/ops/fused_indexer_q_rope_quant.py:69-280.  q bf16 [T, H, D] dense; cos_sin fp32 [max_pos, rot_dim];
+ * weights fp32 [T, H] (already widened).  fp4 == 0: out e4m3 [T, H, D], weights_out = w*scale*softmax*head.
+ * fp4 != 0: out [T, H, D/2] packed e2m1, scales [T, H, D/32] bytes, weights_out = w*softmax*head.
+ */
+int dsv4_oracle_indexer_q_rope_quant(const int64_t* positions, const uint16_t* q, const float* cos_sin, int64_t rot_dim,
+                                     const float* weights, float softmax_scale, float head_scale, int64_t num_tokens,
+                                     int64_t num_heads, int64_t head_dim, int fp4, uint8_t* out, uint8_t* scales,
+                                     float* weights_out) {
+    if (num_tokens < 0 || head_dim <= 0 || head_dim > 1024 || rot_dim > head_dim || rot_dim % 2) return -1;
+    const int64_t nope = head_dim - rot_dim, half = rot_dim / 2;
+    for (int64_t t = 0; t < num_tokens; ++t) {
+        const float* cs = cos_sin + positions[t] * rot_dim;
+        for (int64_t h = 0; h < num_heads; ++h) {
+            const uint16_t* row = q + (t * num_heads + h) * head_dim;
+            float x[1024];
+            for (int64_t i = 0; i < nope; ++i) x[i] = bf16_bits_to_f32(row[i]);
+            for (int64_t j = 0; j < half; ++j) {
+                float e = bf16_bits_to_f32(row[nope + 2 * j]), o = bf16_bits_to_f32(row[nope + 2 * j + 1]);
+                float ec = e * cs[j], os = o * cs[half + j], oc = o * cs[j], es = e * cs[half + j];
+                x[nope + 2 * j] = bf16_bits_to_f32(f32_to_bf16_bits(ec - os));
+                x[nope + 2 * j + 1] = bf16_bits_to_f32(f32_to_bf16_bits(oc + es));
+            }
+            float w = weights[t * num_heads + h];
+            if (!fp4) {
+                float amax = 0.0f;
+                for (int64_t i = 0; i < head_dim; ++i) amax = fabsf(x[i]) > amax ? fabsf(x[i]) : amax;
+                float scale = exp2f(ceilf(log2f((amax > 1e-4f ? amax : 1e-4f) / 448.0f)));
+                for (int64_t i = 0; i < head_dim; ++i) out[(t * num_heads + h) * head_dim + i] = f32_to_e4m3_bits(x[i] / scale);
+                w = w * scale;
+            } else {
+                for (int64_t b = 0; b < head_dim / 32; ++b) {
+                    float amax = 0.0f;
+                    for (int i = 0; i < 32; ++i) amax = fabsf(x[32 * b + i]) > amax ? fabsf(x[32 * b + i]) : amax;
+                    const float floor_ = 6.0f * 1.17549435e-38f;
+                    float lr = ceilf(log2f((amax > floor_ ? amax : floor_) / 6.0f));
+                    lr = lr < -127.0f ? -127.0f : (lr > 127.0f ? 127.0f : lr);
+                    float scale = exp2f(lr);
+                    scales[(t * num_heads + h) * (head_dim / 32) + b] = (uint8_t)(lr + 127.0f);
+                    for (int i = 0; i < 32; i += 2) {
+                        float lo = x[32 * b + i] / scale, hi = x[32 * b + i + 1] / scale;
+                        lo = lo < -6.0f ? -6.0f : (lo > 6.0f ? 6.0f : lo);
+                        hi = hi < -6.0f ? -6.0f : (hi > 6.0f ? 6.0f : hi);
+                        out[(t * num_heads + h) * (head_dim / 2) + (32 * b + i) / 2] = (uint8_t)(e2m1_code(lo) | (e2m1_code(hi) << 4));
+                    }
+                }
+            }
+            w = w * softmax_scale;
+            weights_out[t * num_heads + h] = w * head_scale;
+        }
+    }
+    return 0;
+}
+
 const char* dsv4_oracle_version(void) { return "dsv4-oracle 1"; }

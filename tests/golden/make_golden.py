@@ -243,7 +243,37 @@ def indexer_cases() -> None:
         print(name, "ok")
 
 
+def indexer_q_cases() -> None:
+    """Seeded inputs through the upstream test's torch statements `_rotate_tail_gptj`, `_reference_fp8` and
+    `_reference_mxfp4` (tests/test_fused_indexer_q_rope_quant.py:48-113), with the test's geometry (8 heads x 128,
+    rotary tail 64, fp32 and bf16 tables) and its token counts (:121)."""
+    M = ref_loader.load_upstream_helper_test("test_fused_indexer_q_rope_quant.py", "flaggems_vllm.ops", ("fused_indexer_q_rope_quant",),
+                                             package_attrs={"SUPPORTED_FP8_DTYPE": torch.float8_e4m3fn})
+    for tokens in (1, 7, 32):
+        for cache_dtype in (torch.float32, torch.bfloat16):
+            torch.manual_seed(400 + tokens)
+            q = torch.randn(tokens, 8, 128, dtype=torch.bfloat16)
+            if tokens == 7:  # zero head, tiny head, exact power-of-two amax, e2m1 ties
+                q[0, 0] = 0
+                q[0, 1] *= 1e-6
+                q[1, 0, :64] = torch.tensor([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 6.0] * 8).to(torch.bfloat16)
+                q[1, 1, 3] = 7.0
+            pos = torch.randint(0, 4096, (tokens,), dtype=torch.int64)
+            cs = M._make_cos_sin_cache(4096, 64, "cpu", cache_dtype)
+            w = torch.randn(tokens, 8, dtype=torch.bfloat16)
+            sm, hs = 128 ** -0.5, 8 ** -0.5
+            q_rot = M._rotate_tail_gptj(q, pos, cs)
+            f8, w8 = M._reference_fp8(q_rot.clone(), w, sm, hs)
+            (p4, s4), w4 = M._reference_mxfp4(q_rot.clone(), w, sm, hs)
+            name = f"indexer_q_t{tokens}_{'bf16' if cache_dtype == torch.bfloat16 else 'f32'}table"
+            np.savez_compressed(HERE / f"{name}.npz", q=u16(q), positions=pos.numpy(), weights=u16(w), table_bf16=int(cache_dtype == torch.bfloat16),
+                                fp8=f8.view(torch.uint8).numpy(), w_fp8=w8.numpy(), fp4=p4.numpy(), fp4_scales=s4.numpy(), w_fp4=w4.numpy())
+            print(name, "ok")
+
+
 if __name__ == "__main__":
+    if len(sys.argv) < 2 or sys.argv[1] == "indexer_q":
+        indexer_q_cases()
     if len(sys.argv) < 2 or sys.argv[1] == "indexer":
         indexer_cases()
     if len(sys.argv) < 2 or sys.argv[1] == "inv_rope":

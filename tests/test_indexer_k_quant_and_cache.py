@@ -10,7 +10,7 @@ import flaggems_vllm
 from conftest import GOLDEN
 from oracle import c_oracle
 
-NAMES = sorted(p.stem for p in GOLDEN.glob("indexer_*.npz"))
+NAMES = sorted(p.stem for p in GOLDEN.glob("indexer_*f16_*.npz"))
 DEV = "cuda:0"
 
 
