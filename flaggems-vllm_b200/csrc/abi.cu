@@ -213,7 +213,8 @@ int dsv4_fused_indexer_q_rope_quant(const int64_t* positions, const void* index_
     if (rot_dim < 0 || rot_dim > head_dim || rot_dim % 2 != 0 || (head_dim - rot_dim) % lane_elems != 0) return DSV4_ERR_BAD_SIZE;
     if (weights_dtype < 0 || weights_dtype > 2) return DSV4_ERR_BAD_SIZE;
     if (num_tokens == 0) return DSV4_OK;
-    if (!positions || !index_q || !cos_sin_cache || !q_out || !weights || !weights_out || (use_fp4 && !q_scales_out))
+    if (!positions || !index_q || (!cos_sin_cache && rot_dim > 0) || !q_out || !weights || !weights_out ||
+        (use_fp4 && !q_scales_out))
         return DSV4_ERR_NULL_POINTER;
     const auto addr = [](const void* p) { return reinterpret_cast<uintptr_t>(p); };
     const int64_t in_bytes = lane_elems * 2, out_bytes = use_fp4 ? lane_elems / 2 : lane_elems;

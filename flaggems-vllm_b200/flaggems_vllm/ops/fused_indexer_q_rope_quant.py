@@ -78,7 +78,11 @@ def fused_indexer_q_rope_quant(
                 )
             )
     if use_fp4:
-        return (q_out, q_scale.view(torch.int32).squeeze(-1)), index_weights_out
+        # four UE8M0 bytes per head (head_dim 128) are handed on as one int32, as the reference does; other
+        # head sizes keep the byte tensor where the reference's int32 view is only defined for multiples of 4
+        if q_scale.shape[-1] % 4 == 0:
+            q_scale = q_scale.view(torch.int32).squeeze(-1)
+        return (q_out, q_scale), index_weights_out
     return q_out, index_weights_out
 
 
