@@ -93,6 +93,24 @@ int dsv4_qnorm_rope_kv_insert(void* q, const void* kv, void* k_cache, const int6
     return static_cast<int>(err);
 }
 
+int dsv4_qnorm_rope_kv_insert_padded(const void* q, void* q_out, const void* kv, void* k_cache, const int64_t* slot_mapping,
+                                     const int64_t* position_ids, const float* cos_sin_cache, float eps, int64_t num_tokens,
+                                     int64_t num_heads, int64_t padded_heads, int64_t num_tokens_insert,
+                                     int64_t cache_block_size, int64_t kv_block_stride_bytes, void* cuda_stream) {
+    const int rc = validate(q, kv, k_cache, slot_mapping, position_ids, cos_sin_cache, num_tokens, num_heads,
+                            num_tokens_insert, cache_block_size, kv_block_stride_bytes);
+    if (rc != DSV4_OK || num_tokens == 0) return rc;
+    if (padded_heads < num_heads || padded_heads >= (1LL << 31) || num_tokens > ((1LL << 31) - 1) / (padded_heads > 0 ? padded_heads : 1))
+        return DSV4_ERR_BAD_SIZE;
+    if (padded_heads > 0 && !q_out) return DSV4_ERR_NULL_POINTER;
+    if (!aligned16(q_out)) return DSV4_ERR_MISALIGNED;
+    PrologueParams p = make_params(const_cast<void*>(q), kv, k_cache, slot_mapping, position_ids, cos_sin_cache, eps, num_tokens,
+                                   num_heads, num_tokens_insert, cache_block_size, kv_block_stride_bytes);
+    p.q_out = static_cast<uint8_t*>(q_out);
+    p.out_heads = padded_heads;
+    return static_cast<int>(launch_prologue_rows_padded(p, static_cast<cudaStream_t>(cuda_stream)));
+}
+
 int dsv4_qnorm_rope_kv_insert_checked(void* q, const void* kv, void* k_cache, const int64_t* slot_mapping,
                                       const int64_t* position_ids, const float* cos_sin_cache, float eps,
                                       int64_t num_tokens, int64_t num_heads, int64_t num_tokens_insert,

@@ -49,6 +49,10 @@ struct PrologueParams {
     // row / num_heads for row < 2^31 without a divide: (row * heads_mul) >> heads_shift
     uint32_t heads_mul;
     uint32_t heads_shift;
+    // out-of-place form only: q rows are written to q_out [num_tokens, out_heads, 512] (out_heads >= num_heads),
+    // heads num_heads..out_heads-1 of every token are zero-filled; q itself is then left untouched
+    uint8_t* q_out;
+    int64_t out_heads;
 };
 
 // floor(n / d) for n < 2^31 via the multiplier the host derived with make_fast_divisor().
@@ -324,6 +328,7 @@ __device__ __forceinline__ void kv_row_to_cache(const uint4& a, const uint4& b, 
 
 // Launchers implemented by the kernel files; each returns cudaGetLastError() of its launch.
 cudaError_t launch_prologue_rows(const PrologueParams& p, bool checked, cudaStream_t stream);
+cudaError_t launch_prologue_rows_padded(const PrologueParams& p, cudaStream_t stream);
 cudaError_t launch_prologue_bulk(const PrologueParams& p, cudaStream_t stream);
 cudaError_t launch_gather_dequant(const uint8_t* k_cache, const int64_t* slots, int64_t num_slots, uint8_t* out,
                                   int64_t out_row_stride, int64_t block_size, int64_t block_stride,

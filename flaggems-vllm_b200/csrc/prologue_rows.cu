@@ -16,7 +16,9 @@
 namespace dsv4 {
 namespace {
 
-template <int RPW, int WARPS, int MIN_CTAS, bool CHECKED>
+// PADDED: out-of-place form (vLLM >= 0.22 calls the operator that way): rows go to p.q_out with out_heads heads per
+// token and the CTAs after the q tiles zero-fill the extra heads.
+template <int RPW, int WARPS, int MIN_CTAS, bool CHECKED, bool PADDED>
 __global__ void __launch_bounds__(WARPS * 32, MIN_CTAS) prologue_rows_kernel(const PrologueParams p, const int64_t kv_ctas) {
     constexpr int TILE = RPW * WARPS;
     constexpr int MAX_TOKENS = TILE + 1;  // a tile of TILE rows touches at most TILE tokens (+1 slack)
@@ -60,6 +62,23 @@ __global__ void __launch_bounds__(WARPS * 32, MIN_CTAS) prologue_rows_kernel(con
     const uint32_t total_rows = static_cast<uint32_t>(p.num_tokens * p.num_heads);
     const uint32_t tile_row0 = (blockIdx.x - static_cast<uint32_t>(kv_ctas)) * TILE;
     const uint32_t row0 = tile_row0 + warp * RPW;
+    if (PADDED && tile_row0 >= total_rows) {
+        // zero-fill: padding row j is head num_heads + j % extra of token j / extra
+        const uint32_t extra = static_cast<uint32_t>(p.out_heads - p.num_heads);
+        const uint32_t pad_rows = static_cast<uint32_t>(p.num_tokens) * extra;
+        const uint32_t first_pad_tile = (total_rows + TILE - 1) / TILE * TILE;
+#pragma unroll
+        for (int i = 0; i < RPW; ++i) {
+            const uint32_t j = row0 - first_pad_tile + i;
+            if (j >= pad_rows) break;
+            const uint32_t tok = j / extra;
+            uint8_t* dst = p.q_out + (static_cast<uint64_t>(tok) * p.out_heads + p.num_heads + (j - tok * extra)) * kRowBytes;
+            const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+            st_stream16(dst + 16 * lane, z);
+            st_stream16(dst + 512 + 16 * lane, z);
+        }
+        return;
+    }
 
     // 1. every row load of the CTA goes out first (A/B/T layout, 16 + 16 + 4 bytes per lane)
     uint4 a[RPW], b[RPW];
@@ -100,13 +119,15 @@ __global__ void __launch_bounds__(WARPS * 32, MIN_CTAS) prologue_rows_kernel(con
 #pragma unroll
     for (int i = 0; i < RPW; ++i) {
         if (row0 + i >= total_rows) break;
-        const int tok = static_cast<int>(fast_div(row0 + i, p.heads_mul, p.heads_shift) - first_token);
+        const uint32_t token = fast_div(row0 + i, p.heads_mul, p.heads_shift);
+        const int tok = static_cast<int>(token - first_token);
         if (CHECKED && bad_token[tok]) continue;
         float xa[8], xb[8];
         unpack8(a[i], xa), unpack8(b[i], xb);
         const float r = row_inv_rms(xa, xb, tail[i], p.eps);
         scale8(xa, r), scale8(xb, r);
-        uint8_t* row = p.q + static_cast<uint64_t>(row0 + i) * kRowBytes;
+        uint8_t* row = PADDED ? p.q_out + (static_cast<uint64_t>(row0 + i) + static_cast<uint64_t>(token) * (p.out_heads - p.num_heads)) * kRowBytes
+                              : p.q + static_cast<uint64_t>(row0 + i) * kRowBytes;
         st_stream16(row + 16 * lane, pack8(xa));
         if (lane < kFirstRopeLane) st_stream16(row + 512 + 16 * lane, pack8(xb));
         st_stream4(row + 2 * kNopeDim + 4 * lane,
@@ -124,9 +145,23 @@ cudaError_t launch(const PrologueParams& p, bool checked, cudaStream_t stream) {
     if (grid == 0) return cudaSuccess;
     if (grid > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
     if (checked)
-        prologue_rows_kernel<RPW, WARPS, MIN_CTAS, true><<<static_cast<unsigned>(grid), WARPS * 32, 0, stream>>>(p, kv_ctas);
+        prologue_rows_kernel<RPW, WARPS, MIN_CTAS, true, false><<<static_cast<unsigned>(grid), WARPS * 32, 0, stream>>>(p, kv_ctas);
     else
-        prologue_rows_kernel<RPW, WARPS, MIN_CTAS, false><<<static_cast<unsigned>(grid), WARPS * 32, 0, stream>>>(p, kv_ctas);
+        prologue_rows_kernel<RPW, WARPS, MIN_CTAS, false, false><<<static_cast<unsigned>(grid), WARPS * 32, 0, stream>>>(p, kv_ctas);
+    count_launch();
+    return cudaGetLastError();
+}
+
+template <int RPW, int WARPS, int MIN_CTAS>
+cudaError_t launch_padded(const PrologueParams& p, cudaStream_t stream) {
+    constexpr int TILE = RPW * WARPS;
+    const int64_t kv_ctas = (p.num_tokens_insert + WARPS - 1) / WARPS;
+    const int64_t q_ctas = (p.num_tokens * p.num_heads + TILE - 1) / TILE;
+    const int64_t pad_ctas = (p.num_tokens * (p.out_heads - p.num_heads) + TILE - 1) / TILE;
+    const int64_t grid = kv_ctas + q_ctas + pad_ctas;
+    if (grid == 0) return cudaSuccess;
+    if (grid > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
+    prologue_rows_kernel<RPW, WARPS, MIN_CTAS, false, true><<<static_cast<unsigned>(grid), WARPS * 32, 0, stream>>>(p, kv_ctas);
     count_launch();
     return cudaGetLastError();
 }
@@ -141,5 +176,7 @@ cudaError_t launch_prologue_rows(const PrologueParams& p, bool checked, cudaStre
     return launch<2, 4, 10>(p, checked, stream);
 #endif
 }
+
+cudaError_t launch_prologue_rows_padded(const PrologueParams& p, cudaStream_t stream) { return launch_padded<2, 4, 10>(p, stream); }
 
 }  // namespace dsv4

@@ -15,6 +15,7 @@ LIB_PATH = Path(__file__).resolve().parent / LIB_NAME
 EXPORTS = (
     "dsv4_qnorm_rope_kv_insert",
     "dsv4_qnorm_rope_kv_insert_checked",
+    "dsv4_qnorm_rope_kv_insert_padded",
     "dsv4_gather_dequant_k_cache",
     "dsv4_dequantize_and_gather_k_cache",
     "dsv4_fused_q_kv_rmsnorm",
@@ -62,6 +63,8 @@ def lib() -> ctypes.CDLL:
     L.dsv4_qnorm_rope_kv_insert_checked.argtypes = [vp, vp, vp, vp, vp, vp, f32, i64, i64, i64, i64, i64,
                                                     i64, i64, vp, vp]
     L.dsv4_qnorm_rope_kv_insert_checked.restype = i32
+    L.dsv4_qnorm_rope_kv_insert_padded.argtypes = [vp, vp, vp, vp, vp, vp, vp, f32, i64, i64, i64, i64, i64, i64, vp]
+    L.dsv4_qnorm_rope_kv_insert_padded.restype = i32
     L.dsv4_gather_dequant_k_cache.argtypes = [vp, vp, i64, vp, i64, i64, i64, vp]
     L.dsv4_gather_dequant_k_cache.restype = i32
     L.dsv4_dequantize_and_gather_k_cache.argtypes = [vp, i64, i64, i64, vp, vp, vp, vp, i64, i64, i64, i64, i64,

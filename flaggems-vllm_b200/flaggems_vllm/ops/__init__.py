@@ -4,6 +4,7 @@ from .deepseek_v4_attention_fused_q_kv_rmsnorm import fused_q_kv_rmsnorm
 from .fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert import (
     fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert,
     fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert_checked,
+    fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert_padded,
 )
 from .fused_indexer_q_rope_quant import fused_indexer_q_rope_quant
 from .fused_inv_rope_fp8_quant import fused_inv_rope_fp8_quant
@@ -19,6 +20,7 @@ __all__ = [
     "dequantize_and_gather_k_cache",
     "fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert",
     "fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert_checked",
+    "fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert_padded",
     "gather_dequant_k_cache_slots",
     "HostStagedPrologue",
 ]

@@ -83,6 +83,50 @@ def fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert(
         )
 
 
+def fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert_padded(
+    q: torch.Tensor,
+    kv: torch.Tensor,
+    k_cache: torch.Tensor,
+    slot_mapping: torch.Tensor,
+    position_ids: torch.Tensor,
+    cos_sin_cache: torch.Tensor,
+    padded_heads: int,
+    eps: float,
+    cache_block_size: int,
+) -> torch.Tensor:
+    """The nine-argument, out-of-place form vLLM >= 0.22 uses: q is left untouched and a new tensor
+    [num_tokens, padded_heads, 512] is returned whose first num_heads heads hold the normalised, rotated q and
+    whose remaining heads are zero; the KV side is the same as in the in-place operator."""
+    assert q.is_contiguous() and kv.is_contiguous()
+    num_tokens, num_heads, head_dims = q.shape
+    assert head_dims == HEAD_DIM and padded_heads >= num_heads
+    assert kv.shape == (num_tokens, HEAD_DIM)
+    assert q.dtype == torch.bfloat16 and kv.dtype == torch.bfloat16 and k_cache.dtype == torch.uint8
+    assert slot_mapping.dim() == 1 and slot_mapping.shape[0] <= num_tokens and slot_mapping.dtype == torch.int64
+    assert position_ids.shape == (num_tokens,) and position_ids.dtype == torch.int64
+    assert cos_sin_cache.dim() == 2 and cos_sin_cache.shape[1] == ROPE_DIM and cos_sin_cache.dtype == torch.float32
+    assert k_cache.dim() == 2 and k_cache.stride(1) == 1 and cache_block_size > 0
+    assert k_cache.shape[1] >= cache_block_size * TOKEN_BYTES, "cache block too small"
+    assert slot_mapping.is_contiguous() and position_ids.is_contiguous() and cos_sin_cache.is_contiguous()
+    dev = q.device
+    assert dev.type == "cuda", "this operator has no CPU path: tensors must live on a CUDA device"
+    for t in (kv, k_cache, slot_mapping, position_ids, cos_sin_cache):
+        assert t.device == dev, "all tensors must be on the same device"
+    q_out = torch.empty(num_tokens, padded_heads, HEAD_DIM, dtype=q.dtype, device=dev)
+    if num_tokens == 0:
+        return q_out
+    with torch.cuda.device(dev):
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        _native.check(
+            _native.lib().dsv4_qnorm_rope_kv_insert_padded(
+                q.data_ptr(), q_out.data_ptr(), kv.data_ptr(), k_cache.data_ptr(), slot_mapping.data_ptr(),
+                position_ids.data_ptr(), cos_sin_cache.data_ptr(), float(eps), num_tokens, num_heads, int(padded_heads),
+                slot_mapping.shape[0], int(cache_block_size), k_cache.stride(0), stream,
+            )
+        )
+    return q_out
+
+
 def fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert_checked(
     q, kv, k_cache, slot_mapping, position_ids, cos_sin_cache, eps, cache_block_size
 ) -> int:

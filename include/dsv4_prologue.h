@@ -67,6 +67,19 @@ int dsv4_qnorm_rope_kv_insert(void* q, const void* kv, void* k_cache, const int6
                               int64_t cache_block_size, int64_t kv_block_stride_bytes, void* cuda_stream);
 
 /*
+ * Out-of-place form with head padding: q [num_tokens, num_heads, 512] is read only, the normalised and
+ * rotated rows go to q_out [num_tokens, padded_heads, 512] (padded_heads >= num_heads, 16-byte aligned) and
+ * heads num_heads..padded_heads-1 of every token are zero-filled; the KV side is identical.  This is how
+ * vLLM >= 0.22 calls the operator (torch.ops._C.<same name> with an extra padded_heads argument, returning
+ * the padded tensor); the reference pins the 8-argument in-place form (OP:289-298), so this entry point has
+ * no counterpart there.  One launch, DSV4_VARIANT_ROWS kernel.
+ */
+int dsv4_qnorm_rope_kv_insert_padded(const void* q, void* q_out, const void* kv, void* k_cache, const int64_t* slot_mapping,
+                                     const int64_t* position_ids, const float* cos_sin_cache, float eps, int64_t num_tokens,
+                                     int64_t num_heads, int64_t padded_heads, int64_t num_tokens_insert,
+                                     int64_t cache_block_size, int64_t kv_block_stride_bytes, void* cuda_stream);
+
+/*
  * Same operator with the device-side range checks the reference lacks: a token whose
  * position is outside [0, max_pos) or whose slot is >= num_blocks*cache_block_size is
  * left unprocessed and a bit is OR-ed into *status (device int32, caller-zeroed):

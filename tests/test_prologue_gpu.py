@@ -361,3 +361,24 @@ def test_hbm_probe_modes_leave_or_fill_the_buffer():
     torch.cuda.synchronize()
     assert torch.equal(buf[rows * 1024 :], before[rows * 1024 :])
     assert not torch.equal(buf[: rows * 1024], before[: rows * 1024])
+
+
+@pytest.mark.parametrize("n_heads,padded", [(8, 16), (7, 8), (64, 64), (128, 192), (1, 3)])
+def test_out_of_place_padded_form(n_heads, padded):
+    """The nine-argument form: q untouched, result in a new [N, padded, 512] tensor with zero padding heads,
+    cache identical to the in-place operator's."""
+    q, kv, kc, slots, pos, cs = random_case(45, n_heads, 16, 6, seed=60 + n_heads, minus_one=4)
+    q_ref, kc_ref = oracle_of(q, kv, kc, slots, pos, cs, 1e-6, 16)
+    q_before = q.clone()
+    launches = _native.launch_count()
+    out = flaggems_vllm.fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert_padded(q, kv, kc, slots, pos, cs, padded, 1e-6, 16)
+    torch.cuda.synchronize()
+    assert _native.launch_count() == launches + 1
+    assert torch.equal(q, q_before), "q is read-only in this form"
+    assert out.shape == (45, padded, 512)
+    compare.assert_q_close(out[:, :n_heads].cpu().contiguous(), q_ref)
+    assert int((out[:, n_heads:].view(torch.int16) != 0).sum()) == 0, "padding heads must be zero"
+    assert torch.equal(kc.cpu(), kc_ref)
+    # identical bits to the in-place operator
+    op(q, kv, kc, slots, pos, cs, 1e-6, 16)
+    assert torch.equal(out[:, :n_heads].contiguous().view(torch.int16), q.view(torch.int16))
