@@ -254,6 +254,25 @@ def sibling_ops(steps, warmup):
                       torch.cuda.synchronize)
     out["dequantize_and_gather_k_cache"] = {"tokens": reqs * seq, "us_per_launch": secs / steps * 1e6,
                                             "hbm_gbs": reqs * seq * (584 + 1024) * steps / secs / 1e9}
+    del cache, dst
+    # sparse-indexer siblings: 64 Ki tokens, 64 index heads x 128 (q), one 128-wide key per token (k)
+    nt, ih = 65536, 64
+    iq = torch.randn(nt, ih, 128, generator=g, device=dev).to(torch.bfloat16)
+    ipos = torch.randint(0, 65536, (nt,), generator=g, device=dev, dtype=torch.int64)
+    iw = torch.randn(nt, ih, generator=g, device=dev).to(torch.bfloat16)
+    for fp4, key, out_b in ((False, "fused_indexer_q_rope_quant[fp8]", 128), (True, "fused_indexer_q_rope_quant[mxfp4]", 68)):
+        secs = time_steps(lambda: flaggems_vllm.fused_indexer_q_rope_quant(ipos, iq, cs, iw, 0.088, 0.125, use_fp4=fp4), steps, warmup,
+                          stream, torch.cuda.synchronize)
+        out[key] = {"rows": nt * ih, "us_per_launch": secs / steps * 1e6, "hbm_gbs": nt * ih * (256 + out_b + 6) * steps / secs / 1e9,
+                    "note": "includes torch.empty of the outputs per call"}
+    del iq
+    nk = 1 << 20
+    ik = torch.randn(nk, 128, generator=g, device=dev).to(torch.bfloat16)
+    icache = torch.zeros(nk // 64, 64, 132, device=dev, dtype=torch.uint8)
+    islots = torch.randperm(nk, generator=g, device=dev).to(torch.int64)
+    secs = time_steps(lambda: flaggems_vllm.indexer_k_quant_and_cache(ik, icache, islots, 128, "ue8m0"), steps, warmup, stream,
+                      torch.cuda.synchronize)
+    out["indexer_k_quant_and_cache"] = {"tokens": nk, "us_per_launch": secs / steps * 1e6, "hbm_gbs": nk * (256 + 132 + 8) * steps / secs / 1e9}
     return out
 
 

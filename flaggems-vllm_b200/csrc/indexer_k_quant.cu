@@ -101,6 +101,56 @@ __global__ void __launch_bounds__(WARPS * 32) indexer_k_quant_kernel(const Index
     }
 }
 
+// Fast shape for head_dim 64 / 128 / 256: a token is G = head_dim/8 lanes of 16 bytes, so one warp instruction
+// moves 32/G tokens, and U passes are loaded (slot and row) before any is used.
+template <int WARPS, int G, int U, bool FP16>
+__global__ void __launch_bounds__(WARPS * 32) indexer_k_quant_rows_kernel(const IndexerParams p) {
+    constexpr int TOKENS = 32 / G;
+    const int lane = threadIdx.x & 31, sub = lane % G, which = lane / G;
+    const int64_t base = (static_cast<int64_t>(blockIdx.x) * WARPS + (threadIdx.x >> 5)) * (U * TOKENS) + which;
+    uint4 raw[U];
+    int64_t slot[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        const int64_t t = base + u * TOKENS;
+        slot[u] = t < p.num_tokens ? p.slot_mapping[t] : -1;
+        raw[u] = make_uint4(0u, 0u, 0u, 0u);
+        if (slot[u] >= 0) raw[u] = ld_stream16(p.k + (t * p.k_stride + 8 * sub) * 2);
+    }
+    const int group_lanes = p.quant_block >> 3;  // power of two <= G
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        float x[8];
+        unpack8_any<FP16>(raw[u], x);
+        float amax = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(x[i]));
+        for (int m = 1; m < group_lanes; m <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
+        if (slot[u] < 0) continue;
+        const float s = group_scale(amax, p.ue8m0 != 0);
+        const int64_t block = slot[u] / p.block_size, in_block = slot[u] - block * p.block_size;
+        uint8_t* blk = p.cache + block * p.block_stride;
+        if (p.ue8m0) {
+            const float inv = __uint_as_float((254u - (__float_as_uint(s) >> 23)) << 23);  // exact reciprocal of a power of two
+#pragma unroll
+            for (int i = 0; i < 8; ++i) x[i] = __fmul_rn(x[i], inv);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) x[i] = __fdiv_rn(x[i], s);
+        }
+        st_global8(blk + in_block * p.head_dim + 8 * sub, make_uint2(pack_e4m3x4(x[0], x[1], x[2], x[3]), pack_e4m3x4(x[4], x[5], x[6], x[7])));
+        if ((sub & (group_lanes - 1)) == 0)
+            reinterpret_cast<float*>(blk + p.block_size * p.head_dim)[in_block * p.num_quant_blocks + sub / group_lanes] = s;
+    }
+}
+
+template <int G, bool FP16>
+void launch_rows(const IndexerParams& p, cudaStream_t stream) {
+    constexpr int WARPS = 4, U = 2, PER_CTA = WARPS * U * (32 / G);
+    const unsigned grid = static_cast<unsigned>((p.num_tokens + PER_CTA - 1) / PER_CTA);
+    indexer_k_quant_rows_kernel<WARPS, G, U, FP16><<<grid, WARPS * 32, 0, stream>>>(p);
+}
+
 }  // namespace
 
 cudaError_t launch_indexer_k_quant(const void* k, int64_t k_stride, int is_fp16, void* cache, int64_t block_stride,
@@ -118,6 +168,13 @@ cudaError_t launch_indexer_k_quant(const void* k, int64_t k_stride, int is_fp16,
                (addr(cache) & 7u) == 0 && block_stride % 8 == 0 && head_dim % 8 == 0 && (block_size * head_dim) % 4 == 0;
     const int64_t grid = (num_tokens + WARPS - 1) / WARPS;
     if (grid > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
+    if (p.vec_ok && (head_dim == 64 || head_dim == 128 || head_dim == 256)) {
+        if (head_dim == 64) is_fp16 ? launch_rows<8, true>(p, stream) : launch_rows<8, false>(p, stream);
+        else if (head_dim == 128) is_fp16 ? launch_rows<16, true>(p, stream) : launch_rows<16, false>(p, stream);
+        else is_fp16 ? launch_rows<32, true>(p, stream) : launch_rows<32, false>(p, stream);
+        count_launch();
+        return cudaGetLastError();
+    }
     if (is_fp16) indexer_k_quant_kernel<WARPS, true><<<static_cast<unsigned>(grid), WARPS * 32, 0, stream>>>(p);
     else indexer_k_quant_kernel<WARPS, false><<<static_cast<unsigned>(grid), WARPS * 32, 0, stream>>>(p);
     count_launch();

@@ -5,7 +5,8 @@
 //          an sm_100 instruction), weights scaled by softmax_scale*head_scale only.
 // Reference: src/flaggems_vllm/ops/fused_indexer_q_rope_quant.py:69-410 and its torch statement
 // tests/test_fused_indexer_q_rope_quant.py:48-113.
-// One warp per (token, head) row; lane l keeps E = head_dim/32 consecutive values (E/2 rotary pairs).
+// Fast shape: head_dim/8 lanes per (token, head) row, 16 bytes per lane, several rows per warp instruction.
+// General shape: one warp per row; lane l keeps E = head_dim/32 consecutive values (E/2 rotary pairs).
 #include "dsv4_common.cuh"
 
 namespace dsv4 {
@@ -140,6 +141,109 @@ __global__ void __launch_bounds__(WARPS * 32) indexer_q_rope_quant_kernel(const 
     }
 }
 
+// Fast shape: a row is D/8 lanes holding 8 values (16 bytes) each, so one warp instruction moves 32/G rows;
+// U passes per warp are loaded before any is used.  Needs 16-byte aligned rows and a rotary tail that starts
+// on a multiple of 8 values.
+template <int WARPS, int G, int U, bool FP4>
+__global__ void __launch_bounds__(WARPS * 32) indexer_q_rope_quant_rows_kernel(const IndexerQParams p, const int cs_vec4) {
+    constexpr int D = 8 * G, ROWS = 32 / G;
+    const int lane = threadIdx.x & 31, sub = lane % G, slot = lane / G;
+    const uint32_t total = static_cast<uint32_t>(p.num_tokens) * static_cast<uint32_t>(p.num_heads);
+    const uint32_t base_row = (blockIdx.x * WARPS + (threadIdx.x >> 5)) * (U * ROWS) + slot;
+    uint4 raw[U];
+    uint32_t tok[U];
+    bool live[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        const uint32_t row = base_row + u * ROWS;
+        live[u] = row < total;
+        tok[u] = fast_div(live[u] ? row : 0u, p.heads_mul, p.heads_shift);
+        raw[u] = make_uint4(0u, 0u, 0u, 0u);
+        if (live[u]) {
+            const int h = static_cast<int>(row - tok[u] * static_cast<uint32_t>(p.num_heads));
+            raw[u] = ld_stream16(p.q + (static_cast<int64_t>(tok[u]) * p.q_stride0 + h * p.q_stride1 + 8 * sub) * 2);
+        }
+    }
+    const int first_rot = 8 * sub - (D - p.rot_dim);
+    const int half = p.rot_dim >> 1;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        const uint32_t row = base_row + u * ROWS;
+        const int h = static_cast<int>(row - tok[u] * static_cast<uint32_t>(p.num_heads));
+        float x[8];
+        unpack8(raw[u], x);
+        if (live[u] && first_rot >= 0) {
+            const int64_t pos = p.positions[tok[u]];
+            const int pair0 = first_rot >> 1;
+            float c[4], sn[4];
+            if (cs_vec4) {
+                const float* cs = reinterpret_cast<const float*>(p.cos_sin) + pos * p.cos_sin_stride;
+                const float4 c4 = ld_readonly_f4(cs + pair0), s4 = ld_readonly_f4(cs + half + pair0);
+                c[0] = c4.x, c[1] = c4.y, c[2] = c4.z, c[3] = c4.w, sn[0] = s4.x, sn[1] = s4.y, sn[2] = s4.z, sn[3] = s4.w;
+            } else if (p.cos_sin_bf16) {
+                const uint16_t* cs = reinterpret_cast<const uint16_t*>(p.cos_sin) + pos * p.cos_sin_stride;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) c[j] = bf16_lo(cs[pair0 + j]), sn[j] = bf16_lo(cs[half + pair0 + j]);
+            } else {
+                const float* cs = reinterpret_cast<const float*>(p.cos_sin) + pos * p.cos_sin_stride;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) c[j] = cs[pair0 + j], sn[j] = cs[half + pair0 + j];
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float e = x[2 * j], o = x[2 * j + 1];
+                const uint32_t packed = pack_bf16x2(__fsub_rn(__fmul_rn(e, c[j]), __fmul_rn(o, sn[j])),
+                                                    __fadd_rn(__fmul_rn(o, c[j]), __fmul_rn(e, sn[j])));
+                x[2 * j] = bf16_lo(packed), x[2 * j + 1] = bf16_hi(packed);
+            }
+        }
+        float amax = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(x[i]));
+        uint8_t* out = p.out + static_cast<int64_t>(tok[u]) * p.out_stride0 + h * p.out_stride1;
+        float weight_factor = 1.0f;
+        if (FP4) {
+#pragma unroll
+            for (int m = 1; m < 4; m <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
+            const uint32_t bits = __float_as_uint(__fdiv_rn(fmaxf(amax, 6.0f * 1.17549435e-38f), 6.0f));
+            uint32_t code = ((bits >> 23) & 0xffu) + ((bits & 0x7fffffu) ? 1u : 0u);
+            code = code > 254u ? 254u : code;
+            const float inv = __uint_as_float((254u - code) << 23);
+            uint32_t bytes = 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) bytes |= pack_e2m1x2(__fmul_rn(x[2 * j], inv), __fmul_rn(x[2 * j + 1], inv)) << (8 * j);
+            if (live[u]) {
+                *reinterpret_cast<uint32_t*>(out + 4 * sub) = bytes;
+                if ((sub & 3) == 0)
+                    p.scales[static_cast<int64_t>(tok[u]) * p.scale_stride0 + h * p.scale_stride1 + (sub >> 2)] = static_cast<uint8_t>(code);
+            }
+        } else {
+#pragma unroll
+            for (int m = 1; m < G; m <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
+            const uint32_t code = ue8m0_code(amax);
+            const float inv = __uint_as_float((254u - code) << 23);
+            weight_factor = __uint_as_float(code << 23);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) x[i] = __fmul_rn(x[i], inv);
+            if (live[u]) st_global8(out + 8 * sub, make_uint2(pack_e4m3x4(x[0], x[1], x[2], x[3]), pack_e4m3x4(x[4], x[5], x[6], x[7])));
+        }
+        if (live[u] && sub == 0) {
+            float w = load_weight(p.weights, static_cast<int64_t>(tok[u]) * p.weights_stride + h, p.weights_dtype);
+            if (!FP4) w = __fmul_rn(w, weight_factor);
+            p.weights_out[static_cast<int64_t>(tok[u]) * p.weights_out_stride + h] = __fmul_rn(__fmul_rn(w, p.softmax_scale), p.head_scale);
+        }
+    }
+}
+
+template <int G>
+cudaError_t launch_rows(const IndexerQParams& p, bool fp4, int64_t rows, int cs_vec4, cudaStream_t stream) {
+    constexpr int WARPS = 4, U = 2, PER_CTA = WARPS * U * (32 / G);
+    const unsigned grid = static_cast<unsigned>((rows + PER_CTA - 1) / PER_CTA);
+    if (fp4) indexer_q_rope_quant_rows_kernel<WARPS, G, U, true><<<grid, WARPS * 32, 0, stream>>>(p, cs_vec4);
+    else indexer_q_rope_quant_rows_kernel<WARPS, G, U, false><<<grid, WARPS * 32, 0, stream>>>(p, cs_vec4);
+    return cudaGetLastError();
+}
+
 template <int E>
 cudaError_t launch_e(const IndexerQParams& p, bool fp4, unsigned grid, cudaStream_t stream) {
     constexpr int WARPS = 8;
@@ -168,6 +272,18 @@ cudaError_t launch_indexer_q_rope_quant(const int64_t* positions, const void* q,
     p.weights_out = weights_out, p.weights_out_stride = weights_out_stride;
     p.softmax_scale = softmax_scale, p.head_scale = head_scale, p.num_tokens = num_tokens, p.num_heads = num_heads;
     make_fast_divisor(static_cast<uint32_t>(num_heads), &p.heads_mul, &p.heads_shift);
+    const auto addr = [](const void* q_) { return reinterpret_cast<uintptr_t>(q_); };
+    const int nope = head_dim - rot_dim;
+    const bool rows_shape = nope % 8 == 0 && rot_dim % 8 == 0 && addr(q) % 16 == 0 && q_stride0 % 8 == 0 && q_stride1 % 8 == 0 &&
+                            addr(out) % 8 == 0 && out_stride0 % 8 == 0 && out_stride1 % 8 == 0;
+    if (rows_shape) {
+        const int cs_vec4 = !cos_sin_bf16 && rot_dim > 0 && addr(cos_sin) % 16 == 0 && cos_sin_stride % 4 == 0 && (rot_dim / 2) % 4 == 0;
+        cudaError_t e = head_dim == 64 ? launch_rows<8>(p, fp4 != 0, rows, cs_vec4, stream)
+                        : head_dim == 128 ? launch_rows<16>(p, fp4 != 0, rows, cs_vec4, stream)
+                        : head_dim == 256 ? launch_rows<32>(p, fp4 != 0, rows, cs_vec4, stream) : cudaErrorInvalidValue;
+        if (e != cudaErrorInvalidValue) count_launch();
+        return e;
+    }
     const unsigned grid = static_cast<unsigned>((rows + 7) / 8);
     cudaError_t err;
     if (head_dim == 64) err = launch_e<2>(p, fp4 != 0, grid, stream);

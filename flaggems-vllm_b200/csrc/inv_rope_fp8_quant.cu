@@ -52,73 +52,88 @@ __device__ __forceinline__ uint2 quant8_pow2(const float (&x)[8], uint32_t code)
 }
 
 // PACKED: power-of-two scales, the 4 UE8M0 bytes of a head packed into one int32.
-template <int WARPS, bool PACKED>
+// Each warp owns RPW consecutive (token, head) rows: all their loads are issued before the first is used.
+template <int WARPS, int RPW, bool PACKED>
 __global__ void __launch_bounds__(WARPS * 32) inv_rope_fp8_quant_kernel(const InvRopeParams p) {
     const int lane = threadIdx.x & 31;
-    const uint32_t row = blockIdx.x * WARPS + (threadIdx.x >> 5);
-    if (row >= static_cast<uint32_t>(p.padded_tokens) * static_cast<uint32_t>(p.num_heads)) return;
-    const uint32_t token = fast_div(row, p.heads_mul, p.heads_shift);
-    const int head = static_cast<int>(row - token * static_cast<uint32_t>(p.num_heads));
-    const int group = static_cast<int>(fast_div(static_cast<uint32_t>(head), p.hpg_mul, p.hpg_shift));
-    const int head_in_group = head - group * p.heads_per_group;
-    uint8_t* scale_row = p.scale + (group * p.scale_stride_group + token) * 4;
-    if (token >= p.num_tokens) {
-        // rows of the token padding (scale columns are padded to a multiple of 4 tokens): zero scales
+    const uint32_t total = static_cast<uint32_t>(p.padded_tokens) * static_cast<uint32_t>(p.num_heads);
+    const uint32_t row0 = (blockIdx.x * WARPS + (threadIdx.x >> 5)) * RPW;
+    uint4 a[RPW], b[RPW];
+    uint32_t token[RPW];
+    int head[RPW];
+#pragma unroll
+    for (int i = 0; i < RPW; ++i) {
+        const uint32_t row = row0 + i;
+        token[i] = fast_div(row, p.heads_mul, p.heads_shift);
+        head[i] = static_cast<int>(row - token[i] * static_cast<uint32_t>(p.num_heads));
+        a[i] = b[i] = make_uint4(0u, 0u, 0u, 0u);
+        if (row < total && token[i] < p.num_tokens) {
+            const uint8_t* in = p.o + (static_cast<int64_t>(token[i]) * p.o_stride_token + head[i] * p.o_stride_head) * 2;
+            a[i] = ld_stream16(in + 16 * lane);
+            b[i] = ld_stream16(in + 512 + 16 * lane);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < RPW; ++i) {
+        if (row0 + i >= total) break;
+        const int group = static_cast<int>(fast_div(static_cast<uint32_t>(head[i]), p.hpg_mul, p.hpg_shift));
+        const int head_in_group = head[i] - group * p.heads_per_group;
+        uint8_t* scale_row = p.scale + (group * p.scale_stride_group + token[i]) * 4;
+        if (token[i] >= p.num_tokens) {
+            // rows of the token padding (scale columns are padded to a multiple of 4 tokens): zero scales
+            if (PACKED) {
+                if (lane == 0) *reinterpret_cast<uint32_t*>(scale_row + head_in_group * p.padded_tokens * 4) = 0u;
+            } else if (lane < 4) {
+                *reinterpret_cast<float*>(scale_row + (head_in_group * 4 + lane) * p.padded_tokens * 4) = 0.0f;
+            }
+            continue;
+        }
+        float xa[8], xb[8];
+        unpack8(a[i], xa);
+        unpack8(b[i], xb);
+        if (lane >= kFirstRopeLane) {
+            const float* cs = p.cos_sin + p.positions[token[i]] * p.cos_sin_stride + 4 * (lane - kFirstRopeLane);
+            const float4 c4 = ld_readonly_f4(cs), s4 = ld_readonly_f4(cs + 32);
+            const float c[4] = {c4.x, c4.y, c4.z, c4.w}, s[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float e = xb[2 * j], o = xb[2 * j + 1];
+                // inverse rotation, products rounded separately, then rounded to bf16 as the torch path does
+                const float e2 = __fadd_rn(__fmul_rn(e, c[j]), __fmul_rn(o, s[j]));
+                const float o2 = __fsub_rn(__fmul_rn(o, c[j]), __fmul_rn(e, s[j]));
+                const uint32_t packed = pack_bf16x2(e2, o2);
+                xb[2 * j] = bf16_lo(packed), xb[2 * j + 1] = bf16_hi(packed);
+            }
+        }
+        float ma = 0.0f, mb = 0.0f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) ma = fmaxf(ma, fabsf(xa[k])), mb = fmaxf(mb, fabsf(xb[k]));
+#pragma unroll
+        for (int m = 1; m <= 8; m <<= 1) {
+            ma = fmaxf(ma, __shfl_xor_sync(0xffffffffu, ma, m));
+            mb = fmaxf(mb, __shfl_xor_sync(0xffffffffu, mb, m));
+        }
+        const float sa = __fmul_rn(fmaxf(ma, p.eps), 1.0f / 448.0f), sb = __fmul_rn(fmaxf(mb, p.eps), 1.0f / 448.0f);
+        uint8_t* out = p.fp8 + (static_cast<int64_t>(group) * p.num_tokens + token[i]) * (static_cast<int64_t>(p.heads_per_group) * kRowBytes / 2) +
+                       static_cast<int64_t>(head_in_group) * (kRowBytes / 2);
         if (PACKED) {
-            if (lane == 0) *reinterpret_cast<uint32_t*>(scale_row + head_in_group * p.padded_tokens * 4) = 0u;
-        } else if (lane < 4) {
-            *reinterpret_cast<float*>(scale_row + (head_in_group * 4 + lane) * p.padded_tokens * 4) = 0.0f;
+            const uint32_t code_a = pow2_ceil_code(sa), code_b = pow2_ceil_code(sb);
+            st_global8(out + 8 * lane, quant8_pow2(xa, code_a));
+            st_global8(out + 256 + 8 * lane, quant8_pow2(xb, code_b));
+            // chunk k of the head in byte k: groups 0,1 from register A (lanes 0 / 16), 2,3 from B
+            const uint32_t word = (__shfl_sync(0xffffffffu, code_a, 0) & 0xffu) | ((__shfl_sync(0xffffffffu, code_a, 16) & 0xffu) << 8) |
+                                  ((__shfl_sync(0xffffffffu, code_b, 0) & 0xffu) << 16) |
+                                  ((__shfl_sync(0xffffffffu, code_b, 16) & 0xffu) << 24);
+            if (lane == 0) *reinterpret_cast<uint32_t*>(scale_row + head_in_group * p.padded_tokens * 4) = word;
+        } else {
+            st_global8(out + 8 * lane, quant8_by(xa, sa));
+            st_global8(out + 256 + 8 * lane, quant8_by(xb, sb));
+            if ((lane & 15) == 0) {
+                const int k = head_in_group * 4 + (lane >> 4);
+                *reinterpret_cast<float*>(scale_row + k * p.padded_tokens * 4) = sa;
+                *reinterpret_cast<float*>(scale_row + (k + 2) * p.padded_tokens * 4) = sb;
+            }
         }
-        return;
-    }
-    const uint8_t* in = p.o + (static_cast<int64_t>(token) * p.o_stride_token + head * p.o_stride_head) * 2;
-    float xa[8], xb[8];
-    unpack8(ld_stream16(in + 16 * lane), xa);
-    unpack8(ld_stream16(in + 512 + 16 * lane), xb);
-    if (lane >= kFirstRopeLane) {
-        const float* cs = p.cos_sin + p.positions[token] * p.cos_sin_stride + 4 * (lane - kFirstRopeLane);
-        const float4 c4 = ld_readonly_f4(cs), s4 = ld_readonly_f4(cs + 32);
-        const float c[4] = {c4.x, c4.y, c4.z, c4.w}, s[4] = {s4.x, s4.y, s4.z, s4.w};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const float e = xb[2 * j], o = xb[2 * j + 1];
-            // inverse rotation, products rounded separately, then rounded to bf16 as the torch path does
-            const float e2 = __fadd_rn(__fmul_rn(e, c[j]), __fmul_rn(o, s[j]));
-            const float o2 = __fsub_rn(__fmul_rn(o, c[j]), __fmul_rn(e, s[j]));
-            const uint32_t packed = pack_bf16x2(e2, o2);
-            xb[2 * j] = bf16_lo(packed), xb[2 * j + 1] = bf16_hi(packed);
-        }
-    }
-    float ma = 0.0f, mb = 0.0f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) ma = fmaxf(ma, fabsf(xa[i])), mb = fmaxf(mb, fabsf(xb[i]));
-#pragma unroll
-    for (int m = 1; m <= 8; m <<= 1) {
-        ma = fmaxf(ma, __shfl_xor_sync(0xffffffffu, ma, m));
-        mb = fmaxf(mb, __shfl_xor_sync(0xffffffffu, mb, m));
-    }
-    float sa = __fmul_rn(fmaxf(ma, p.eps), 1.0f / 448.0f), sb = __fmul_rn(fmaxf(mb, p.eps), 1.0f / 448.0f);
-    uint8_t* out = p.fp8 + (static_cast<int64_t>(group) * p.num_tokens + token) * (static_cast<int64_t>(p.heads_per_group) * kRowBytes / 2) +
-                   static_cast<int64_t>(head_in_group) * (kRowBytes / 2);
-    uint32_t code_a = 0, code_b = 0;
-    if (PACKED) {
-        code_a = pow2_ceil_code(sa), code_b = pow2_ceil_code(sb);
-        st_global8(out + 8 * lane, quant8_pow2(xa, code_a));
-        st_global8(out + 256 + 8 * lane, quant8_pow2(xb, code_b));
-    } else {
-        st_global8(out + 8 * lane, quant8_by(xa, sa));
-        st_global8(out + 256 + 8 * lane, quant8_by(xb, sb));
-    }
-    if (PACKED) {
-        // chunk k of the head in byte k: groups 0,1 from register A (lanes 0 / 16), 2,3 from B
-        const uint32_t word = (__shfl_sync(0xffffffffu, code_a, 0) & 0xffu) | ((__shfl_sync(0xffffffffu, code_a, 16) & 0xffu) << 8) |
-                              ((__shfl_sync(0xffffffffu, code_b, 0) & 0xffu) << 16) |
-                              ((__shfl_sync(0xffffffffu, code_b, 16) & 0xffu) << 24);
-        if (lane == 0) *reinterpret_cast<uint32_t*>(scale_row + head_in_group * p.padded_tokens * 4) = word;
-    } else if ((lane & 15) == 0) {
-        const int k = head_in_group * 4 + (lane >> 4);
-        *reinterpret_cast<float*>(scale_row + k * p.padded_tokens * 4) = sa;
-        *reinterpret_cast<float*>(scale_row + (k + 2) * p.padded_tokens * 4) = sb;
     }
 }
 
@@ -128,10 +143,10 @@ cudaError_t launch_inv_rope_fp8_quant(const void* o, int64_t o_stride_token, int
                                       const float* cos_sin, int64_t cos_sin_stride, void* fp8, void* scale,
                                       int64_t scale_stride_group, int64_t num_tokens, int64_t padded_tokens, int num_heads,
                                       int heads_per_group, float eps, int packed, cudaStream_t stream) {
-    constexpr int WARPS = 8;
+    constexpr int WARPS = 4, RPW = 2;
     const int64_t rows = padded_tokens * num_heads;
     if (rows == 0) return cudaSuccess;
-    const int64_t grid = (rows + WARPS - 1) / WARPS;
+    const int64_t grid = (rows + WARPS * RPW - 1) / (WARPS * RPW);
     if (grid > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
     InvRopeParams p{};
     p.o = static_cast<const uint8_t*>(o), p.o_stride_token = o_stride_token, p.o_stride_head = o_stride_head;
@@ -142,8 +157,8 @@ cudaError_t launch_inv_rope_fp8_quant(const void* o, int64_t o_stride_token, int
     if (rows >= (1LL << 31)) return cudaErrorInvalidConfiguration;
     make_fast_divisor(static_cast<uint32_t>(num_heads), &p.heads_mul, &p.heads_shift);
     make_fast_divisor(static_cast<uint32_t>(heads_per_group), &p.hpg_mul, &p.hpg_shift);
-    if (packed) inv_rope_fp8_quant_kernel<WARPS, true><<<static_cast<unsigned>(grid), WARPS * 32, 0, stream>>>(p);
-    else inv_rope_fp8_quant_kernel<WARPS, false><<<static_cast<unsigned>(grid), WARPS * 32, 0, stream>>>(p);
+    if (packed) inv_rope_fp8_quant_kernel<WARPS, RPW, true><<<static_cast<unsigned>(grid), WARPS * 32, 0, stream>>>(p);
+    else inv_rope_fp8_quant_kernel<WARPS, RPW, false><<<static_cast<unsigned>(grid), WARPS * 32, 0, stream>>>(p);
     count_launch();
     return cudaGetLastError();
 }
