@@ -19,7 +19,7 @@ struct NormRows {
     int32_t vec_ok;                 // 16-byte path usable for this tensor
 };
 
-constexpr int kMaxChunks = 8;  // 16-byte chunks per lane held in registers: 8 * 32 * 8 = 2048 elements
+constexpr int kMaxChunks = 8;  // at most 8 16-byte chunks per lane are held in registers: 8 * 32 * 8 = 2048 elements
 
 __device__ __forceinline__ float inv_rms_of(float sum, int size, float eps) {
     const float v = __fadd_rn(__fdiv_rn(sum, static_cast<float>(size)), eps);
@@ -27,7 +27,8 @@ __device__ __forceinline__ float inv_rms_of(float sum, int size, float eps) {
     return fmaf(r0, fmaf(-0.5f * v * r0, r0, 0.5f), r0);
 }
 
-template <int WARPS>
+// CH = chunks per lane the launch needs (2, 4, 6 or 8): fewer live registers for the common 1536 / 512 rows.
+template <int WARPS, int CH>
 __global__ void __launch_bounds__(WARPS * 32) q_kv_rmsnorm_kernel(const NormRows q, const NormRows kv, int64_t num_tokens,
                                                                  float eps) {
     const int lane = threadIdx.x & 31;
@@ -41,16 +42,16 @@ __global__ void __launch_bounds__(WARPS * 32) q_kv_rmsnorm_kernel(const NormRows
     const int size = t.size;
     if (t.vec_ok) {
         const int chunks = size >> 3;
-        uint4 x[kMaxChunks];
+        uint4 x[CH];
         float acc = 0.0f;
 #pragma unroll
-        for (int j = 0; j < kMaxChunks; ++j) {
+        for (int j = 0; j < CH; ++j) {
             const int c = lane + 32 * j;
             x[j] = make_uint4(0u, 0u, 0u, 0u);
             if (c < chunks) x[j] = ld_stream16(in + 16 * c);
         }
 #pragma unroll
-        for (int j = 0; j < kMaxChunks; ++j) {
+        for (int j = 0; j < CH; ++j) {
             float f[8];
             unpack8(x[j], f);
 #pragma unroll
@@ -60,7 +61,7 @@ __global__ void __launch_bounds__(WARPS * 32) q_kv_rmsnorm_kernel(const NormRows
         for (int m = 16; m > 0; m >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, m);
         const float rr = inv_rms_of(acc, size, eps);
 #pragma unroll
-        for (int j = 0; j < kMaxChunks; ++j) {
+        for (int j = 0; j < CH; ++j) {
             const int c = lane + 32 * j;
             if (c < chunks) {
                 float f[8], w[8];
@@ -111,7 +112,12 @@ cudaError_t launch_q_kv_rmsnorm(const void* q, void* q_out, const void* q_weight
                vec_ok(kv, kv_out, kv_weight, kv_in_stride, kv_out_stride, kv_size) ? 1 : 0};
     const int64_t grid = (2 * num_tokens + WARPS - 1) / WARPS;
     if (grid > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
-    q_kv_rmsnorm_kernel<WARPS><<<static_cast<unsigned>(grid), WARPS * 32, 0, stream>>>(a, b, num_tokens, eps);
+    const int64_t longest = (a.vec_ok ? q_size : 0) > (b.vec_ok ? kv_size : 0) ? (a.vec_ok ? q_size : 0) : (b.vec_ok ? kv_size : 0);
+    const unsigned g = static_cast<unsigned>(grid);
+    if (longest <= 512) q_kv_rmsnorm_kernel<WARPS, 2><<<g, WARPS * 32, 0, stream>>>(a, b, num_tokens, eps);
+    else if (longest <= 1024) q_kv_rmsnorm_kernel<WARPS, 4><<<g, WARPS * 32, 0, stream>>>(a, b, num_tokens, eps);
+    else if (longest <= 1536) q_kv_rmsnorm_kernel<WARPS, 6><<<g, WARPS * 32, 0, stream>>>(a, b, num_tokens, eps);
+    else q_kv_rmsnorm_kernel<WARPS, 8><<<g, WARPS * 32, 0, stream>>>(a, b, num_tokens, eps);
     count_launch();
     return cudaGetLastError();
 }
