@@ -436,6 +436,7 @@ def main():
                    "l2": "inputs (>= 1 GiB of q per GPU) exceed the 126 MB L2; no flush between steps",
                    "variant": _native.lib().dsv4_get_variant()},
         "hbm_gbs_aggregate": nbytes * args.steps / secs_max / 1e9,
+        "tokens_per_s_sum_of_rank_rates": agg["sum_of_rank_rates"] * args.steps,
         "hbm_frac_of_nominal_8tbs": achieved / NOMINAL_HBM_GBS,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": traffic, "peak_source": f"{peak_kind} copy bandwidth",

@@ -57,6 +57,8 @@ def test_two_ranks_shard_tokens_and_aggregate():
         assert abs(a["seconds"] - 0.002) < 1e-12, "job time is the slowest rank's"
         assert a["bytes"] == sum(x["bytes"] for x in res)
         assert a["largest_tokens"] == max(x["tokens"] for x in res)
+        want = sum(x["tokens"] / (0.001 * (i + 1)) for i, x in enumerate(res))
+        assert abs(a["sum_of_rank_rates"] - want) < 1e-6 * want
 
 
 def test_failure_on_one_rank_is_seen_by_all_and_others_finish():
@@ -71,4 +73,4 @@ def test_single_rank_needs_no_process_group():
 
     a = sharding.aggregate(0.5, 10, 100, 3)
     assert a == {"world": 1, "seconds": 0.5, "tokens": 10, "bytes": 100, "launches": 3, "largest_tokens": 10,
-                 "largest_bytes": 100, "failed": False}
+                 "largest_bytes": 100, "failed": False, "sum_of_rank_rates": 20.0}
