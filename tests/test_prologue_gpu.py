@@ -382,3 +382,35 @@ def test_out_of_place_padded_form(n_heads, padded):
     # identical bits to the in-place operator
     op(q, kv, kc, slots, pos, cs, 1e-6, 16)
     assert torch.equal(out[:, :n_heads].contiguous().view(torch.int16), q.view(torch.int16))
+
+
+@pytest.mark.parametrize("num_tokens,n_heads", [(131072, 128)])
+def test_largest_upstream_size_sampled(variant, num_tokens, n_heads):
+    """The largest size of the upstream combined test (T:531: 131072 tokens x 128 heads, q = 16 GiB, byte offsets
+    beyond 2^32, positions up to 131071, arange slots): tokens sampled from the start, the 4 GiB boundaries and the
+    end are compared with the oracle; every cache row is compared."""
+    g = torch.Generator(device=DEV).manual_seed(2)
+    q = torch.empty(num_tokens, n_heads, 512, dtype=torch.bfloat16, device=DEV)
+    for a in range(0, num_tokens, 8192):
+        q[a : a + 8192].copy_(torch.randn(8192, n_heads, 512, generator=g, device=DEV))
+    kv = torch.randn(num_tokens, 512, generator=g, device=DEV).to(torch.bfloat16)
+    bs = 64
+    k_cache = torch.zeros(num_tokens // bs + 1, bs * 584, dtype=torch.uint8, device=DEV)
+    pos = torch.arange(num_tokens, dtype=torch.int64, device=DEV)
+    slots = torch.arange(num_tokens, dtype=torch.int64, device=DEV)
+    cs = workloads.cos_sin_table(num_tokens, theta=100000.0, device=DEV)
+    per_4gib = (1 << 32) // (n_heads * 1024)
+    sample = torch.unique(torch.cat([torch.arange(0, 8), torch.arange(num_tokens - 8, num_tokens)] +
+                                    [torch.arange(k * per_4gib - 4, k * per_4gib + 4) for k in range(1, num_tokens // per_4gib)] +
+                                    [torch.randint(0, num_tokens, (256,))]))
+    q_in = q[sample.to(DEV)].cpu()
+    w = workloads.Workload("largest", q, kv, k_cache, slots, pos, cs, 1e-6, bs)
+    check_cache_rows_against_compact_oracle(w, run=True)
+    assert _native.device_error() == 0
+    c_oracle.prologue(q_in, torch.empty(sample.numel(), 512, dtype=torch.bfloat16), torch.zeros(1, bs * 584, dtype=torch.uint8),
+                      torch.empty(0, dtype=torch.int64), sample.clone(), cs.cpu(), 1e-6, bs)
+    compare.assert_q_close(q[sample.to(DEV)].cpu(), q_in)
+    # every row of the 16 GiB tensor was normalised: unit RMS everywhere
+    for a in range(0, num_tokens, 8192):
+        rms = q[a : a + 8192].float().pow(2).mean(dim=-1).sqrt()
+        assert float((rms - 1.0).abs().max()) < 5e-3
