@@ -51,6 +51,8 @@ def parse_args():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extra", action="store_true", help="skip the decode / prefill side measurements")
+    ap.add_argument("--siblings-only", action="store_true",
+                    help="time only the sibling operators (used to profile them); prints their JSON and exits")
     return ap.parse_args()
 
 
@@ -378,6 +380,9 @@ def main():
         _native.set_variant(args.variant)
     op = flaggems_vllm.fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert
 
+    if args.siblings_only:
+        print(json.dumps({"sibling_ops": sibling_ops(args.steps, args.warmup)}), flush=True)
+        return
     if world == 1:
         name = args.workload or "long_prefill"
         w = workloads.make(name, device=dev, seed=0)

@@ -241,14 +241,15 @@ __device__ __forceinline__ float row_inv_rms(const float (&xa)[8], const float (
 // ---- UE8M0 quantisation of one 64-element group -----------------------------
 
 // Stored scale byte for a group whose absolute maximum is `amax`:
-// clamp(ceil(log2(max(amax, 1e-4) / 448)) + 127, 0, 255), obtained from the bit pattern of
-// the quotient: its biased exponent, plus one when any mantissa bit is set.  Identical to
-// the log2/ceil statement for every bf16 amax (the quotient of a bf16 by 448 is either an
-// exact power of two or at least 0.4 % away from one).
+// clamp(ceil(log2(max(amax, 1e-4) / 448)) + 127, 0, 255), without the division: 448 = 1.75 * 2^8, so with
+// a = max(amax, 1e-4) = m * 2^(E-127), 1 <= m < 2, the quotient lies in (2^(E-136), 2^(E-135)) for m < 1.75, is
+// exactly 2^(E-135) for m = 1.75 and lies above it for m > 1.75: code = E - 8 + (m > 1.75).  Equal to the
+// reference's log2/ceil statement for every bf16 and fp16 amax (their quotients by 448 are exact powers of two
+// or at least 0.05 % away from one, so the fp32 rounding of the division cannot cross one); a CPU test checks
+// all of them.
 __device__ __forceinline__ uint32_t ue8m0_code(float amax) {
-    const float raw = __fdiv_rn(fmaxf(amax, 1e-4f), 448.0f);
-    const uint32_t u = __float_as_uint(raw);
-    const uint32_t code = ((u >> 23) & 0xffu) + ((u & 0x7fffffu) ? 1u : 0u);
+    const uint32_t u = __float_as_uint(fmaxf(amax, 1e-4f));
+    const uint32_t code = (u >> 23) - 8u + ((u & 0x7fffffu) > 0x600000u ? 1u : 0u);
     return code > 255u ? 255u : code;
 }
 

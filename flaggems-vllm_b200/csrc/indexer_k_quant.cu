@@ -127,14 +127,17 @@ __global__ void __launch_bounds__(WARPS * 32) indexer_k_quant_rows_kernel(const 
         for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(x[i]));
         for (int m = 1; m < group_lanes; m <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
         if (slot[u] < 0) continue;
-        const float s = group_scale(amax, p.ue8m0 != 0);
         const int64_t block = slot[u] / p.block_size, in_block = slot[u] - block * p.block_size;
         uint8_t* blk = p.cache + block * p.block_stride;
+        float s;
         if (p.ue8m0) {
-            const float inv = __uint_as_float((254u - (__float_as_uint(s) >> 23)) << 23);  // exact reciprocal of a power of two
+            const uint32_t code = ue8m0_code(amax);  // 2^ceil(log2(max(amax, 1e-4)/448)) without dividing
+            s = __uint_as_float(code << 23);
+            const float inv = __uint_as_float((254u - code) << 23);  // exact reciprocal of a power of two
 #pragma unroll
             for (int i = 0; i < 8; ++i) x[i] = __fmul_rn(x[i], inv);
         } else {
+            s = group_scale(amax, false);
 #pragma unroll
             for (int i = 0; i < 8; ++i) x[i] = __fdiv_rn(x[i], s);
         }

@@ -111,16 +111,15 @@ static inline int ue8m0_exponent_logpath(float amax) {
 }
 
 /*
- * The same exponent from the bit pattern of `raw` (no log): biased exponent
- * field, plus one when any mantissa bit is set.  This is the derivation the CUDA
- * kernel uses; the tests prove it equal to the log path for every bf16 amax.
+ * The same exponent without log or division, the derivation the CUDA kernels use: 448 = 1.75 * 2^8, so with
+ * max(amax, 1e-4) = m * 2^e (1 <= m < 2) the exponent is e - 8, plus one when m > 1.75.  The tests prove it
+ * equal to the log path for every bf16 and fp16 amax.
  */
 static inline int ue8m0_exponent_bitpath(float amax) {
     float block_max = amax < 1e-4f ? 1e-4f : amax;
-    float raw = block_max / 448.0f;
     uint32_t u;
-    memcpy(&u, &raw, 4);
-    return (int)((u >> 23) & 0xffu) - 127 + ((u & 0x7fffffu) ? 1 : 0);
+    memcpy(&u, &block_max, 4);
+    return (int)(u >> 23) - 127 - 8 + ((u & 0x7fffffu) > 0x600000u ? 1 : 0);
 }
 
 static inline float pow2_from_code(int code) {

@@ -89,17 +89,18 @@ def test_bf16_rounding_matches_torch():
     assert torch.equal(c_oracle.bf16_from_f32(x).view(torch.int16), x.to(torch.bfloat16).view(torch.int16))
 
 
-def test_ue8m0_bit_derivation_equals_log_statement_for_every_bf16():
-    """The CUDA kernel derives the scale byte from the bit pattern of amax/448; the reference
-    states it as ceil(log2(.)).  They agree for all 32768 non-negative bf16 magnitudes, and both
-    agree with torch's log2/ceil."""
-    bits = torch.arange(0, 0x7F80, dtype=torch.int32).to(torch.int16)  # +0 .. largest finite
-    amax = bits.view(torch.bfloat16).float()
-    by_log, by_bits = c_oracle.ue8m0_codes(amax)
-    assert torch.equal(by_log, by_bits)
-    want = (torch.ceil(torch.log2(amax.clamp(min=1e-4) / 448.0)) + 127.0).clamp(0, 255).to(torch.uint8)
-    assert torch.equal(by_log, want)
-    assert int(by_log.min()) >= 105 and int(by_log.max()) <= 247  # never reaches the clamps
+def test_ue8m0_bit_derivation_equals_log_statement_for_every_bf16_and_fp16():
+    """The CUDA kernels derive the scale byte from the exponent and mantissa of max(amax, 1e-4) (448 = 1.75 * 2^8);
+    the reference states it as ceil(log2(. / 448)).  They agree for all non-negative finite bf16 and fp16
+    magnitudes, and both agree with torch's log2/ceil."""
+    bf16 = torch.arange(0, 0x7F80, dtype=torch.int32).to(torch.int16).view(torch.bfloat16).float()
+    fp16 = torch.arange(0, 0x7C00, dtype=torch.int32).to(torch.int16).view(torch.float16).float()
+    for amax in (bf16, fp16):
+        by_log, by_bits = c_oracle.ue8m0_codes(amax)
+        assert torch.equal(by_log, by_bits)
+        want = (torch.ceil(torch.log2(amax.clamp(min=1e-4) / 448.0)) + 127.0).clamp(0, 255).to(torch.uint8)
+        assert torch.equal(by_log, want)
+        assert int(by_log.min()) >= 105 and int(by_log.max()) <= 247  # never reaches the clamps
 
 
 def test_gather_dequant_oracle_inverts_the_insert(golden_case):
