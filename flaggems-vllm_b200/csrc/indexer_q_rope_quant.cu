@@ -145,8 +145,7 @@ __global__ void __launch_bounds__(WARPS * 32) indexer_q_rope_quant_kernel(const 
 // U passes per warp are loaded before any is used.  Needs 16-byte aligned rows and a rotary tail that starts
 // on a multiple of 8 values.
 template <int WARPS, int G, int U, bool FP4>
-__global__ void __launch_bounds__(WARPS * 32) indexer_q_rope_quant_rows_kernel(const IndexerQParams p, const int cs_vec4,
-                                                                             const int dense) {
+__global__ void __launch_bounds__(WARPS * 32) indexer_q_rope_quant_rows_kernel(const IndexerQParams p, const int cs_vec4) {
     constexpr int D = 8 * G, ROWS = 32 / G;
     const int lane = threadIdx.x & 31, sub = lane % G, slot = lane / G;
     const uint32_t total = static_cast<uint32_t>(p.num_tokens) * static_cast<uint32_t>(p.num_heads);
@@ -161,10 +160,8 @@ __global__ void __launch_bounds__(WARPS * 32) indexer_q_rope_quant_rows_kernel(c
         tok[u] = fast_div(live[u] ? row : 0u, p.heads_mul, p.heads_shift);
         raw[u] = make_uint4(0u, 0u, 0u, 0u);
         if (live[u]) {
-            // dense: every tensor is contiguous, so row r of q / out / weights is simply at r * its row size
             const int h = static_cast<int>(row - tok[u] * static_cast<uint32_t>(p.num_heads));
-            raw[u] = ld_stream16(dense ? p.q + (static_cast<uint64_t>(row) * D + 8 * sub) * 2
-                                       : p.q + (static_cast<int64_t>(tok[u]) * p.q_stride0 + h * p.q_stride1 + 8 * sub) * 2);
+            raw[u] = ld_stream16(p.q + (static_cast<int64_t>(tok[u]) * p.q_stride0 + h * p.q_stride1 + 8 * sub) * 2);
         }
     }
     const int first_rot = 8 * sub - (D - p.rot_dim);
@@ -203,8 +200,7 @@ __global__ void __launch_bounds__(WARPS * 32) indexer_q_rope_quant_rows_kernel(c
         float amax = 0.0f;
 #pragma unroll
         for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(x[i]));
-        uint8_t* out = dense ? p.out + static_cast<uint64_t>(row) * (FP4 ? D / 2 : D)
-                             : p.out + static_cast<int64_t>(tok[u]) * p.out_stride0 + h * p.out_stride1;
+        uint8_t* out = p.out + static_cast<int64_t>(tok[u]) * p.out_stride0 + h * p.out_stride1;
         float weight_factor = 1.0f;
         if (FP4) {
 #pragma unroll
@@ -219,8 +215,7 @@ __global__ void __launch_bounds__(WARPS * 32) indexer_q_rope_quant_rows_kernel(c
             if (live[u]) {
                 *reinterpret_cast<uint32_t*>(out + 4 * sub) = bytes;
                 if ((sub & 3) == 0)
-                    p.scales[(dense ? static_cast<int64_t>(row) * (D / 32) : static_cast<int64_t>(tok[u]) * p.scale_stride0 + h * p.scale_stride1) +
-                             (sub >> 2)] = static_cast<uint8_t>(code);
+                    p.scales[static_cast<int64_t>(tok[u]) * p.scale_stride0 + h * p.scale_stride1 + (sub >> 2)] = static_cast<uint8_t>(code);
             }
         } else {
 #pragma unroll
@@ -233,21 +228,19 @@ __global__ void __launch_bounds__(WARPS * 32) indexer_q_rope_quant_rows_kernel(c
             if (live[u]) st_global8(out + 8 * sub, make_uint2(pack_e4m3x4(x[0], x[1], x[2], x[3]), pack_e4m3x4(x[4], x[5], x[6], x[7])));
         }
         if (live[u] && sub == 0) {
-            float w = load_weight(p.weights, dense ? static_cast<int64_t>(row) : static_cast<int64_t>(tok[u]) * p.weights_stride + h,
-                                  p.weights_dtype);
+            float w = load_weight(p.weights, static_cast<int64_t>(tok[u]) * p.weights_stride + h, p.weights_dtype);
             if (!FP4) w = __fmul_rn(w, weight_factor);
-            p.weights_out[dense ? static_cast<int64_t>(row) : static_cast<int64_t>(tok[u]) * p.weights_out_stride + h] =
-                __fmul_rn(__fmul_rn(w, p.softmax_scale), p.head_scale);
+            p.weights_out[static_cast<int64_t>(tok[u]) * p.weights_out_stride + h] = __fmul_rn(__fmul_rn(w, p.softmax_scale), p.head_scale);
         }
     }
 }
 
 template <int G>
-cudaError_t launch_rows(const IndexerQParams& p, bool fp4, int64_t rows, int cs_vec4, int dense, cudaStream_t stream) {
+cudaError_t launch_rows(const IndexerQParams& p, bool fp4, int64_t rows, int cs_vec4, cudaStream_t stream) {
     constexpr int WARPS = 4, U = 2, PER_CTA = WARPS * U * (32 / G);
     const unsigned grid = static_cast<unsigned>((rows + PER_CTA - 1) / PER_CTA);
-    if (fp4) indexer_q_rope_quant_rows_kernel<WARPS, G, U, true><<<grid, WARPS * 32, 0, stream>>>(p, cs_vec4, dense);
-    else indexer_q_rope_quant_rows_kernel<WARPS, G, U, false><<<grid, WARPS * 32, 0, stream>>>(p, cs_vec4, dense);
+    if (fp4) indexer_q_rope_quant_rows_kernel<WARPS, G, U, true><<<grid, WARPS * 32, 0, stream>>>(p, cs_vec4);
+    else indexer_q_rope_quant_rows_kernel<WARPS, G, U, false><<<grid, WARPS * 32, 0, stream>>>(p, cs_vec4);
     return cudaGetLastError();
 }
 
@@ -285,13 +278,9 @@ cudaError_t launch_indexer_q_rope_quant(const int64_t* positions, const void* q,
                             addr(out) % 8 == 0 && out_stride0 % 8 == 0 && out_stride1 % 8 == 0;
     if (rows_shape) {
         const int cs_vec4 = !cos_sin_bf16 && rot_dim > 0 && addr(cos_sin) % 16 == 0 && cos_sin_stride % 4 == 0 && (rot_dim / 2) % 4 == 0;
-        const int64_t out_row = fp4 ? head_dim / 2 : head_dim;
-        const int dense = q_stride1 == head_dim && q_stride0 == static_cast<int64_t>(num_heads) * head_dim && out_stride1 == out_row &&
-                          out_stride0 == num_heads * out_row && weights_stride == num_heads && weights_out_stride == num_heads &&
-                          (!fp4 || (scale_stride1 == head_dim / 32 && scale_stride0 == static_cast<int64_t>(num_heads) * (head_dim / 32)));
-        cudaError_t e = head_dim == 64 ? launch_rows<8>(p, fp4 != 0, rows, cs_vec4, dense, stream)
-                        : head_dim == 128 ? launch_rows<16>(p, fp4 != 0, rows, cs_vec4, dense, stream)
-                        : head_dim == 256 ? launch_rows<32>(p, fp4 != 0, rows, cs_vec4, dense, stream) : cudaErrorInvalidValue;
+        cudaError_t e = head_dim == 64 ? launch_rows<8>(p, fp4 != 0, rows, cs_vec4, stream)
+                        : head_dim == 128 ? launch_rows<16>(p, fp4 != 0, rows, cs_vec4, stream)
+                        : head_dim == 256 ? launch_rows<32>(p, fp4 != 0, rows, cs_vec4, stream) : cudaErrorInvalidValue;
         if (e != cudaErrorInvalidValue) count_launch();
         return e;
     }
