@@ -74,10 +74,13 @@ def test_kernel_reproduces_upstream_reference(name):
     (33, 8, 128, 64, torch.float32, torch.bfloat16), (17, 4, 64, 32, torch.float16, torch.float32),
     (19, 3, 256, 64, torch.bfloat16, torch.float32), (8, 8, 128, 128, torch.bfloat16, torch.float32),
     (8, 8, 128, 0, torch.bfloat16, torch.float32),
+    # 8192 tokens and more take the warp-per-token kernel (even and odd head counts, both table dtypes)
+    (8195, 8, 128, 64, torch.bfloat16, torch.float32), (8192, 7, 128, 64, torch.float32, torch.bfloat16),
+    (9000, 1, 128, 64, torch.float16, torch.float32),
 ])
 def test_kernel_matches_oracle(tokens, heads, head_dim, rot_dim, wdtype, tdtype, use_fp4):
     g = torch.Generator().manual_seed(tokens * 7 + head_dim + rot_dim)
-    q = (torch.randn(tokens, heads, head_dim, generator=g) * torch.logspace(-3, 3, tokens)[:, None, None]).to(torch.bfloat16)
+    q = (torch.randn(tokens, heads, head_dim, generator=g) * torch.logspace(-3, 3, min(tokens, 64)).repeat((tokens + 63) // 64)[:tokens, None, None]).to(torch.bfloat16)
     pos = torch.randint(0, 2048, (tokens,), generator=g, dtype=torch.int64)
     cs = table(2048, rot_dim, tdtype) if rot_dim else torch.zeros(2048, 0, dtype=tdtype)
     w = torch.randn(tokens, heads, generator=g).to(wdtype)
