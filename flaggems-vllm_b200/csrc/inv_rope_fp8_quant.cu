@@ -5,9 +5,7 @@
 // tests/test_fused_inv_rope_fp8_quant.py:150-198, which this kernel follows to the bit: the rotated
 // tail is rounded to bf16 before it is quantised (the torch path does, the Triton kernel does not).
 //
-// One warp per (token, head) row in the A/B layout: the four quantisation groups are lanes 0-15 and
-// 16-31 of each register; the rotary tail is register B of lanes 24-31.  HBM-bound: 1 KiB read,
-// 512 + 16 bytes written per row.
+// HBM traffic: 1 KiB read, 512 + 16 bytes written per (token, head) row.
 #include "dsv4_common.cuh"
 
 namespace dsv4 {
@@ -52,86 +50,105 @@ __device__ __forceinline__ uint2 quant8_pow2(const float (&x)[8], uint32_t code)
 }
 
 // PACKED: power-of-two scales, the 4 UE8M0 bytes of a head packed into one int32.
-// Each warp owns RPW consecutive (token, head) rows: all their loads are issued before the first is used.
-template <int WARPS, int RPW, bool PACKED>
-__global__ void __launch_bounds__(WARPS * 32) inv_rope_fp8_quant_kernel(const InvRopeParams p) {
+// A warp owns kHeadsPerTask consecutive heads of one token and walks them two at a time.  Rows are held in the
+// A/B/T layout (A: 16 B per lane, B: 16 B in lanes 0-23, T: the 4-byte rotary pair 448+2l, 449+2l of lane l), so
+// every lane rotates exactly one pair with a cosine and sine it loaded once for the whole task.  The four
+// quantisation groups of 128 are: A lanes 0-15, A lanes 16-31, B lanes 0-15, and B lanes 16-23 together with T.
+constexpr int kHeadsPerTask = 16;
+
+template <int WARPS, bool PACKED>
+__global__ void __launch_bounds__(WARPS * 32) inv_rope_fp8_quant_kernel(const InvRopeParams p, const uint32_t tasks_per_token,
+                                                                      const uint32_t tpt_mul, const uint32_t tpt_shift) {
     const int lane = threadIdx.x & 31;
-    const uint32_t total = static_cast<uint32_t>(p.padded_tokens) * static_cast<uint32_t>(p.num_heads);
-    const uint32_t row0 = (blockIdx.x * WARPS + (threadIdx.x >> 5)) * RPW;
-    uint4 a[RPW], b[RPW];
-    uint32_t token[RPW];
-    int head[RPW];
-#pragma unroll
-    for (int i = 0; i < RPW; ++i) {
-        const uint32_t row = row0 + i;
-        token[i] = fast_div(row, p.heads_mul, p.heads_shift);
-        head[i] = static_cast<int>(row - token[i] * static_cast<uint32_t>(p.num_heads));
-        a[i] = b[i] = make_uint4(0u, 0u, 0u, 0u);
-        if (row < total && token[i] < p.num_tokens) {
-            const uint8_t* in = p.o + (static_cast<int64_t>(token[i]) * p.o_stride_token + head[i] * p.o_stride_head) * 2;
-            a[i] = ld_stream16(in + 16 * lane);
-            b[i] = ld_stream16(in + 512 + 16 * lane);
-        }
-    }
-#pragma unroll
-    for (int i = 0; i < RPW; ++i) {
-        if (row0 + i >= total) break;
-        const int group = static_cast<int>(fast_div(static_cast<uint32_t>(head[i]), p.hpg_mul, p.hpg_shift));
-        const int head_in_group = head[i] - group * p.heads_per_group;
-        uint8_t* scale_row = p.scale + (group * p.scale_stride_group + token[i]) * 4;
-        if (token[i] >= p.num_tokens) {
-            // rows of the token padding (scale columns are padded to a multiple of 4 tokens): zero scales
+    const uint32_t task = blockIdx.x * WARPS + (threadIdx.x >> 5);
+    if (task >= static_cast<uint32_t>(p.padded_tokens) * tasks_per_token) return;
+    const uint32_t token = fast_div(task, tpt_mul, tpt_shift);
+    const int head_begin = static_cast<int>(task - token * tasks_per_token) * kHeadsPerTask;
+    const int head_end = head_begin + kHeadsPerTask < p.num_heads ? head_begin + kHeadsPerTask : p.num_heads;
+    if (token >= p.num_tokens) {
+        // token padding of the scale storage (a multiple of 4 tokens): zero scales
+        for (int head = head_begin; head < head_end; ++head) {
+            const int group = static_cast<int>(fast_div(static_cast<uint32_t>(head), p.hpg_mul, p.hpg_shift));
+            const int head_in_group = head - group * p.heads_per_group;
+            uint8_t* scale_row = p.scale + (group * p.scale_stride_group + token) * 4;
             if (PACKED) {
                 if (lane == 0) *reinterpret_cast<uint32_t*>(scale_row + head_in_group * p.padded_tokens * 4) = 0u;
             } else if (lane < 4) {
                 *reinterpret_cast<float*>(scale_row + (head_in_group * 4 + lane) * p.padded_tokens * 4) = 0.0f;
             }
-            continue;
         }
-        float xa[8], xb[8];
-        unpack8(a[i], xa);
-        unpack8(b[i], xb);
-        if (lane >= kFirstRopeLane) {
-            const float* cs = p.cos_sin + p.positions[token[i]] * p.cos_sin_stride + 4 * (lane - kFirstRopeLane);
-            const float4 c4 = ld_readonly_f4(cs), s4 = ld_readonly_f4(cs + 32);
-            const float c[4] = {c4.x, c4.y, c4.z, c4.w}, s[4] = {s4.x, s4.y, s4.z, s4.w};
+        return;
+    }
+    const float* cs = p.cos_sin + p.positions[token] * p.cos_sin_stride;
+    const float c = cs[lane], sn = cs[32 + lane];
+    const uint8_t* in_token = p.o + static_cast<int64_t>(token) * p.o_stride_token * 2;
+    constexpr int U = 2;
+    for (int h0 = head_begin; h0 < head_end; h0 += U) {
+        uint4 a[U], b[U];
+        uint32_t tail[U];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const float e = xb[2 * j], o = xb[2 * j + 1];
-                // inverse rotation, products rounded separately, then rounded to bf16 as the torch path does
-                const float e2 = __fadd_rn(__fmul_rn(e, c[j]), __fmul_rn(o, s[j]));
-                const float o2 = __fsub_rn(__fmul_rn(o, c[j]), __fmul_rn(e, s[j]));
-                const uint32_t packed = pack_bf16x2(e2, o2);
-                xb[2 * j] = bf16_lo(packed), xb[2 * j + 1] = bf16_hi(packed);
+        for (int u = 0; u < U; ++u) {
+            a[u] = b[u] = make_uint4(0u, 0u, 0u, 0u);
+            tail[u] = 0u;
+            if (h0 + u < head_end) {
+                const uint8_t* in = in_token + (h0 + u) * p.o_stride_head * 2;
+                a[u] = ld_stream16(in + 16 * lane);
+                if (lane < kFirstRopeLane) b[u] = ld_stream16(in + 512 + 16 * lane);
+                tail[u] = ld_stream4(in + 2 * kNopeDim + 4 * lane);
             }
         }
-        float ma = 0.0f, mb = 0.0f;
 #pragma unroll
-        for (int k = 0; k < 8; ++k) ma = fmaxf(ma, fabsf(xa[k])), mb = fmaxf(mb, fabsf(xb[k]));
+        for (int u = 0; u < U; ++u) {
+            const int head = h0 + u;
+            if (head >= head_end) break;
+            float xa[8], xb[8];
+            unpack8(a[u], xa);
+            unpack8(b[u], xb);
+            // inverse rotation of the lane's pair, products rounded separately, then to bf16 as the torch path does
+            const float e = bf16_lo(tail[u]), o = bf16_hi(tail[u]);
+            const uint32_t rot = pack_bf16x2(__fadd_rn(__fmul_rn(e, c), __fmul_rn(o, sn)), __fsub_rn(__fmul_rn(o, c), __fmul_rn(e, sn)));
+            const float te = bf16_lo(rot), to = bf16_hi(rot);
+            float ma = 0.0f, mb = 0.0f, mt = fmaxf(fabsf(te), fabsf(to));
 #pragma unroll
-        for (int m = 1; m <= 8; m <<= 1) {
-            ma = fmaxf(ma, __shfl_xor_sync(0xffffffffu, ma, m));
-            mb = fmaxf(mb, __shfl_xor_sync(0xffffffffu, mb, m));
-        }
-        const float sa = __fmul_rn(fmaxf(ma, p.eps), 1.0f / 448.0f), sb = __fmul_rn(fmaxf(mb, p.eps), 1.0f / 448.0f);
-        uint8_t* out = p.fp8 + (static_cast<int64_t>(group) * p.num_tokens + token[i]) * (static_cast<int64_t>(p.heads_per_group) * kRowBytes / 2) +
-                       static_cast<int64_t>(head_in_group) * (kRowBytes / 2);
-        if (PACKED) {
-            const uint32_t code_a = pow2_ceil_code(sa), code_b = pow2_ceil_code(sb);
-            st_global8(out + 8 * lane, quant8_pow2(xa, code_a));
-            st_global8(out + 256 + 8 * lane, quant8_pow2(xb, code_b));
-            // chunk k of the head in byte k: groups 0,1 from register A (lanes 0 / 16), 2,3 from B
-            const uint32_t word = (__shfl_sync(0xffffffffu, code_a, 0) & 0xffu) | ((__shfl_sync(0xffffffffu, code_a, 16) & 0xffu) << 8) |
-                                  ((__shfl_sync(0xffffffffu, code_b, 0) & 0xffu) << 16) |
-                                  ((__shfl_sync(0xffffffffu, code_b, 16) & 0xffu) << 24);
-            if (lane == 0) *reinterpret_cast<uint32_t*>(scale_row + head_in_group * p.padded_tokens * 4) = word;
-        } else {
-            st_global8(out + 8 * lane, quant8_by(xa, sa));
-            st_global8(out + 256 + 8 * lane, quant8_by(xb, sb));
-            if ((lane & 15) == 0) {
-                const int k = head_in_group * 4 + (lane >> 4);
-                *reinterpret_cast<float*>(scale_row + k * p.padded_tokens * 4) = sa;
-                *reinterpret_cast<float*>(scale_row + (k + 2) * p.padded_tokens * 4) = sb;
+            for (int k = 0; k < 8; ++k) ma = fmaxf(ma, fabsf(xa[k])), mb = fmaxf(mb, fabsf(xb[k]));
+#pragma unroll
+            for (int m = 1; m <= 8; m <<= 1) {
+                ma = fmaxf(ma, __shfl_xor_sync(0xffffffffu, ma, m));
+                mb = fmaxf(mb, __shfl_xor_sync(0xffffffffu, mb, m));
+                mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, m));
+            }
+            mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, 16));
+            // group 3 = B of lanes 16-23 (mb of the upper half-warp) and all of T
+            const float m3 = fmaxf(mt, __shfl_sync(0xffffffffu, mb, 16));
+            if (lane >= 16) mb = m3;
+            const float sa = __fmul_rn(fmaxf(ma, p.eps), 1.0f / 448.0f), sb = __fmul_rn(fmaxf(mb, p.eps), 1.0f / 448.0f);
+            const float s3 = __fmul_rn(fmaxf(m3, p.eps), 1.0f / 448.0f);
+            const int group = static_cast<int>(fast_div(static_cast<uint32_t>(head), p.hpg_mul, p.hpg_shift));
+            const int head_in_group = head - group * p.heads_per_group;
+            uint8_t* scale_row = p.scale + (group * p.scale_stride_group + token) * 4;
+            uint8_t* out = p.fp8 + (static_cast<int64_t>(group) * p.num_tokens + token) * (static_cast<int64_t>(p.heads_per_group) * kRowBytes / 2) +
+                           static_cast<int64_t>(head_in_group) * (kRowBytes / 2);
+            if (PACKED) {
+                const uint32_t code_a = pow2_ceil_code(sa), code_b = pow2_ceil_code(sb), code_3 = pow2_ceil_code(s3);
+                st_global8(out + 8 * lane, quant8_pow2(xa, code_a));
+                if (lane < kFirstRopeLane) st_global8(out + 256 + 8 * lane, quant8_pow2(xb, code_b));
+                const float inv3 = __uint_as_float((254u - code_3) << 23);
+                *reinterpret_cast<uint16_t*>(out + kNopeDim + 2 * lane) =
+                    static_cast<uint16_t>(pack_e4m3x4(__fmul_rn(te, inv3), __fmul_rn(to, inv3), 0.f, 0.f));
+                // chunk k of the head in byte k: groups 0,1 from register A (lanes 0 / 16), 2 from B lane 0, 3
+                const uint32_t word = (__shfl_sync(0xffffffffu, code_a, 0) & 0xffu) | ((__shfl_sync(0xffffffffu, code_a, 16) & 0xffu) << 8) |
+                                      ((__shfl_sync(0xffffffffu, code_b, 0) & 0xffu) << 16) | ((code_3 & 0xffu) << 24);
+                if (lane == 0) *reinterpret_cast<uint32_t*>(scale_row + head_in_group * p.padded_tokens * 4) = word;
+            } else {
+                st_global8(out + 8 * lane, quant8_by(xa, sa));
+                if (lane < kFirstRopeLane) st_global8(out + 256 + 8 * lane, quant8_by(xb, sb));
+                *reinterpret_cast<uint16_t*>(out + kNopeDim + 2 * lane) =
+                    static_cast<uint16_t>(pack_e4m3x4(__fdiv_rn(te, s3), __fdiv_rn(to, s3), 0.f, 0.f));
+                if ((lane & 15) == 0) {
+                    const int k = head_in_group * 4 + (lane >> 4);
+                    *reinterpret_cast<float*>(scale_row + k * p.padded_tokens * 4) = sa;
+                    *reinterpret_cast<float*>(scale_row + (k + 2) * p.padded_tokens * 4) = sb;  // lane 16: sb is s3
+                }
             }
         }
     }
@@ -143,22 +160,27 @@ cudaError_t launch_inv_rope_fp8_quant(const void* o, int64_t o_stride_token, int
                                       const float* cos_sin, int64_t cos_sin_stride, void* fp8, void* scale,
                                       int64_t scale_stride_group, int64_t num_tokens, int64_t padded_tokens, int num_heads,
                                       int heads_per_group, float eps, int packed, cudaStream_t stream) {
-    constexpr int WARPS = 4, RPW = 2;
+    constexpr int WARPS = 4;
     const int64_t rows = padded_tokens * num_heads;
     if (rows == 0) return cudaSuccess;
-    const int64_t grid = (rows + WARPS * RPW - 1) / (WARPS * RPW);
-    if (grid > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
+    const int64_t tasks_per_token = (num_heads + kHeadsPerTask - 1) / kHeadsPerTask;
+    const int64_t tasks = padded_tokens * tasks_per_token;
+    const int64_t grid = (tasks + WARPS - 1) / WARPS;
+    if (grid > 0x7fffffffLL || tasks >= (1LL << 31)) return cudaErrorInvalidConfiguration;
     InvRopeParams p{};
     p.o = static_cast<const uint8_t*>(o), p.o_stride_token = o_stride_token, p.o_stride_head = o_stride_head;
     p.positions = positions, p.cos_sin = cos_sin, p.cos_sin_stride = cos_sin_stride;
     p.fp8 = static_cast<uint8_t*>(fp8), p.scale = static_cast<uint8_t*>(scale), p.scale_stride_group = scale_stride_group;
     p.num_tokens = num_tokens, p.padded_tokens = padded_tokens, p.num_heads = num_heads, p.heads_per_group = heads_per_group;
     p.eps = eps;
-    if (rows >= (1LL << 31)) return cudaErrorInvalidConfiguration;
     make_fast_divisor(static_cast<uint32_t>(num_heads), &p.heads_mul, &p.heads_shift);
     make_fast_divisor(static_cast<uint32_t>(heads_per_group), &p.hpg_mul, &p.hpg_shift);
-    if (packed) inv_rope_fp8_quant_kernel<WARPS, RPW, true><<<static_cast<unsigned>(grid), WARPS * 32, 0, stream>>>(p);
-    else inv_rope_fp8_quant_kernel<WARPS, RPW, false><<<static_cast<unsigned>(grid), WARPS * 32, 0, stream>>>(p);
+    uint32_t tpt_mul, tpt_shift;
+    make_fast_divisor(static_cast<uint32_t>(tasks_per_token), &tpt_mul, &tpt_shift);
+    const unsigned g = static_cast<unsigned>(grid);
+    const uint32_t tpt = static_cast<uint32_t>(tasks_per_token);
+    if (packed) inv_rope_fp8_quant_kernel<WARPS, true><<<g, WARPS * 32, 0, stream>>>(p, tpt, tpt_mul, tpt_shift);
+    else inv_rope_fp8_quant_kernel<WARPS, false><<<g, WARPS * 32, 0, stream>>>(p, tpt, tpt_mul, tpt_shift);
     count_launch();
     return cudaGetLastError();
 }
