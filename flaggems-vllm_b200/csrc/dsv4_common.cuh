@@ -60,6 +60,25 @@ __device__ __forceinline__ uint32_t fast_div(uint32_t n, uint32_t mul, uint32_t 
     return static_cast<uint32_t>((static_cast<uint64_t>(n) * mul) >> shift);
 }
 
+// slot -> (block, offset in block); block sizes are powers of two in practice (16, 64): shift and mask then,
+// a 64-bit division otherwise.  `shift` < 0 means "not a power of two".
+__device__ __forceinline__ void split_slot(int64_t slot, int64_t block_size, int shift, int64_t* block, int64_t* in_block) {
+    if (shift >= 0) {
+        *block = slot >> shift;
+        *in_block = slot & (block_size - 1);
+    } else {
+        *block = slot / block_size;
+        *in_block = slot - *block * block_size;
+    }
+}
+
+inline int pow2_shift(int64_t v) {
+    if (v <= 0 || (v & (v - 1)) != 0) return -1;
+    int s = 0;
+    while ((1LL << s) < v) ++s;
+    return s;
+}
+
 // mul = ceil(2^shift / d), shift = 31 + ceil(log2 d): exact for every n < 2^31 and 1 <= d < 2^31,
 // because the error d*mul - 2^shift is below d <= 2^(shift-31), so n*error < 2^shift.
 inline void make_fast_divisor(uint32_t d, uint32_t* mul, uint32_t* shift) {

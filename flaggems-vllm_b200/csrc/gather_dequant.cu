@@ -89,6 +89,7 @@ struct GatherParams {
     int64_t offset;
     int32_t nope_dim, rope_dim, scale_slots;
     int32_t index64;          // 1: seq_lens / gather_lens / block_table are int64, 0: int32
+    int32_t bs_shift;         // log2(block_size) or -1
 };
 
 __device__ __forceinline__ int64_t load_index(const void* p, int64_t i, int is64) {
@@ -119,14 +120,15 @@ __global__ void __launch_bounds__(WARPS * 32) gather_dequant_requests_kernel(con
                 const int64_t i = i0 + u * warps_per_req;
                 live[u] = i < gather_len;
                 const int64_t pos = start + (live[u] ? i : i0);
-                block[u] = load_index(g.block_table, req * g.max_blocks_per_seq + pos / g.block_size, g.index64);
+                const int64_t block_in_seq = g.bs_shift >= 0 ? pos >> g.bs_shift : pos / g.block_size;
+                block[u] = load_index(g.block_table, req * g.max_blocks_per_seq + block_in_seq, g.index64);
             }
             uint2 codes[U], qa[U];
             uint4 qb[U];
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 const int64_t pos = start + (live[u] ? i0 + u * warps_per_req : i0);
-                const int64_t in_block = pos % g.block_size;
+                const int64_t in_block = g.bs_shift >= 0 ? pos & (g.block_size - 1) : pos % g.block_size;
                 const uint8_t* base = g.k_cache + block[u] * g.block_stride;
                 data[u] = base + in_block * kTokenDataBytes;
                 scales[u] = base + g.block_size * kTokenDataBytes + in_block * kScaleBytes;
@@ -205,6 +207,7 @@ cudaError_t launch_gather_dequant_requests(uint8_t* out, int64_t out_stride0, in
     g.seq_lens = seq_lens, g.gather_lens = gather_lens, g.block_table = block_table;
     g.max_blocks_per_seq = max_blocks_per_seq, g.block_size = block_size, g.block_stride = block_stride, g.offset = offset;
     g.nope_dim = nope_dim, g.rope_dim = rope_dim, g.scale_slots = scale_slots, g.index64 = index64;
+    g.bs_shift = pow2_shift(block_size);
     // gather lengths live on the device; size the grid from the room the output has per request
     int64_t ctas = (tokens_hint + WARPS - 1) / WARPS;
     if (ctas < 1) ctas = 1;

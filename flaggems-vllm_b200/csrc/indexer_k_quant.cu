@@ -22,6 +22,7 @@ struct IndexerParams {
     int64_t num_tokens, block_size;
     int32_t head_dim, quant_block, num_quant_blocks;
     int32_t ue8m0, vec_ok;
+    int32_t bs_shift;  // log2(block_size) or -1
 };
 
 template <bool FP16>
@@ -127,7 +128,8 @@ __global__ void __launch_bounds__(WARPS * 32) indexer_k_quant_rows_kernel(const 
         for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(x[i]));
         for (int m = 1; m < group_lanes; m <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
         if (slot[u] < 0) continue;
-        const int64_t block = slot[u] / p.block_size, in_block = slot[u] - block * p.block_size;
+        int64_t block, in_block;
+        split_slot(slot[u], p.block_size, p.bs_shift, &block, &in_block);
         uint8_t* blk = p.cache + block * p.block_stride;
         float s;
         if (p.ue8m0) {
@@ -164,6 +166,7 @@ cudaError_t launch_indexer_k_quant(const void* k, int64_t k_stride, int is_fp16,
     IndexerParams p{};
     p.k = static_cast<const uint8_t*>(k), p.k_stride = k_stride, p.cache = static_cast<uint8_t*>(cache);
     p.block_stride = block_stride, p.slot_mapping = slot_mapping, p.num_tokens = num_tokens, p.block_size = block_size;
+    p.bs_shift = pow2_shift(block_size);
     p.head_dim = head_dim, p.quant_block = quant_block, p.num_quant_blocks = head_dim / quant_block, p.ue8m0 = ue8m0;
     const bool pow2 = (quant_block & (quant_block - 1)) == 0;
     const auto addr = [](const void* q) { return reinterpret_cast<uintptr_t>(q); };

@@ -68,7 +68,7 @@ def random_case(seed, batch, max_seq, bs, nope, rope, with_gather=True, extra_ou
 @pytest.mark.parametrize("batch,max_seq,bs,nope,rope,with_gather,offset,pad", [
     (4, 300, 64, 448, 64, True, 0, 0), (5, 1000, 64, 448, 64, False, 0, 0), (3, 200, 16, 448, 64, True, 5, 0),
     (2, 90, 64, 448, 64, True, 0, 8), (3, 77, 4, 64, 16, True, 2, 0), (2, 50, 8, 100, 32, True, 0, 0),
-    (70, 40, 64, 448, 64, True, 0, 0),
+    (70, 40, 64, 448, 64, True, 0, 0), (4, 200, 24, 448, 64, True, 0, 0),  # 24: a block size that is not a power of two
 ])
 def test_kernel_matches_oracle_on_random_caches(batch, max_seq, bs, nope, rope, with_gather, offset, pad):
     seq, gather, table, kc, slots, t_out = random_case(batch * 7 + max_seq, batch, max_seq, bs, nope, rope, with_gather,

@@ -47,7 +47,7 @@ def test_kernel_reproduces_upstream_reference(name):
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("tokens,blocks,bs,hd,qbs,fmt", [
     (1, 2, 16, 128, 128, "ue8m0"), (1000, 40, 64, 128, 128, "ue8m0"), (333, 12, 64, 512, 128, "fp32"),
-    (50, 8, 16, 256, 32, "ue8m0"), (40, 8, 16, 768, 256, "ue8m0"), (30, 4, 16, 96, 48, "ue8m0"), (25, 4, 16, 120, 24, "fp32"),
+    (50, 8, 16, 256, 32, "ue8m0"), (60, 8, 12, 128, 128, "ue8m0"), (40, 8, 16, 768, 256, "ue8m0"), (30, 4, 16, 96, 48, "ue8m0"), (25, 4, 16, 120, 24, "fp32"),
 ])
 def test_kernel_matches_oracle(dtype, tokens, blocks, bs, hd, qbs, fmt):
     """Vector path (power-of-two groups) and scalar path (48, 24), untouched slots included in the comparison."""
