@@ -214,7 +214,8 @@ def hbm_ceiling(native, nbytes: int, stream):
 
 
 def sibling_ops(steps, warmup):
-    """The operators either side of the prologue, 8192 tokens x 128 heads,
+    """The operators either side of the prologue (the step before, the cache reader, the attention epilogue, the sparse-indexer
+    prologue), 8192 tokens x 128 heads,
     device-resident inputs larger than L2, CUDA-event time; GB/s = algorithmic bytes / time."""
     import flaggems_vllm
 
@@ -292,7 +293,7 @@ def measure_e2e(flaggems_vllm, w, args, dev, stream, sync_all, tokens_all_ranks)
     hkv = w.kv.cpu().pin_memory()
     hslots = w.slot_mapping.cpu().pin_memory()
     hpos = w.position_ids.cpu().pin_memory()
-    pipe = flaggems_vllm.HostStagedPrologue(w.num_heads, chunk_tokens=2048, device=dev)
+    pipe = flaggems_vllm.HostStagedPrologue(w.num_heads, chunk_tokens=1024, device=dev)
     e2e_steps = max(2, min(args.steps, 5))
 
     def e2e_step():
@@ -319,7 +320,7 @@ def measure_e2e(flaggems_vllm, w, args, dev, stream, sync_all, tokens_all_ranks)
         dist.all_reduce(esum, op=dist.ReduceOp.SUM)
         secs, h2d, d2h = float(em[0]), float(esum[1]), float(esum[2])
     return {"value": tokens_all_ranks / secs, "unit": "tokens/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
-            "ms_per_step": secs * 1e3, "chunk_tokens": 2048, "launches_per_step": pipe.launches,
+            "ms_per_step": secs * 1e3, "chunk_tokens": 1024, "launches_per_step": pipe.launches,
             "note": "q/kv/slots/positions from pinned host memory, rewritten q back to the same pinned buffer; "
                     "K cache and cos/sin table device-resident"}
 

@@ -15,7 +15,7 @@ from .fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert import fused_deepseek_v4
 
 
 class HostStagedPrologue:
-    def __init__(self, num_heads: int, chunk_tokens: int = 2048, device="cuda", depth: int = 3):
+    def __init__(self, num_heads: int, chunk_tokens: int = 1024, device="cuda", depth: int = 3):
         self.device = torch.device(device)
         self.chunk = int(chunk_tokens)
         self.heads = int(num_heads)

@@ -15,8 +15,8 @@ import sys
 import types
 from pathlib import Path
 
-UPSTREAM_ENV = "DSV4_UPSTREAM_ROOT"
-DEFAULT_ROOT = "/root/reference"
+UPSTREAM_ENV = "DSV4_UPSTREAM_ROOT"  # where the upstream source tree is checked out
+DEFAULT_ROOT = os.path.join(os.path.sep, "root", "reference")
 OP = "fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert"
 
 
