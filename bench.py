@@ -325,6 +325,23 @@ def measure_e2e(flaggems_vllm, w, args, dev, stream, sync_all, tokens_all_ranks)
                     "K cache and cos/sin table device-resident"}
 
 
+def library_kernel_time(w, steps, warmup, stream):
+    """vLLM's own CUDA kernel for this operator (the nine-argument torch.ops._C form of the installed wheel), timed
+    on the same device-resident workload as a same-box comparison; None when the wheel does not provide it."""
+    try:
+        import vllm._custom_ops  # noqa: F401
+
+        kernel = torch.ops._C.fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert
+        fn = lambda: kernel(w.q, w.kv, w.k_cache, w.slot_mapping, w.position_ids, w.cos_sin_cache, w.num_heads, w.eps, 64)  # noqa: E731
+        fn()
+        torch.cuda.synchronize()
+    except Exception as e:
+        return {"unavailable": str(e).splitlines()[0][:120] if str(e) else type(e).__name__}
+    secs = time_steps(fn, steps, warmup, stream, torch.cuda.synchronize)
+    return {"name": "vllm torch.ops._C.fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert (out of place, 9 arguments)",
+            "ms_per_step": secs / steps * 1e3, "note": "allocates and writes a new q tensor instead of rewriting q in place"}
+
+
 def side_measurement(name, steps, warmup, op, native):
     """decode / prefill configurations, reported beside the headline (N=1, rank 0 only).
     The 256-token decode batch fits in L2, so it rotates over enough independent q/kv sets to
@@ -453,6 +470,10 @@ def main():
     if not args.no_cpu_baseline and world == 1:
         line["cpu_baseline"] = cpu_baseline(w)
     if not args.no_extra and world == 1:
+        lib_k = library_kernel_time(w, min(args.steps, 50), 5, stream)
+        if "ms_per_step" in lib_k:
+            lib_k["ours_over_library_speed"] = lib_k["ms_per_step"] / (secs_max / args.steps * 1e3)
+        line["same_box_library_kernel"] = lib_k
         q_bytes = w.q.numel() * 2
         del w
         torch.cuda.empty_cache()

@@ -128,8 +128,8 @@ def cache_stats(k_cache, k_cache_ref, slot_mapping, block_size: int) -> dict:
     """Compare the rows at the valid slots of two caches."""
     slots = valid_slots(slot_mapping)
     if slots.numel() == 0:
-        return {"rows": 0, "fp8_identical_fraction": 1.0, "fp8_max_code_distance": 0,
-                "scale_bytes_equal": True, "pad_zero": True, "rope_max_ulp": 0}
+        return {"rows": 0, "fp8_identical_fraction": 1.0, "fp8_max_code_distance": 0, "scale_bytes_equal": True,
+                "pad_zero": True, "rope_max_ulp": 0, "rope_identical": True, "rope_cancellations": 0}
     d, s = gather_rows(k_cache, slots, block_size)
     dr, sr = gather_rows(k_cache_ref, slots, block_size)
     fp8, fp8r = d[:, :NOPE_DIM], dr[:, :NOPE_DIM]
@@ -137,13 +137,22 @@ def cache_stats(k_cache, k_cache_ref, slot_mapping, block_size: int) -> dict:
     dist = e4m3_code_distance(fp8, fp8r)
     rope = d[:, NOPE_DIM:].contiguous().view(torch.bfloat16)
     roper = dr[:, NOPE_DIM:].contiguous().view(torch.bfloat16)
+    rope_d = bf16_ulp_distance(rope, roper)
+    far = rope_d > 1
+    cancellations = 0
+    if bool(far.any().item()):  # same rule as for q: a cancelled rotation is judged at its pair's magnitude
+        within = (rope.float() - roper.float()).abs() <= _pair_ulp(roper)
+        cancellations = int((far & within).sum().item())
+        rope_d = torch.where(far & within, torch.ones_like(rope_d), rope_d)
     return {
         "rows": int(slots.numel()),
         "fp8_identical_fraction": float(same.float().mean().item()),
         "fp8_max_code_distance": int(dist.max().item()),
         "scale_bytes_equal": bool(torch.equal(s[:, :7], sr[:, :7])),
         "pad_zero": bool((s[:, 7] == 0).all().item()),
-        "rope_max_ulp": int(bf16_ulp_distance(rope, roper).max().item()),
+        "rope_max_ulp": int(rope_d.max().item()),
+        "rope_identical": bool(torch.equal(rope.view(torch.int16), roper.view(torch.int16))),
+        "rope_cancellations": cancellations,
     }
 
 
@@ -157,5 +166,5 @@ def assert_cache_close(k_cache, k_cache_ref, slot_mapping, block_size: int, exac
     assert st["fp8_max_code_distance"] <= 1, "an e4m3 byte is more than 1 ulp off"
     assert st["rope_max_ulp"] <= 1, "cached RoPE bf16 differs by more than 1 ulp"
     if exact:
-        assert st["fp8_identical_fraction"] == 1.0 and st["rope_max_ulp"] == 0, st
+        assert st["fp8_identical_fraction"] == 1.0 and st["rope_identical"], st
     return st

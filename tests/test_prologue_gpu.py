@@ -414,3 +414,39 @@ def test_largest_upstream_size_sampled(variant, num_tokens, n_heads):
     for a in range(0, num_tokens, 8192):
         rms = q[a : a + 8192].float().pow(2).mean(dim=-1).sqrt()
         assert float((rms - 1.0).abs().max()) < 5e-3
+
+
+def _vllm_kernel():
+    """vLLM's own CUDA kernel for this operator, if the installed wheel has it (nine-argument form, returns the
+    padded q); None otherwise.  A library kernel used only as a cross-check, as the upstream test does (T:629-681)."""
+    try:
+        import vllm._custom_ops  # noqa: F401 - registers torch.ops._C
+
+        return torch.ops._C.fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert
+    except Exception:
+        return None
+
+
+@pytest.mark.parametrize("num_tokens", [17, 512, 777, 4096])
+@pytest.mark.parametrize("n_heads", [64, 128])
+@pytest.mark.parametrize("block_size", [16, 64])
+def test_matches_vllm_kernel_if_present(num_tokens, n_heads, block_size):
+    """Cross-check against vLLM's kernel (shapes of T:629-640): e4m3 bytes and scale bytes identical, q and the
+    cached RoPE values within 1 bf16 ulp (that kernel contracts the rotation into FMAs)."""
+    kernel = _vllm_kernel()
+    if kernel is None:
+        pytest.skip("vLLM's _C operator is not available")
+    nb = (num_tokens + block_size - 1) // block_size + 1
+    q, kv, kc, slots, pos, cs = random_case(num_tokens, n_heads, block_size, nb, seed=4, zero_cache=True)
+    kc_ref = kc.clone()
+    try:
+        q_ref = kernel(q.clone(), kv, kc_ref, slots, pos, cs, n_heads, 1e-6, block_size)
+        torch.cuda.synchronize()
+    except Exception as e:  # another signature in another vLLM release
+        pytest.skip("vLLM kernel present but not callable with nine arguments: " + str(e).splitlines()[0])
+    op(q, kv, kc, slots, pos, cs, 1e-6, block_size)
+    torch.cuda.synchronize()
+    compare.assert_q_close(q.cpu(), q_ref.cpu())
+    compare.assert_untouched(kc, kc_ref, slots, block_size)
+    st = compare.assert_cache_close(kc.cpu(), kc_ref.cpu(), slots.cpu(), block_size, exact=False)
+    assert st["fp8_identical_fraction"] == 1.0 and st["scale_bytes_equal"]
