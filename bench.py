@@ -51,6 +51,8 @@ def parse_args():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extra", action="store_true", help="skip the decode / prefill side measurements")
+    ap.add_argument("--upstream-shapes", action="store_true",
+                    help="time the shapes of the reference's own benchmark for this operator; prints JSON and exits")
     ap.add_argument("--siblings-only", action="store_true",
                     help="time only the sibling operators (used to profile them); prints their JSON and exits")
     return ap.parse_args()
@@ -342,6 +344,61 @@ def library_kernel_time(w, steps, warmup, stream):
             "ms_per_step": secs / steps * 1e3, "note": "allocates and writes a new q tensor instead of rewriting q in place"}
 
 
+def upstream_shapes(op, reps: int = 20):
+    """The shapes the reference benchmarks this operator at (benchmark/test_fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert.py:137-163,
+    195-236): N in {1..131072} x H in {64, 128}, block 64, positions = slots = arange, table of max(4096, N) rows.
+    As that harness does (triton do_bench): L2 flushed by writing a 256 MB buffer before every timed call, median of
+    the per-call CUDA-event times.  Its baseline, vLLM's own kernel, is timed the same way where the wheel has it."""
+    from flaggems_vllm.testing.workloads import cos_sin_table
+
+    dev = "cuda"
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    try:
+        import vllm._custom_ops  # noqa: F401
+
+        lib_kernel = torch.ops._C.fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert
+    except Exception:
+        lib_kernel = None
+
+    def median_us(fn):
+        for _ in range(3):
+            fn()
+        times = []
+        for _ in range(reps):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            times.append(a.elapsed_time(b) * 1e3)
+        return statistics.median(times)
+
+    rows = []
+    for n in (1, 4, 17, 64, 1024, 2048, 8192, 32768, 65536, 98304, 131072):
+        for h in (64, 128):
+            q = torch.empty(n, h, 512, dtype=torch.bfloat16, device=dev)
+            for a in range(0, n, 8192):
+                q[a : a + 8192].normal_()
+            kv = torch.randn(n, 512, device=dev).to(torch.bfloat16)
+            pos = torch.arange(n, dtype=torch.int64, device=dev)
+            cs = cos_sin_table(max(4096, n), device=dev)
+            cache = torch.zeros((n + 63) // 64 + 1, 64 * 584, dtype=torch.uint8, device=dev)
+            ours = median_us(lambda: op(q, kv, cache, pos, pos, cs, 1e-6, 64))
+            row = {"num_tokens": n, "num_heads": h, "ours_us": ours, "ours_gbs": (n * (2048 * h + 1880)) / ours / 1e3}
+            if lib_kernel is not None:
+                try:
+                    row["vllm_us"] = median_us(lambda: lib_kernel(q, kv, cache, pos, pos, cs, h, 1e-6, 64))
+                    row["speedup_vs_vllm"] = row["vllm_us"] / ours
+                except Exception as e:
+                    row["vllm_us"] = None
+                    row["vllm_error"] = str(e).splitlines()[0][:80]
+            rows.append(row)
+            del q, kv, cache
+            torch.cuda.empty_cache()
+    return rows
+
+
 def side_measurement(name, steps, warmup, op, native):
     """decode / prefill configurations, reported beside the headline (N=1, rank 0 only).
     The 256-token decode batch fits in L2, so it rotates over enough independent q/kv sets to
@@ -400,6 +457,9 @@ def main():
 
     if args.siblings_only:
         print(json.dumps({"sibling_ops": sibling_ops(args.steps, args.warmup)}), flush=True)
+        return
+    if args.upstream_shapes:
+        print(json.dumps({"upstream_benchmark_shapes": upstream_shapes(op)}), flush=True)
         return
     if world == 1:
         name = args.workload or "long_prefill"
