@@ -4,6 +4,8 @@ Keeps the import surface the reference package offers for this path
 (src/flaggems_vllm/__init__.py:21-46): the operator at package level and under
 `flaggems_vllm.ops`, the compatibility alias, `device`, `vendor_name`, `runtime`.
 """
+import torch
+
 from . import _native, ops, runtime, utils  # noqa: F401
 from .ops import *  # noqa: F401,F403
 from .ops import fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert as _prologue
@@ -14,6 +16,8 @@ vendor_name = runtime.device.vendor_name
 # compatibility alias kept by the reference (src/flaggems_vllm/__init__.py:37-46)
 ops_deepseek_v4_qnorm_rope_kv_rope_quant_insert = _prologue
 ops_inv_rope_fp8_quant = ops.fused_inv_rope_fp8_quant
-SUPPORTED_FP8_DTYPE = ops.fused_inv_rope_fp8_quant.__globals__["SUPPORTED_FP8_DTYPE"]
+
+# the FP8 format every quantising operator here produces (reference: ops/fused_inv_rope_fp8_quant.py:25-28)
+SUPPORTED_FP8_DTYPE = torch.float8_e4m3fn
 
 __version__ = "0.1.0"
