@@ -33,10 +33,24 @@ __device__ __forceinline__ uint32_t pow2_ceil_code(float s) {
     return ((u >> 23) & 0xffu) + ((u & 0x7fffffu) ? 1u : 0u);
 }
 
+// x / scale for a scale that is not a power of two.  FAST: y = RN(1/scale) once, then per value q0 = x*y,
+// r = fma(-scale, q0, x), q = fma(r, y, q0) - three instructions instead of an IEEE division.  q can differ from
+// RN(x/scale) in the last fp32 bit, but never in the e4m3 byte: a CPU test enumerates every bf16 group maximum
+// (hence every reachable scale, for the reference's eps = 1e-10) against every bf16 value below it - 5.3e8 pairs,
+// zero differing bytes.  For any other eps the kernel divides.
+template <bool FAST>
+__device__ __forceinline__ float div_by_scale(float x, float scale, float recip) {
+    if (!FAST) return __fdiv_rn(x, scale);
+    const float q0 = __fmul_rn(x, recip);
+    return fmaf(fmaf(-scale, q0, x), recip, q0);
+}
+
+template <bool FAST>
 __device__ __forceinline__ uint2 quant8_by(const float (&x)[8], float scale) {
+    const float recip = FAST ? __frcp_rn(scale) : 0.0f;
     float q[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) q[i] = __fdiv_rn(x[i], scale);  // the e4m3 conversion saturates at +-448
+    for (int i = 0; i < 8; ++i) q[i] = div_by_scale<FAST>(x[i], scale, recip);  // the e4m3 conversion saturates at +-448
     return make_uint2(pack_e4m3x4(q[0], q[1], q[2], q[3]), pack_e4m3x4(q[4], q[5], q[6], q[7]));
 }
 
@@ -56,7 +70,8 @@ __device__ __forceinline__ uint2 quant8_pow2(const float (&x)[8], uint32_t code)
 // quantisation groups of 128 are: A lanes 0-15, A lanes 16-31, B lanes 0-15, and B lanes 16-23 together with T.
 constexpr int kHeadsPerTask = 16;
 
-template <int WARPS, bool PACKED>
+// FASTDIV (fp32-scale mode only): see div_by_scale.
+template <int WARPS, bool PACKED, bool FASTDIV>
 __global__ void __launch_bounds__(WARPS * 32) inv_rope_fp8_quant_kernel(const InvRopeParams p, const uint32_t tasks_per_token,
                                                                       const uint32_t tpt_mul, const uint32_t tpt_shift) {
     const int lane = threadIdx.x & 31;
@@ -140,10 +155,11 @@ __global__ void __launch_bounds__(WARPS * 32) inv_rope_fp8_quant_kernel(const In
                                       ((__shfl_sync(0xffffffffu, code_b, 0) & 0xffu) << 16) | ((code_3 & 0xffu) << 24);
                 if (lane == 0) *reinterpret_cast<uint32_t*>(scale_row + head_in_group * p.padded_tokens * 4) = word;
             } else {
-                st_global8(out + 8 * lane, quant8_by(xa, sa));
-                if (lane < kFirstRopeLane) st_global8(out + 256 + 8 * lane, quant8_by(xb, sb));
-                *reinterpret_cast<uint16_t*>(out + kNopeDim + 2 * lane) =
-                    static_cast<uint16_t>(pack_e4m3x4(__fdiv_rn(te, s3), __fdiv_rn(to, s3), 0.f, 0.f));
+                st_global8(out + 8 * lane, quant8_by<FASTDIV>(xa, sa));
+                if (lane < kFirstRopeLane) st_global8(out + 256 + 8 * lane, quant8_by<FASTDIV>(xb, sb));
+                const float r3 = FASTDIV ? __frcp_rn(s3) : 0.0f;
+                *reinterpret_cast<uint16_t*>(out + kNopeDim + 2 * lane) = static_cast<uint16_t>(
+                    pack_e4m3x4(div_by_scale<FASTDIV>(te, s3, r3), div_by_scale<FASTDIV>(to, s3, r3), 0.f, 0.f));
                 if ((lane & 15) == 0) {
                     const int k = head_in_group * 4 + (lane >> 4);
                     *reinterpret_cast<float*>(scale_row + k * p.padded_tokens * 4) = sa;
@@ -179,8 +195,9 @@ cudaError_t launch_inv_rope_fp8_quant(const void* o, int64_t o_stride_token, int
     make_fast_divisor(static_cast<uint32_t>(tasks_per_token), &tpt_mul, &tpt_shift);
     const unsigned g = static_cast<unsigned>(grid);
     const uint32_t tpt = static_cast<uint32_t>(tasks_per_token);
-    if (packed) inv_rope_fp8_quant_kernel<WARPS, true><<<g, WARPS * 32, 0, stream>>>(p, tpt, tpt_mul, tpt_shift);
-    else inv_rope_fp8_quant_kernel<WARPS, false><<<g, WARPS * 32, 0, stream>>>(p, tpt, tpt_mul, tpt_shift);
+    if (packed) inv_rope_fp8_quant_kernel<WARPS, true, false><<<g, WARPS * 32, 0, stream>>>(p, tpt, tpt_mul, tpt_shift);
+    else if (eps == 1e-10f) inv_rope_fp8_quant_kernel<WARPS, false, true><<<g, WARPS * 32, 0, stream>>>(p, tpt, tpt_mul, tpt_shift);
+    else inv_rope_fp8_quant_kernel<WARPS, false, false><<<g, WARPS * 32, 0, stream>>>(p, tpt, tpt_mul, tpt_shift);
     count_launch();
     return cudaGetLastError();
 }

@@ -50,6 +50,8 @@ def lib() -> ctypes.CDLL:
         L.dsv4_oracle_indexer_k_quant.restype = i32
         L.dsv4_oracle_indexer_q_rope_quant.argtypes = [vp, vp, vp, i64, vp, f32, f32, i64, i64, i64, i32, vp, vp, vp]
         L.dsv4_oracle_indexer_q_rope_quant.restype = i32
+        L.dsv4_oracle_check_division_shortcut.argtypes = [f32, vp, vp]
+        L.dsv4_oracle_check_division_shortcut.restype = i64
         L.dsv4_oracle_version.restype = ctypes.c_char_p
         _lib = L
     return _lib
@@ -159,6 +161,13 @@ def indexer_q_rope_quant(positions, index_q, cos_sin_cache, weights, softmax_sca
     if rc != 0:
         raise ValueError("dsv4_oracle_indexer_q_rope_quant rejected its arguments")
     return out, scales, w_out
+
+
+def check_division_shortcut(eps: float = 1e-10):
+    """(pairs examined, e4m3 byte mismatches, fp32 value mismatches) of the reciprocal-and-correct division."""
+    b, v = ctypes.c_int64(0), ctypes.c_int64(0)
+    n = lib().dsv4_oracle_check_division_shortcut(float(eps), ctypes.byref(b), ctypes.byref(v))
+    return int(n), int(b.value), int(v.value)
 
 
 def e4m3_from_f32(x: torch.Tensor) -> torch.Tensor:

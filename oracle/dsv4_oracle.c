@@ -524,4 +524,40 @@ int dsv4_oracle_indexer_q_rope_quant(const int64_t* positions, const uint16_t* q
     return 0;
 }
 
+/*
+ * Exhaustive check of the division shortcut the CUDA epilogue kernel uses when its scales are not powers of
+ * two: y = RN(1/s) once per group, then per value q0 = RN(x*y), r = fma(-s, q0, x), q = fma(r, y, q0).
+ * For every non-negative finite bf16 amax, s = RN(max(amax, eps) * RN(1/448)), and every bf16 x with
+ * 0 <= x <= amax, counts the pairs whose e4m3 byte differs from that of the IEEE quotient RN(x/s)
+ * (`byte_mismatches`) and, for information, those whose fp32 value differs (`value_mismatches`).
+ * Negative x behave symmetrically.  Returns the number of pairs examined.
+ */
+__attribute__((target("fma"))) static inline float fma_hw(float a, float b, float c) { return __builtin_fmaf(a, b, c); }
+
+int64_t dsv4_oracle_check_division_shortcut(float eps, int64_t* byte_mismatches, int64_t* value_mismatches) {
+    int64_t pairs = 0, bytes = 0, values = 0;
+    const float inv448 = (float)(1.0 / 448.0);
+    const int have_fma = __builtin_cpu_supports("fma");
+#pragma omp parallel for schedule(dynamic, 64) reduction(+ : pairs, bytes, values)
+    for (int32_t ia = 0; ia < 0x7f80; ++ia) {
+        float amax = bf16_bits_to_f32((uint16_t)ia);
+        float s = (amax < eps ? eps : amax) * inv448;
+        float y = 1.0f / s;
+        for (int32_t ix = 0; ix <= ia; ++ix) {
+            float x = bf16_bits_to_f32((uint16_t)ix);
+            float q0 = x * y;
+            float r = have_fma ? fma_hw(-s, q0, x) : fmaf(-s, q0, x);
+            float q = have_fma ? fma_hw(r, y, q0) : fmaf(r, y, q0);
+            float want = x / s;
+            pairs++;
+            if (q != want) values++;
+            float qc = q > 448.0f ? 448.0f : q, wc = want > 448.0f ? 448.0f : want;
+            if (f32_to_e4m3_bits(qc) != f32_to_e4m3_bits(wc)) bytes++;
+        }
+    }
+    *byte_mismatches = bytes;
+    *value_mismatches = values;
+    return pairs;
+}
+
 const char* dsv4_oracle_version(void) { return "dsv4-oracle 1"; }

@@ -40,6 +40,13 @@ def test_pow2_scale_bit_derivation_equals_log_statement_for_every_bf16_amax():
     assert torch.equal(got, want)
 
 
+def test_division_shortcut_never_changes_a_byte():
+    """fp32-scale mode divides with a reciprocal and one correction (three instructions) instead of an IEEE
+    division.  Every reachable (scale, value) pair for bf16 inputs and the reference's eps: no e4m3 byte differs."""
+    pairs, byte_mismatches, _ = c_oracle.check_division_shortcut(1e-10)
+    assert pairs > 5e8 and byte_mismatches == 0
+
+
 @pytest.mark.parametrize("packed", [False, True])
 @pytest.mark.parametrize("name", NAMES)
 def test_oracle_reproduces_upstream_reference(name, packed):
@@ -119,6 +126,21 @@ def test_inverse_of_the_prologue_rotation():
     normed = q0.float() * torch.rsqrt(q0.float().pow(2).mean(-1, keepdim=True) + 1e-6)
     err = (deq.view(32, 8, 512)[..., 448:] - normed[..., 448:]).abs()
     assert float(err.max()) < 0.3 and float(err.mean()) < 0.03  # e4m3 step at |x| ~ 4 is 0.25
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("eps", [1e-10, 1e-4])
+def test_fp32_scale_mode_with_and_without_the_division_shortcut(eps):
+    """eps = 1e-10 takes the shortcut, any other eps the IEEE division; both must equal the oracle, on values of
+    widely different magnitude (tiny groups hit the eps clamp)."""
+    g = torch.Generator().manual_seed(77)
+    o = (torch.randn(257, 16, 512, generator=g) * torch.logspace(-8, 4, 257)[:, None, None]).to(torch.bfloat16)
+    pos = torch.randint(0, 4096, (257,), generator=g)
+    cs = workloads.cos_sin_table(4096)
+    fp8, scale = flaggems_vllm.fused_inv_rope_fp8_quant(o.to(DEV), pos.to(DEV), cs.to(DEV), 2, 8, eps=eps)
+    want_fp8, want_scale = c_oracle.inv_rope_fp8_quant(o, pos, cs, 2, 8, eps=eps)
+    assert torch.equal(fp8.cpu().view(torch.uint8), want_fp8)
+    assert torch.equal(scale.cpu().contiguous().view(torch.int32), want_scale.view(torch.int32))
 
 
 def test_host_checks_without_gpu():
