@@ -4,7 +4,7 @@
 //   y = (x * rsqrt(mean(x^2) + eps)) * w, fp32 arithmetic, bf16 in and out.
 // One warp per row; a row of up to 2048 elements stays in registers between the reduction and
 // the scaling (one read, one write per element); longer or unaligned rows take a two-pass
-// scalar path.  Rows [0, N) are q rows, rows [N, 2N) are kv rows.
+// scalar path.  Row 2t is the q row of token t, row 2t+1 its kv row.
 #include "dsv4_common.cuh"
 
 namespace dsv4 {
@@ -29,14 +29,14 @@ __device__ __forceinline__ float inv_rms_of(float sum, int size, float eps) {
 
 // CH = chunks per lane the launch needs (2, 4, 6 or 8): fewer live registers for the common 1536 / 512 rows.
 template <int WARPS, int CH>
-__global__ void __launch_bounds__(WARPS * 32) q_kv_rmsnorm_kernel(const NormRows q, const NormRows kv, int64_t num_tokens,
+__global__ void __launch_bounds__(WARPS * 32, CH <= 2 ? 16 : (CH <= 6 ? 8 : 6)) q_kv_rmsnorm_kernel(const NormRows q, const NormRows kv, int64_t num_tokens,
                                                                  float eps) {
     const int lane = threadIdx.x & 31;
     const int64_t r = static_cast<int64_t>(blockIdx.x) * WARPS + (threadIdx.x >> 5);
     if (r >= 2 * num_tokens) return;
-    const bool is_q = r < num_tokens;
+    const bool is_q = (r & 1) == 0;  // rows alternate q, kv, q, kv ... so long and short rows mix in every CTA
     const NormRows& t = is_q ? q : kv;
-    const int64_t token = is_q ? r : r - num_tokens;
+    const int64_t token = r >> 1;
     const uint8_t* in = t.in + token * t.in_stride * 2;
     uint8_t* out = t.out + token * t.out_stride * 2;
     const int size = t.size;
