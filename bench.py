@@ -426,8 +426,24 @@ def side_measurement(name, steps, warmup, op, native):
     stream = torch.cuda.current_stream()
     secs = time_steps(fn, steps, warmup, stream, torch.cuda.synchronize)
     nbytes = w.algorithmic_bytes()
-    return {"tokens": w.num_tokens, "us_per_launch": secs / steps * 1e6, "tokens_per_s": w.num_tokens * steps / secs,
-            "hbm_gbs": nbytes * steps / secs / 1e9, "rotating_sets": sets}
+    out = {"tokens": w.num_tokens, "us_per_launch": secs / steps * 1e6, "tokens_per_s": w.num_tokens * steps / secs,
+           "hbm_gbs": nbytes * steps / secs / 1e9, "rotating_sets": sets}
+    if sets > 1:
+        # launches this short are bounded by the Python call, not by the GPU: the same rotation captured once in a
+        # CUDA graph (how serving runs decode steps) and replayed gives the device-side time per launch
+        side = torch.cuda.Stream()
+        side.wait_stream(stream)
+        with torch.cuda.stream(side):
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                for _ in range(sets):
+                    fn()
+        stream.wait_stream(side)
+        replays = max(2, steps // sets)
+        gsecs = time_steps(graph.replay, replays, 2, stream, torch.cuda.synchronize)
+        out["us_per_launch_cuda_graph"] = gsecs / (replays * sets) * 1e6
+        out["hbm_gbs_cuda_graph"] = nbytes * replays * sets / gsecs / 1e9
+    return out
 
 
 def main():

@@ -71,16 +71,22 @@ def fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert(
     if num_tokens == 0:
         return
 
-    lib = _native.lib()
-    with torch.cuda.device(dev):
-        stream = torch.cuda.current_stream(dev).cuda_stream
-        _native.check(
-            lib.dsv4_qnorm_rope_kv_insert(
-                q.data_ptr(), kv.data_ptr(), k_cache.data_ptr(), slot_mapping.data_ptr(), position_ids.data_ptr(),
-                cos_sin_cache.data_ptr(), float(eps), num_tokens, num_heads, num_tokens_insert,
-                int(cache_block_size), k_cache.stride(0), stream,
-            )
+    def launch():
+        code = _native.lib().dsv4_qnorm_rope_kv_insert(
+            q.data_ptr(), kv.data_ptr(), k_cache.data_ptr(), slot_mapping.data_ptr(), position_ids.data_ptr(),
+            cos_sin_cache.data_ptr(), float(eps), num_tokens, num_heads, num_tokens_insert,
+            int(cache_block_size), k_cache.stride(0), torch.cuda.current_stream(dev).cuda_stream,
         )
+        if code != 0:
+            _native.check(code)
+
+    # the library launches on the current device: switch only when q lives elsewhere (the guard costs
+    # several microseconds, which matters for decode-sized calls outside CUDA graphs)
+    if dev.index is None or dev.index == torch.cuda.current_device():
+        launch()
+    else:
+        with torch.cuda.device(dev):
+            launch()
 
 
 def fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert_padded(
