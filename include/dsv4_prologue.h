@@ -84,7 +84,8 @@ int dsv4_qnorm_rope_kv_insert_padded(const void* q, void* q_out, const void* kv,
  * position is outside [0, max_pos) or whose slot is >= num_blocks*cache_block_size is
  * left unprocessed and a bit is OR-ed into *status (device int32, caller-zeroed):
  * bit 0 = bad position, bit 1 = bad slot.  Used by the test-suite in place of a
- * memory checker.  Always the DSV4_VARIANT_ROWS kernel.
+ * memory checker.  Always the DSV4_VARIANT_ROWS kernel.  No counterpart in the reference
+ * (its kernel trusts its indices).
  */
 int dsv4_qnorm_rope_kv_insert_checked(void* q, const void* kv, void* k_cache, const int64_t* slot_mapping,
                                       const int64_t* position_ids, const float* cos_sin_cache, float eps,
@@ -213,11 +214,13 @@ int dsv4_hbm_probe(int mode, void* buffer, int64_t rows, void* cuda_stream);
 /*
  * Reads into *value_host, and clears, the error word the kernels of the current device keep:
  * bit 0 = a bounded wait inside the DSV4_VARIANT_BULK kernel ran out (its result is then
- * incomplete).  Synchronises the device.  0 after every healthy run.
+ * incomplete).  Synchronises the device.  0 after every healthy run.  No counterpart in the reference.
  */
 int dsv4_device_error(int32_t* value_host);
 
-/* Process-wide kernel variant (DSV4_VARIANT_*); also read once from the environment
+/* The remaining entry points are housekeeping of this library and have no counterpart in the reference.
+ *
+ * Process-wide kernel variant (DSV4_VARIANT_*); also read once from the environment
  * variable DSV4_VARIANT.  Returns the previous value or DSV4_ERR_BAD_VARIANT. */
 int dsv4_set_variant(int variant);
 int dsv4_get_variant(void);
