@@ -156,9 +156,20 @@ def cpu_baseline(workload, budget_s: float = 12.0):
         torch_path.prologue(qq, kv, cache, compact, pos, cs, workload.eps, 64)
         best = min(best, time.perf_counter() - t)
         runs += 1
-    return {"value": n / best, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
-            "sample": f"first {n} tokens x {workload.num_heads} heads of the workload, torch CPU path, best of {runs} runs",
-            "ms_per_sample": best * 1e3}
+    out = {"value": n / best, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
+           "sample": f"first {n} tokens x {workload.num_heads} heads of the workload, torch CPU path, best of {runs} runs",
+           "ms_per_sample": best * 1e3}
+    # for scale: the plain-C oracle (OpenMP over tokens) on the same sample
+    from oracle import c_oracle
+
+    c_best = float("inf")
+    for _ in range(5):
+        qq = q.clone()
+        t = time.perf_counter()
+        c_oracle.prologue(qq, kv, cache, compact, pos, cs, workload.eps, 64, threads=threads)
+        c_best = min(c_best, time.perf_counter() - t)
+    out["c_oracle_tokens_per_s"] = n / c_best
+    return out
 
 
 def run_reference(args, rank, world):
