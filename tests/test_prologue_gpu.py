@@ -450,3 +450,18 @@ def test_matches_vllm_kernel_if_present(num_tokens, n_heads, block_size):
     compare.assert_untouched(kc, kc_ref, slots, block_size)
     st = compare.assert_cache_close(kc.cpu(), kc_ref.cpu(), slots.cpu(), block_size, exact=False)
     assert st["fp8_identical_fraction"] == 1.0 and st["scale_bytes_equal"]
+
+
+@pytest.mark.parametrize("seed", range(24))
+def test_random_shapes(variant, seed):
+    """Seeded random geometry: token and head counts, block size (1..128, not only powers of two), block pitch,
+    slot_mapping length, share of -1 slots."""
+    g = torch.Generator().manual_seed(1000 + seed)
+    r = lambda lo, hi: int(torch.randint(lo, hi + 1, (1,), generator=g))  # noqa: E731
+    n, h = r(1, 300), r(0, 40)
+    bs = [1, 2, 3, 16, 24, 64, 128][r(0, 6)]
+    nb = (n + bs - 1) // bs + r(1, 3)
+    n_ins = r(0, n)
+    pad = [0, 0, 16, 8, 1][r(0, 4)]
+    q, kv, kc, slots, pos, cs = random_case(n, h, bs, nb, seed=2000 + seed, n_insert=n_ins, minus_one=n_ins // 5, stride_pad=pad)
+    run_and_check(q, kv, kc, slots, pos, cs, 1e-6 if seed % 2 else 1e-5, bs)
