@@ -4,6 +4,8 @@ Keeps the import surface the reference package offers for this path
 (src/flaggems_vllm/__init__.py:21-46): the operator at package level and under
 `flaggems_vllm.ops`, the compatibility alias, `device`, `vendor_name`, `runtime`.
 """
+import contextlib
+
 import torch
 
 from . import _native, ops, runtime, utils  # noqa: F401
@@ -19,5 +21,15 @@ ops_inv_rope_fp8_quant = ops.fused_inv_rope_fp8_quant
 
 # the FP8 format every quantising operator here produces (reference: ops/fused_inv_rope_fp8_quant.py:25-28)
 SUPPORTED_FP8_DTYPE = torch.float8_e4m3fn
+
+
+
+@contextlib.contextmanager
+def use_gems(*_args, **_kwargs):
+    """Kept for callers that wrap operator calls in `with flaggems_vllm.use_gems():` (the reference registers aten
+    overrides inside it, src/flaggems_vllm/__init__.py:150-214).  This package registers nothing: its operators are
+    the functions themselves, so the context changes nothing."""
+    yield
+
 
 __version__ = "0.1.0"

@@ -25,6 +25,18 @@ def test_import_surface():
     from flaggems_vllm.utils.device_info import get_device_capability  # noqa: F401
 
 
+def test_compat_helpers():
+    import flaggems_vllm.testing as fg_testing
+
+    a = torch.tensor([1.0, 2.0], dtype=torch.bfloat16)
+    fg_testing.assert_close(a, a.float() * 1.005, dtype=torch.bfloat16)
+    with pytest.raises(AssertionError):
+        fg_testing.assert_close(a, a.float() * 1.1, dtype=torch.bfloat16)
+    fg_testing.assert_equal(a, a.clone())
+    with flaggems_vllm.use_gems():
+        assert flaggems_vllm.SUPPORTED_FP8_DTYPE == torch.float8_e4m3fn
+
+
 def test_signature_is_the_reference_one():
     names = list(inspect.signature(op).parameters)
     assert names == ["q", "kv", "k_cache", "slot_mapping", "position_ids", "cos_sin_cache", "eps", "cache_block_size"]
