@@ -285,10 +285,14 @@ def sibling_ops(steps, warmup):
     nk = 1 << 20
     ik = torch.randn(nk, 128, generator=g, device=dev).to(torch.bfloat16)
     icache = torch.zeros(nk // 64, 64, 132, device=dev, dtype=torch.uint8)
-    islots = torch.randperm(nk, generator=g, device=dev).to(torch.int64)
-    secs = time_steps(lambda: flaggems_vllm.indexer_k_quant_and_cache(ik, icache, islots, 128, "ue8m0"), steps, warmup, stream,
-                      torch.cuda.synchronize)
-    out["indexer_k_quant_and_cache"] = {"tokens": nk, "us_per_launch": secs / steps * 1e6, "hbm_gbs": nk * (256 + 132 + 8) * steps / secs / 1e9}
+    # slots as a prefill produces them (tokens fill randomly chosen blocks in order) and fully random slots
+    table = torch.randperm(nk // 64, generator=g, device=dev).to(torch.int64)
+    order = torch.arange(nk, device=dev, dtype=torch.int64)
+    for key, islots in (("indexer_k_quant_and_cache[block-contiguous slots]", (table[order // 64] * 64 + order % 64).contiguous()),
+                        ("indexer_k_quant_and_cache[random slots]", torch.randperm(nk, generator=g, device=dev).to(torch.int64))):
+        secs = time_steps(lambda: flaggems_vllm.indexer_k_quant_and_cache(ik, icache, islots, 128, "ue8m0"), steps, warmup, stream,
+                          torch.cuda.synchronize)
+        out[key] = {"tokens": nk, "us_per_launch": secs / steps * 1e6, "hbm_gbs": nk * (256 + 132 + 8) * steps / secs / 1e9}
     return out
 
 

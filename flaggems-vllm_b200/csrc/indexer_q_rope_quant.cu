@@ -245,55 +245,64 @@ cudaError_t launch_rows(const IndexerQParams& p, bool fp4, int64_t rows, int cs_
 }
 
 // Large batches of the DeepSeek-V4 geometry (head_dim 128 = 64 un-rotated + 64 rotary): one warp per TOKEN.
-// A head is 16 lanes; lane s keeps un-rotated values [4s, 4s+4) and rotary values [64+4s, 64+4s+4) (two pairs), so
-// every lane rotates (no divergence), the lane's two cosines and sines are loaded once per token and reused for
-// every head, and pointers advance by constants from head pair to head pair.  MXFP4 blocks of 32 are 8 lanes.
+// A head is 8 lanes; lane s keeps un-rotated values [8s, 8s+8) and rotary values [64+8s, 64+8s+8) (four pairs), so
+// every lane rotates (no divergence), the lane's four cosines and sines are loaded once per token and reused for
+// every head, and pointers advance by constants from one group of four heads to the next.  MXFP4 blocks of 32 are
+// 4 lanes.
 template <int WARPS, bool FP4>
 __global__ void __launch_bounds__(WARPS * 32) indexer_q_rope_quant_token_kernel(const IndexerQParams p) {
-    const int lane = threadIdx.x & 31, sub = lane & 15, which = lane >> 4;
+    const int lane = threadIdx.x & 31, sub = lane & 7, which = lane >> 3;
     const int64_t t = static_cast<int64_t>(blockIdx.x) * WARPS + (threadIdx.x >> 5);
     if (t >= p.num_tokens) return;
     const int64_t pos = p.positions[t];
-    float c0, c1, s0, s1;
+    float c[4], sn[4];
     if (p.cos_sin_bf16) {
-        const uint16_t* cs = reinterpret_cast<const uint16_t*>(p.cos_sin) + pos * p.cos_sin_stride + 2 * sub;
-        c0 = bf16_lo(cs[0]), c1 = bf16_lo(cs[1]), s0 = bf16_lo(cs[32]), s1 = bf16_lo(cs[33]);
+        const uint16_t* cs = reinterpret_cast<const uint16_t*>(p.cos_sin) + pos * p.cos_sin_stride + 4 * sub;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) c[j] = bf16_lo(cs[j]), sn[j] = bf16_lo(cs[32 + j]);
     } else {
-        const float* cs = reinterpret_cast<const float*>(p.cos_sin) + pos * p.cos_sin_stride + 2 * sub;
-        c0 = cs[0], c1 = cs[1], s0 = cs[32], s1 = cs[33];
+        const float* cs = reinterpret_cast<const float*>(p.cos_sin) + pos * p.cos_sin_stride + 4 * sub;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) c[j] = cs[j], sn[j] = cs[32 + j];
     }
-    const uint8_t* q_tok = p.q + t * p.q_stride0 * 2 + 8 * sub;
+    const uint8_t* q_tok = p.q + t * p.q_stride0 * 2 + 16 * sub;
     uint8_t* out_tok = p.out + t * p.out_stride0;
-    constexpr int U = 2;  // head pairs loaded before the first is used
-    for (int h0 = 0; h0 < p.num_heads; h0 += 2 * U) {
-        uint2 nope[U], rope[U];
+    constexpr int U = 2;  // groups of four heads loaded before the first is used
+    for (int h0 = 0; h0 < p.num_heads; h0 += 4 * U) {
+        uint4 nope[U], rope[U];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-            const int h = h0 + 2 * u + which;
-            nope[u] = rope[u] = make_uint2(0u, 0u);
+            const int h = h0 + 4 * u + which;
+            nope[u] = rope[u] = make_uint4(0u, 0u, 0u, 0u);
             if (h < p.num_heads) {
                 const uint8_t* row = q_tok + h * p.q_stride1 * 2;
-                nope[u] = ld_stream8(row);
-                rope[u] = ld_stream8(row + 128);
+                nope[u] = ld_stream16(row);
+                rope[u] = ld_stream16(row + 128);
             }
         }
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-            const int h = h0 + 2 * u + which;
+            const int h = h0 + 4 * u + which;
             const bool live = h < p.num_heads;
-            float x[4] = {bf16_lo(nope[u].x), bf16_hi(nope[u].x), bf16_lo(nope[u].y), bf16_hi(nope[u].y)};
-            const float e0 = bf16_lo(rope[u].x), o0 = bf16_hi(rope[u].x), e1 = bf16_lo(rope[u].y), o1 = bf16_hi(rope[u].y);
-            // separately rounded products, then the bf16 round trip the reference makes before quantising
-            const uint32_t r0 = pack_bf16x2(__fsub_rn(__fmul_rn(e0, c0), __fmul_rn(o0, s0)), __fadd_rn(__fmul_rn(o0, c0), __fmul_rn(e0, s0)));
-            const uint32_t r1 = pack_bf16x2(__fsub_rn(__fmul_rn(e1, c1), __fmul_rn(o1, s1)), __fadd_rn(__fmul_rn(o1, c1), __fmul_rn(e1, s1)));
-            float y[4] = {bf16_lo(r0), bf16_hi(r0), bf16_lo(r1), bf16_hi(r1)};
-            float amax_n = fmaxf(fmaxf(fabsf(x[0]), fabsf(x[1])), fmaxf(fabsf(x[2]), fabsf(x[3])));
-            float amax_r = fmaxf(fmaxf(fabsf(y[0]), fabsf(y[1])), fmaxf(fabsf(y[2]), fabsf(y[3])));
+            float x[8], y[8];
+            unpack8(nope[u], x);
+            unpack8(rope[u], y);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float e = y[2 * j], o = y[2 * j + 1];
+                // separately rounded products, then the bf16 round trip the reference makes before quantising
+                const uint32_t r = pack_bf16x2(__fsub_rn(__fmul_rn(e, c[j]), __fmul_rn(o, sn[j])),
+                                               __fadd_rn(__fmul_rn(o, c[j]), __fmul_rn(e, sn[j])));
+                y[2 * j] = bf16_lo(r), y[2 * j + 1] = bf16_hi(r);
+            }
+            float amax_n = 0.0f, amax_r = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) amax_n = fmaxf(amax_n, fabsf(x[i])), amax_r = fmaxf(amax_r, fabsf(y[i]));
             uint8_t* out = out_tok + h * p.out_stride1;
             float weight_factor = 1.0f;
             if (FP4) {
 #pragma unroll
-                for (int m = 1; m < 8; m <<= 1) {
+                for (int m = 1; m < 4; m <<= 1) {
                     amax_n = fmaxf(amax_n, __shfl_xor_sync(0xffffffffu, amax_n, m));
                     amax_r = fmaxf(amax_r, __shfl_xor_sync(0xffffffffu, amax_r, m));
                 }
@@ -306,13 +315,17 @@ __global__ void __launch_bounds__(WARPS * 32) indexer_q_rope_quant_token_kernel(
                     code[k] = cd > 254u ? 254u : cd;
                 }
                 const float inv_n = __uint_as_float((254u - code[0]) << 23), inv_r = __uint_as_float((254u - code[1]) << 23);
-                const uint32_t bn = pack_e2m1x2(__fmul_rn(x[0], inv_n), __fmul_rn(x[1], inv_n)) | (pack_e2m1x2(__fmul_rn(x[2], inv_n), __fmul_rn(x[3], inv_n)) << 8);
-                const uint32_t br = pack_e2m1x2(__fmul_rn(y[0], inv_r), __fmul_rn(y[1], inv_r)) | (pack_e2m1x2(__fmul_rn(y[2], inv_r), __fmul_rn(y[3], inv_r)) << 8);
+                uint32_t bn = 0, br = 0;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    bn |= pack_e2m1x2(__fmul_rn(x[2 * j], inv_n), __fmul_rn(x[2 * j + 1], inv_n)) << (8 * j);
+                    br |= pack_e2m1x2(__fmul_rn(y[2 * j], inv_r), __fmul_rn(y[2 * j + 1], inv_r)) << (8 * j);
+                }
                 if (live) {
-                    *reinterpret_cast<uint16_t*>(out + 2 * sub) = static_cast<uint16_t>(bn);
-                    *reinterpret_cast<uint16_t*>(out + 32 + 2 * sub) = static_cast<uint16_t>(br);
-                    if ((sub & 7) == 0) {
-                        uint8_t* sc = p.scales + t * p.scale_stride0 + h * p.scale_stride1 + (sub >> 3);
+                    *reinterpret_cast<uint32_t*>(out + 4 * sub) = bn;
+                    *reinterpret_cast<uint32_t*>(out + 32 + 4 * sub) = br;
+                    if ((sub & 3) == 0) {
+                        uint8_t* sc = p.scales + t * p.scale_stride0 + h * p.scale_stride1 + (sub >> 2);
                         sc[0] = static_cast<uint8_t>(code[0]);
                         sc[2] = static_cast<uint8_t>(code[1]);
                     }
@@ -320,13 +333,15 @@ __global__ void __launch_bounds__(WARPS * 32) indexer_q_rope_quant_token_kernel(
             } else {
                 float amax = fmaxf(amax_n, amax_r);
 #pragma unroll
-                for (int m = 1; m < 16; m <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
+                for (int m = 1; m < 8; m <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
                 const uint32_t code = ue8m0_code(amax);
                 const float inv = __uint_as_float((254u - code) << 23);
                 weight_factor = __uint_as_float(code << 23);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) x[i] = __fmul_rn(x[i], inv), y[i] = __fmul_rn(y[i], inv);
                 if (live) {
-                    *reinterpret_cast<uint32_t*>(out + 4 * sub) = pack_e4m3x4(__fmul_rn(x[0], inv), __fmul_rn(x[1], inv), __fmul_rn(x[2], inv), __fmul_rn(x[3], inv));
-                    *reinterpret_cast<uint32_t*>(out + 64 + 4 * sub) = pack_e4m3x4(__fmul_rn(y[0], inv), __fmul_rn(y[1], inv), __fmul_rn(y[2], inv), __fmul_rn(y[3], inv));
+                    st_global8(out + 8 * sub, make_uint2(pack_e4m3x4(x[0], x[1], x[2], x[3]), pack_e4m3x4(x[4], x[5], x[6], x[7])));
+                    st_global8(out + 64 + 8 * sub, make_uint2(pack_e4m3x4(y[0], y[1], y[2], y[3]), pack_e4m3x4(y[4], y[5], y[6], y[7])));
                 }
             }
             if (live && sub == 0) {
@@ -371,8 +386,9 @@ cudaError_t launch_indexer_q_rope_quant(const int64_t* positions, const void* q,
     const bool rows_shape = nope % 8 == 0 && rot_dim % 8 == 0 && addr(q) % 16 == 0 && q_stride0 % 8 == 0 && q_stride1 % 8 == 0 &&
                             addr(out) % 8 == 0 && out_stride0 % 8 == 0 && out_stride1 % 8 == 0;
     // one warp per token pays off once there are enough tokens to fill the GPU with warps
-    const bool token_shape = head_dim == 128 && rot_dim == 64 && num_tokens >= 8192 && addr(q) % 8 == 0 && q_stride0 % 4 == 0 &&
-                             q_stride1 % 4 == 0 && addr(out) % 4 == 0 && out_stride0 % 4 == 0 && out_stride1 % 4 == 0;
+    const bool token_shape = head_dim == 128 && rot_dim == 64 && num_tokens >= 8192 && addr(q) % 16 == 0 && q_stride0 % 8 == 0 &&
+                             q_stride1 % 8 == 0 && addr(out) % 8 == 0 && out_stride0 % 8 == 0 && out_stride1 % 8 == 0 &&
+                             (cos_sin_bf16 || addr(cos_sin) % 4 == 0);
     if (token_shape) {
         constexpr int WARPS = 4;
         const unsigned grid = static_cast<unsigned>((num_tokens + WARPS - 1) / WARPS);
