@@ -149,6 +149,58 @@ __global__ void __launch_bounds__(WARPS * 32) indexer_k_quant_rows_kernel(const 
     }
 }
 
+// The DeepSeek-V4 indexer shape (head_dim = quant_block = 128): 8 lanes per token, lane s keeps values [8s, 8s+8)
+// and [64+8s, 64+8s+8), one scale per token; 4 tokens per warp instruction, U passes in flight.
+template <int WARPS, int U, bool FP16>
+__global__ void __launch_bounds__(WARPS * 32) indexer_k_quant_128_kernel(const IndexerParams p) {
+    const int lane = threadIdx.x & 31, sub = lane & 7, which = lane >> 3;
+    const int64_t base = (static_cast<int64_t>(blockIdx.x) * WARPS + (threadIdx.x >> 5)) * (U * 4) + which;
+    uint4 lo[U], hi[U];
+    int64_t slot[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        const int64_t t = base + u * 4;
+        slot[u] = t < p.num_tokens ? p.slot_mapping[t] : -1;
+        lo[u] = hi[u] = make_uint4(0u, 0u, 0u, 0u);
+        if (slot[u] >= 0) {
+            const uint8_t* row = p.k + (t * p.k_stride + 8 * sub) * 2;
+            lo[u] = ld_stream16(row);
+            hi[u] = ld_stream16(row + 128);
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        float x[8], y[8];
+        unpack8_any<FP16>(lo[u], x);
+        unpack8_any<FP16>(hi[u], y);
+        float amax = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fmaxf(fabsf(x[i]), fabsf(y[i])));
+#pragma unroll
+        for (int m = 1; m < 8; m <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
+        if (slot[u] < 0) continue;
+        int64_t block, in_block;
+        split_slot(slot[u], p.block_size, p.bs_shift, &block, &in_block);
+        uint8_t* blk = p.cache + block * p.block_stride;
+        uint8_t* dst = blk + in_block * 128 + 8 * sub;
+        float s;
+        if (p.ue8m0) {
+            const uint32_t code = ue8m0_code(amax);
+            s = __uint_as_float(code << 23);
+            const float inv = __uint_as_float((254u - code) << 23);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) x[i] = __fmul_rn(x[i], inv), y[i] = __fmul_rn(y[i], inv);
+        } else {
+            s = group_scale(amax, false);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) x[i] = __fdiv_rn(x[i], s), y[i] = __fdiv_rn(y[i], s);
+        }
+        st_global8(dst, make_uint2(pack_e4m3x4(x[0], x[1], x[2], x[3]), pack_e4m3x4(x[4], x[5], x[6], x[7])));
+        st_global8(dst + 64, make_uint2(pack_e4m3x4(y[0], y[1], y[2], y[3]), pack_e4m3x4(y[4], y[5], y[6], y[7])));
+        if (sub == 0) reinterpret_cast<float*>(blk + p.block_size * 128)[in_block] = s;
+    }
+}
+
 template <int G, bool FP16>
 void launch_rows(const IndexerParams& p, cudaStream_t stream) {
     constexpr int WARPS = 4, U = 2, PER_CTA = WARPS * U * (32 / G);
@@ -174,6 +226,14 @@ cudaError_t launch_indexer_k_quant(const void* k, int64_t k_stride, int is_fp16,
                (addr(cache) & 7u) == 0 && block_stride % 8 == 0 && head_dim % 8 == 0 && (block_size * head_dim) % 4 == 0;
     const int64_t grid = (num_tokens + WARPS - 1) / WARPS;
     if (grid > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
+    if (p.vec_ok && head_dim == 128 && quant_block == 128) {
+        constexpr int W = 4, U = 2;
+        const unsigned g128 = static_cast<unsigned>((num_tokens + W * U * 4 - 1) / (W * U * 4));
+        if (is_fp16) indexer_k_quant_128_kernel<W, U, true><<<g128, W * 32, 0, stream>>>(p);
+        else indexer_k_quant_128_kernel<W, U, false><<<g128, W * 32, 0, stream>>>(p);
+        count_launch();
+        return cudaGetLastError();
+    }
     if (p.vec_ok && (head_dim == 64 || head_dim == 128 || head_dim == 256)) {
         if (head_dim == 64) is_fp16 ? launch_rows<8, true>(p, stream) : launch_rows<8, false>(p, stream);
         else if (head_dim == 128) is_fp16 ? launch_rows<16, true>(p, stream) : launch_rows<16, false>(p, stream);
