@@ -116,6 +116,33 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
+def bind_to_gpu_numa_node(device_index: int):
+    """Pin this process to the CPU cores next to its GPU (the "CPU Affinity" column of `nvidia-smi topo -m`), so that
+    the pinned host buffers of the end-to-end leg are allocated on the GPU's own NUMA node and the ranks of a
+    multi-GPU run do not all stream through one socket.  Reads settings only; returns the core list or None."""
+    try:
+        uuid = str(torch.cuda.get_device_properties(device_index).uuid)
+        q = subprocess.run(["nvidia-smi", "--query-gpu=index,uuid", "--format=csv,noheader"], capture_output=True, text=True,
+                           timeout=20).stdout
+        smi_index = next(int(line.split(",")[0]) for line in q.splitlines() if uuid in line)
+        topo = subprocess.run(["nvidia-smi", "topo", "-m"], capture_output=True, text=True, timeout=20).stdout.splitlines()
+        header = next(line for line in topo if "CPU Affinity" in line)
+        col = next(i for i, c in enumerate(header.split("\t")) if "CPU Affinity" in c)
+        row = next(line for line in topo if line.split("\t")[0].strip() == f"GPU{smi_index}")
+        spec = [c.strip() for c in row.split("\t")][col]
+        cores = set()
+        for part in spec.split(","):
+            lo, _, hi = part.partition("-")
+            cores.update(range(int(lo), int(hi or lo) + 1))
+        cores &= os.sched_getaffinity(0)
+        if cores:
+            os.sched_setaffinity(0, cores)
+            return sorted(cores)
+    except Exception:
+        pass
+    return None
+
+
 def time_steps(fn, steps: int, warmup: int, stream, sync_all):
     """W untimed steps, then exactly K steps between two CUDA events on the launching stream,
     bracketed by a barrier + device synchronise on both sides.  Returns seconds for the K steps."""
@@ -478,6 +505,7 @@ def main():
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     distributed = world > 1
+    numa_cores = bind_to_gpu_numa_node(local_rank) if distributed else None
     if distributed:
         import torch.distributed as dist
 
@@ -557,6 +585,7 @@ def main():
                      "algorithmic_bytes_per_launch": int(largest_bytes),
                      "kernel_ms": secs_max / args.steps * 1e3},
         "clocks": clocks, "gpu_launches": launches_total, "e2e": e2e,
+        "host_numa_binding": (f"rank 0 bound to {len(numa_cores)} cores next to its GPU" if numa_cores else None),
     }
     if not args.no_cpu_baseline and world == 1:
         line["cpu_baseline"] = cpu_baseline(w)
