@@ -1,0 +1,70 @@
+"""Where the upstream source tree is present (the build container; not the GPU box), run its own torch reference
+functions on fresh seeded inputs - larger than the committed fixtures - and compare the oracles with them directly.
+Skipped elsewhere.  No GPU."""
+from __future__ import annotations
+
+import pytest
+import torch
+
+from flaggems_vllm.testing import compare, workloads
+from oracle import c_oracle, ref_loader, torch_path
+
+pytestmark = pytest.mark.skipif(ref_loader.upstream_root() is None, reason="upstream source tree not present")
+
+
+@pytest.fixture(scope="module")
+def upstream():
+    return ref_loader.load_upstream_test_module()
+
+
+@pytest.mark.parametrize("seed,n,h,bs", [(11, 512, 16, 64), (12, 300, 128, 16), (13, 1000, 1, 64)])
+def test_prologue_oracles_against_upstream_ref_impl(upstream, seed, n, h, bs):
+    w = workloads.make("long_prefill", device="cpu", seed=seed, num_tokens=n, num_heads=h, num_blocks=(n + bs - 1) // bs + 4)
+    nb = w.k_cache.shape[0]
+    w.k_cache = w.k_cache[:, : 64 * 584].reshape(-1)[: nb * bs * 584].view(nb, bs * 584).contiguous()
+    w.slot_mapping = torch.where(w.slot_mapping >= nb * bs, w.slot_mapping % (nb * bs), w.slot_mapping)
+    # slots must stay distinct after the fold
+    valid = w.slot_mapping[w.slot_mapping >= 0]
+    keep = torch.ones_like(w.slot_mapping, dtype=torch.bool)
+    seen = set()
+    for i, s in enumerate(w.slot_mapping.tolist()):
+        if s >= 0 and s in seen:
+            keep[i] = False
+        seen.add(s)
+    w.slot_mapping = torch.where(keep, w.slot_mapping, torch.full_like(w.slot_mapping, -1))
+    cs = upstream.make_cos_sin_cache(131072, 64, torch.float32, "cpu")
+    q_up, kc_up = w.q.clone(), w.k_cache.clone()
+    upstream.ref_impl(q_up, w.kv.clone(), kc_up, w.slot_mapping.clone(), w.position_ids.clone(), cs, w.eps, bs)
+    q_t, kc_t = w.q.clone(), w.k_cache.clone()
+    torch_path.prologue(q_t, w.kv, kc_t, w.slot_mapping, w.position_ids, cs, w.eps, bs)
+    assert torch.equal(q_t.view(torch.int16), q_up.view(torch.int16)) and torch.equal(kc_t, kc_up)
+    q_c, kc_c = w.q.clone(), w.k_cache.clone()
+    c_oracle.prologue(q_c, w.kv, kc_c, w.slot_mapping, w.position_ids, cs, w.eps, bs)
+    assert torch.equal(kc_c, kc_up)
+    st = compare.assert_q_close(q_c, q_up)
+    assert st["mismatch_fraction"] < 1e-4
+    assert valid.numel() > 0
+
+
+def test_sibling_oracles_against_upstream_helpers():
+    g = torch.Generator().manual_seed(99)
+    # weighted RMSNorm
+    R = ref_loader.load_upstream_helper_test("test_deepseek_v4_attention_fused_q_kv_rmsnorm.py",
+                                             "flaggems_vllm.ops.deepseek_v4_attention_fused_q_kv_rmsnorm", ("fused_q_kv_rmsnorm",))
+    x, wgt = torch.randn(200, 1536, generator=g).to(torch.bfloat16), torch.randn(1536, generator=g).to(torch.bfloat16)
+    d = compare.bf16_ulp_distance(c_oracle.weighted_rmsnorm(x, wgt, 1e-6), R._rmsnorm_ref(x, wgt, 1e-6))
+    assert int(d.max()) <= 1 and float((d != 0).float().mean()) < 1e-3
+    # indexer q prologue, both formats
+    M = ref_loader.load_upstream_helper_test("test_fused_indexer_q_rope_quant.py", "flaggems_vllm.ops", ("fused_indexer_q_rope_quant",),
+                                             package_attrs={"SUPPORTED_FP8_DTYPE": torch.float8_e4m3fn})
+    q = (torch.randn(300, 8, 128, generator=g) * torch.logspace(-4, 3, 300)[:, None, None]).to(torch.bfloat16)
+    pos = torch.randint(0, 4096, (300,), generator=g)
+    cs = M._make_cos_sin_cache(4096, 64, "cpu", torch.float32)
+    wts = torch.randn(300, 8, generator=g).to(torch.bfloat16)
+    q_rot = M._rotate_tail_gptj(q, pos, cs)
+    f8, w8 = M._reference_fp8(q_rot.clone(), wts, 0.09, 0.35)
+    out, _, w_out = c_oracle.indexer_q_rope_quant(pos, q, cs, wts, 0.09, 0.35)
+    assert torch.equal(out, f8.view(torch.uint8)) and torch.equal(w_out, w8)
+    (p4, s4), w4 = M._reference_mxfp4(q_rot.clone(), wts, 0.09, 0.35)
+    out, sc, w_out = c_oracle.indexer_q_rope_quant(pos, q, cs, wts, 0.09, 0.35, use_fp4=True)
+    assert torch.equal(out, p4) and torch.equal(sc.view(torch.int32).squeeze(-1), s4) and torch.equal(w_out, w4)
