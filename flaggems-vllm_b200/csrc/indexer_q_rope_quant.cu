@@ -43,6 +43,16 @@ __device__ __forceinline__ float load_weight(const uint8_t* base, int64_t idx, i
     return f;
 }
 
+// UE8M0 byte of an MXFP4 block whose absolute maximum is `amax`: ceil(log2(max(amax, 6*2^-126) / 6)) + 127 clamped to
+// [0, 254], without the division: 6 = 1.5 * 4, so with the clamped maximum m * 2^(E-127), 1 <= m < 2, the quotient is
+// below, at or above 2^(E-129) for m below, at or above 1.5.  Equal to the log2/ceil statement for every bf16
+// maximum (a CPU test enumerates them).
+__device__ __forceinline__ uint32_t mxfp4_code(float amax) {
+    const uint32_t u = __float_as_uint(fmaxf(amax, 6.0f * 1.17549435e-38f));
+    const uint32_t code = (u >> 23) - 2u + ((u & 0x7fffffu) > 0x400000u ? 1u : 0u);
+    return code > 254u ? 254u : code;
+}
+
 // Two floats -> one byte of two e2m1 codes (lo in bits 0-3), round to nearest even, saturating at +-6.
 __device__ __forceinline__ uint32_t pack_e2m1x2(float lo, float hi) {
     uint32_t r;
@@ -107,10 +117,7 @@ __global__ void __launch_bounds__(WARPS * 32) indexer_q_rope_quant_kernel(const 
         constexpr int kGroupLanes = 32 / E;  // lanes per block of 32 values
 #pragma unroll
         for (int m = 1; m < kGroupLanes; m <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
-        // block scale 2^ceil(log2(max(amax, 6*2^-126)/6)), exponent clamped to [-127, 127]
-        const uint32_t u = __float_as_uint(__fdiv_rn(fmaxf(amax, 6.0f * 1.17549435e-38f), 6.0f));
-        uint32_t code = ((u >> 23) & 0xffu) + ((u & 0x7fffffu) ? 1u : 0u);
-        code = code > 254u ? 254u : code;
+        const uint32_t code = mxfp4_code(amax);
         const float inv = __uint_as_float((254u - code) << 23);  // code >= 1 because of the amax floor
         uint32_t bytes = 0;
 #pragma unroll
@@ -205,9 +212,7 @@ __global__ void __launch_bounds__(WARPS * 32) indexer_q_rope_quant_rows_kernel(c
         if (FP4) {
 #pragma unroll
             for (int m = 1; m < 4; m <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
-            const uint32_t bits = __float_as_uint(__fdiv_rn(fmaxf(amax, 6.0f * 1.17549435e-38f), 6.0f));
-            uint32_t code = ((bits >> 23) & 0xffu) + ((bits & 0x7fffffu) ? 1u : 0u);
-            code = code > 254u ? 254u : code;
+            const uint32_t code = mxfp4_code(amax);
             const float inv = __uint_as_float((254u - code) << 23);
             uint32_t bytes = 0;
 #pragma unroll
@@ -306,14 +311,7 @@ __global__ void __launch_bounds__(WARPS * 32) indexer_q_rope_quant_token_kernel(
                     amax_n = fmaxf(amax_n, __shfl_xor_sync(0xffffffffu, amax_n, m));
                     amax_r = fmaxf(amax_r, __shfl_xor_sync(0xffffffffu, amax_r, m));
                 }
-                uint32_t code[2];
-                const float am[2] = {amax_n, amax_r};
-#pragma unroll
-                for (int k = 0; k < 2; ++k) {
-                    const uint32_t bits = __float_as_uint(__fdiv_rn(fmaxf(am[k], 6.0f * 1.17549435e-38f), 6.0f));
-                    const uint32_t cd = ((bits >> 23) & 0xffu) + ((bits & 0x7fffffu) ? 1u : 0u);
-                    code[k] = cd > 254u ? 254u : cd;
-                }
+                const uint32_t code[2] = {mxfp4_code(amax_n), mxfp4_code(amax_r)};
                 const float inv_n = __uint_as_float((254u - code[0]) << 23), inv_r = __uint_as_float((254u - code[1]) << 23);
                 uint32_t bn = 0, br = 0;
 #pragma unroll

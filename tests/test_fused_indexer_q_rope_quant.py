@@ -39,8 +39,9 @@ def test_mxfp4_scale_bit_derivation_equals_log_statement_for_every_bf16_amax():
     amax = torch.arange(0, 0x7F80, dtype=torch.int32).to(torch.int16).view(torch.bfloat16).float()
     r = amax.clamp(min=6 * 2.0 ** -126) / 6.0
     want = (r.log2().ceil().clamp(-127.0, 127.0) + 127.0).to(torch.int32)
-    bits = r.view(torch.int32)
-    got = (((bits >> 23) & 0xFF) + ((bits & 0x7FFFFF) != 0).to(torch.int32)).clamp(max=254)
+    # the kernel's division-free form: 6 = 1.5 * 4 -> exponent of the clamped maximum minus 2, plus 1 if mantissa > 1.5
+    bits = amax.clamp(min=6 * 2.0 ** -126).view(torch.int32)
+    got = ((bits >> 23) - 2 + ((bits & 0x7FFFFF) > 0x400000).to(torch.int32)).clamp(max=254)
     assert torch.equal(got, want)
 
 
