@@ -156,8 +156,7 @@ __global__ void __launch_bounds__(WARPS * 32) gather_dequant_requests_kernel(con
                 *reinterpret_cast<uint4*>(row + 512 + 16 * lane) = b;
             }
         }
-        return;
-    }
+    } else {
     for (int64_t i = first; i < gather_len; i += warps_per_req) {
         const int64_t pos = start + i;
         const int64_t block_in_seq = pos / g.block_size, in_block = pos - block_in_seq * g.block_size;
@@ -175,6 +174,7 @@ __global__ void __launch_bounds__(WARPS * 32) gather_dequant_requests_kernel(con
         for (int j = lane; j < g.rope_dim; j += 32)
             out16[g.nope_dim + j] = static_cast<uint16_t>(data[g.nope_dim + 2 * j]) |
                                     (static_cast<uint16_t>(data[g.nope_dim + 2 * j + 1]) << 8);
+    }
     }
 }
 
