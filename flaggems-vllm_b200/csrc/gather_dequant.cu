@@ -65,98 +65,98 @@ gather_dequant_kernel(const uint8_t* __restrict__ k_cache, const int64_t* __rest
     if (lane >= kFirstRopeLane) {
         b = load_bytes<uint4>(data + kNopeDim + 16 * (lane - kFirstRopeLane), al);
     } else {
-            const float scale_b = ue8m0_to_float((codes.y >> (8 * (gb - 4))) & 0xffu);
-            b = dequant8(load_bytes<uint2>(data + 256 + 8 * lane, al), scale_b);
-        }
-        *reinterpret_cast<uint4*>(row + 512 + 16 * lane) = b;
+        const float scale_b = ue8m0_to_float((codes.y >> (8 * (gb - 4))) & 0xffu);
+        b = dequant8(load_bytes<uint2>(data + 256 + 8 * lane, al), scale_b);
     }
+    *reinterpret_cast<uint4*>(row + 512 + 16 * lane) = b;
+}
 
-    // ---- request / block-table form (the reference operator's own addressing) -------------------------
-    //
-    // out[r, offset + i, :] = token at position seq_len[r] - gather_len[r] + i of request r, found through
-    // block_table[r, pos / block_size].  grid = (CTAs per request, requests); the warps of a request stride
-    // over its gathered positions.  FAST = DeepSeek-V4 layout (448 e4m3 + 64 bf16, 8 scale bytes) with
-    // 16-byte aligned rows on both sides; otherwise any nope/rope/scale_slots with scalar accesses.
-    struct GatherParams {
-        uint8_t* out;            // bf16, element strides below, unit stride in the last dimension
-        int64_t out_stride0, out_stride1;
-        const uint8_t* k_cache;
-        const void* seq_lens;
-        const void* gather_lens;  // may be null: gather the whole sequence
-        const void* block_table;
-        int64_t max_blocks_per_seq;
-        int64_t block_size, block_stride;
-        int64_t offset;
-        int32_t nope_dim, rope_dim, scale_slots;
-        int32_t index64;          // 1: seq_lens / gather_lens / block_table are int64, 0: int32
-        int32_t bs_shift;         // log2(block_size) or -1
-    };
+// ---- request / block-table form (the reference operator's own addressing) -------------------------
+//
+// out[r, offset + i, :] = token at position seq_len[r] - gather_len[r] + i of request r, found through
+// block_table[r, pos / block_size].  grid = (CTAs per request, requests); the warps of a request stride
+// over its gathered positions.  FAST = DeepSeek-V4 layout (448 e4m3 + 64 bf16, 8 scale bytes) with
+// 16-byte aligned rows on both sides; otherwise any nope/rope/scale_slots with scalar accesses.
+struct GatherParams {
+    uint8_t* out;            // bf16, element strides below, unit stride in the last dimension
+    int64_t out_stride0, out_stride1;
+    const uint8_t* k_cache;
+    const void* seq_lens;
+    const void* gather_lens;  // may be null: gather the whole sequence
+    const void* block_table;
+    int64_t max_blocks_per_seq;
+    int64_t block_size, block_stride;
+    int64_t offset;
+    int32_t nope_dim, rope_dim, scale_slots;
+    int32_t index64;          // 1: seq_lens / gather_lens / block_table are int64, 0: int32
+    int32_t bs_shift;         // log2(block_size) or -1
+};
 
-    __device__ __forceinline__ int64_t load_index(const void* p, int64_t i, int is64) {
-        return is64 ? static_cast<const int64_t*>(p)[i] : static_cast<int64_t>(static_cast<const int32_t*>(p)[i]);
-    }
+__device__ __forceinline__ int64_t load_index(const void* p, int64_t i, int is64) {
+    return is64 ? static_cast<const int64_t*>(p)[i] : static_cast<int64_t>(static_cast<const int32_t*>(p)[i]);
+}
 
-    template <int WARPS, bool FAST>
-    __global__ void __launch_bounds__(WARPS * 32) gather_dequant_requests_kernel(const GatherParams g) {
-        const int lane = threadIdx.x & 31;
-        const int64_t req = blockIdx.y;
-        const int64_t seq_len = load_index(g.seq_lens, req, g.index64);
-        const int64_t gather_len = g.gather_lens ? load_index(g.gather_lens, req, g.index64) : seq_len;
-        const int64_t start = seq_len - gather_len;
-        const int64_t token_data = g.nope_dim + 2 * g.rope_dim;
-        const int64_t warps_per_req = static_cast<int64_t>(gridDim.x) * WARPS;
-        const int64_t first = static_cast<int64_t>(blockIdx.x) * WARPS + (threadIdx.x >> 5);
-        if (FAST) {
-            // two tokens per warp and iteration: both block-table lookups, then all cache reads, are in flight
-            // together before anything is converted
-            constexpr int U = 2;
-            for (int64_t i0 = first; i0 < gather_len; i0 += U * warps_per_req) {
-                const uint8_t* data[U];
-                const uint8_t* scales[U];
-                int64_t block[U];
-                bool live[U];
-    #pragma unroll
-                for (int u = 0; u < U; ++u) {
-                    const int64_t i = i0 + u * warps_per_req;
-                    live[u] = i < gather_len;
-                    const int64_t pos = start + (live[u] ? i : i0);
-                    const int64_t block_in_seq = g.bs_shift >= 0 ? pos >> g.bs_shift : pos / g.block_size;
-                    block[u] = load_index(g.block_table, req * g.max_blocks_per_seq + block_in_seq, g.index64);
-                }
-                uint2 codes[U], qa[U];
-                uint4 qb[U];
-    #pragma unroll
-                for (int u = 0; u < U; ++u) {
-                    const int64_t pos = start + (live[u] ? i0 + u * warps_per_req : i0);
-                    const int64_t in_block = g.bs_shift >= 0 ? pos & (g.block_size - 1) : pos % g.block_size;
-                    const uint8_t* base = g.k_cache + block[u] * g.block_stride;
-                    data[u] = base + in_block * kTokenDataBytes;
-                    scales[u] = base + g.block_size * kTokenDataBytes + in_block * kScaleBytes;
-                    codes[u] = *reinterpret_cast<const uint2*>(scales[u]);
-                    qa[u] = *reinterpret_cast<const uint2*>(data[u] + 8 * lane);
-                    if (lane >= kFirstRopeLane) {
-                        qb[u] = *reinterpret_cast<const uint4*>(data[u] + kNopeDim + 16 * (lane - kFirstRopeLane));
-                    } else {
-                        const uint2 t = *reinterpret_cast<const uint2*>(data[u] + 256 + 8 * lane);
-                        qb[u] = make_uint4(t.x, t.y, 0u, 0u);
-                    }
-                }
-    #pragma unroll
-                for (int u = 0; u < U; ++u) {
-                    if (!live[u]) continue;
-                    const int64_t i = i0 + u * warps_per_req;
-                    uint8_t* row = g.out + (req * g.out_stride0 + (g.offset + i) * g.out_stride1) * 2;
-                    const float scale_a = ue8m0_to_float((codes[u].x >> (8 * (lane >> 3))) & 0xffu);
-                    *reinterpret_cast<uint4*>(row + 16 * lane) = dequant8(qa[u], scale_a);
-                    uint4 b = qb[u];
-                    if (lane < kFirstRopeLane) {
-                        const float scale_b = ue8m0_to_float((codes[u].y >> (8 * (lane >> 3))) & 0xffu);
-                        b = dequant8(make_uint2(qb[u].x, qb[u].y), scale_b);
-                    }
-                    *reinterpret_cast<uint4*>(row + 512 + 16 * lane) = b;
+template <int WARPS, bool FAST>
+__global__ void __launch_bounds__(WARPS * 32) gather_dequant_requests_kernel(const GatherParams g) {
+    const int lane = threadIdx.x & 31;
+    const int64_t req = blockIdx.y;
+    const int64_t seq_len = load_index(g.seq_lens, req, g.index64);
+    const int64_t gather_len = g.gather_lens ? load_index(g.gather_lens, req, g.index64) : seq_len;
+    const int64_t start = seq_len - gather_len;
+    const int64_t token_data = g.nope_dim + 2 * g.rope_dim;
+    const int64_t warps_per_req = static_cast<int64_t>(gridDim.x) * WARPS;
+    const int64_t first = static_cast<int64_t>(blockIdx.x) * WARPS + (threadIdx.x >> 5);
+    if (FAST) {
+        // two tokens per warp and iteration: both block-table lookups, then all cache reads, are in flight
+        // together before anything is converted
+        constexpr int U = 2;
+        for (int64_t i0 = first; i0 < gather_len; i0 += U * warps_per_req) {
+            const uint8_t* data[U];
+            const uint8_t* scales[U];
+            int64_t block[U];
+            bool live[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int64_t i = i0 + u * warps_per_req;
+                live[u] = i < gather_len;
+                const int64_t pos = start + (live[u] ? i : i0);
+                const int64_t block_in_seq = g.bs_shift >= 0 ? pos >> g.bs_shift : pos / g.block_size;
+                block[u] = load_index(g.block_table, req * g.max_blocks_per_seq + block_in_seq, g.index64);
+            }
+            uint2 codes[U], qa[U];
+            uint4 qb[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int64_t pos = start + (live[u] ? i0 + u * warps_per_req : i0);
+                const int64_t in_block = g.bs_shift >= 0 ? pos & (g.block_size - 1) : pos % g.block_size;
+                const uint8_t* base = g.k_cache + block[u] * g.block_stride;
+                data[u] = base + in_block * kTokenDataBytes;
+                scales[u] = base + g.block_size * kTokenDataBytes + in_block * kScaleBytes;
+                codes[u] = *reinterpret_cast<const uint2*>(scales[u]);
+                qa[u] = *reinterpret_cast<const uint2*>(data[u] + 8 * lane);
+                if (lane >= kFirstRopeLane) {
+                    qb[u] = *reinterpret_cast<const uint4*>(data[u] + kNopeDim + 16 * (lane - kFirstRopeLane));
+                } else {
+                    const uint2 t = *reinterpret_cast<const uint2*>(data[u] + 256 + 8 * lane);
+                    qb[u] = make_uint4(t.x, t.y, 0u, 0u);
                 }
             }
-        } else {
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                if (!live[u]) continue;
+                const int64_t i = i0 + u * warps_per_req;
+                uint8_t* row = g.out + (req * g.out_stride0 + (g.offset + i) * g.out_stride1) * 2;
+                const float scale_a = ue8m0_to_float((codes[u].x >> (8 * (lane >> 3))) & 0xffu);
+                *reinterpret_cast<uint4*>(row + 16 * lane) = dequant8(qa[u], scale_a);
+                uint4 b = qb[u];
+                if (lane < kFirstRopeLane) {
+                    const float scale_b = ue8m0_to_float((codes[u].y >> (8 * (lane >> 3))) & 0xffu);
+                    b = dequant8(make_uint2(qb[u].x, qb[u].y), scale_b);
+                }
+                *reinterpret_cast<uint4*>(row + 512 + 16 * lane) = b;
+            }
+        }
+    } else {
         for (int64_t i = first; i < gather_len; i += warps_per_req) {
             const int64_t pos = start + i;
             const int64_t block_in_seq = pos / g.block_size, in_block = pos - block_in_seq * g.block_size;
