@@ -1,0 +1,86 @@
+"""The sibling operators at the sizes `bench.py` times them at, compared in full with their oracles."""
+from __future__ import annotations
+
+import pytest
+import torch
+
+import flaggems_vllm
+from flaggems_vllm.testing import compare, workloads
+from oracle import c_oracle
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def gen(seed):
+    return torch.Generator(device=DEV).manual_seed(seed)
+
+
+@pytest.mark.parametrize("packed", [True, False])
+def test_epilogue_quantiser_8192_tokens_128_heads(packed):
+    g = gen(1)
+    o = torch.randn(8192, 128, 512, generator=g, device=DEV, dtype=torch.float32).to(torch.bfloat16)
+    pos = torch.randint(0, 65536, (8192,), generator=g, device=DEV, dtype=torch.int64)
+    cs = workloads.cos_sin_table(65536, device=DEV)
+    fp8, scale = flaggems_vllm.fused_inv_rope_fp8_quant(o, pos, cs, 8, 16, tma_aligned_scales=packed)
+    want_fp8, want_scale = c_oracle.inv_rope_fp8_quant(o.cpu(), pos.cpu(), cs.cpu(), 8, 16, packed=packed)
+    assert torch.equal(fp8.cpu().view(torch.uint8), want_fp8)
+    assert torch.equal(scale.cpu().contiguous().view(torch.int32), want_scale.view(torch.int32))
+
+
+@pytest.mark.parametrize("use_fp4", [False, True])
+def test_indexer_q_prologue_16384_tokens_64_heads(use_fp4):
+    g = gen(2)
+    q = torch.randn(16384, 64, 128, generator=g, device=DEV).to(torch.bfloat16)
+    pos = torch.randint(0, 65536, (16384,), generator=g, device=DEV, dtype=torch.int64)
+    cs = workloads.cos_sin_table(65536, device=DEV)
+    w = torch.randn(16384, 64, generator=g, device=DEV).to(torch.bfloat16)
+    res, w_out = flaggems_vllm.fused_indexer_q_rope_quant(pos, q, cs, w, 0.0884, 0.125, use_fp4=use_fp4)
+    want_q, want_s, want_w = c_oracle.indexer_q_rope_quant(pos.cpu(), q.cpu(), cs.cpu(), w.cpu(), 0.0884, 0.125, use_fp4=use_fp4)
+    assert torch.equal(w_out.cpu(), want_w)
+    if use_fp4:
+        assert torch.equal(res[0].cpu(), want_q) and torch.equal(res[1].cpu().view(torch.uint8).view(16384, 64, 4), want_s)
+    else:
+        assert torch.equal(res.cpu().view(torch.uint8), want_q)
+
+
+def test_indexer_k_insert_one_million_tokens():
+    g = gen(3)
+    n = 1 << 20
+    k = torch.randn(n, 128, generator=g, device=DEV).to(torch.bfloat16)
+    cache = torch.randint(0, 256, (n // 64 + 8, 64, 132), generator=g, device=DEV, dtype=torch.uint8)
+    slots = torch.randperm(cache.shape[0] * 64, generator=g, device=DEV)[:n].to(torch.int64)
+    slots[::17] = -1
+    want = cache.cpu().clone()
+    c_oracle.indexer_k_quant_and_cache(k.cpu(), want, slots.cpu(), 128, "ue8m0")
+    flaggems_vllm.indexer_k_quant_and_cache(k, cache, slots, 128, "ue8m0")
+    assert torch.equal(cache.cpu(), want)
+
+
+def test_q_kv_rmsnorm_65536_tokens():
+    g = gen(4)
+    qr = torch.randn(65536, 1536, generator=g, device=DEV).to(torch.bfloat16)
+    kv = torch.randn(65536, 512, generator=g, device=DEV).to(torch.bfloat16)
+    qw = (1 + 0.1 * torch.randn(1536, generator=g, device=DEV)).to(torch.bfloat16)
+    kw = (1 + 0.1 * torch.randn(512, generator=g, device=DEV)).to(torch.bfloat16)
+    q_out, kv_out = flaggems_vllm.fused_q_kv_rmsnorm(qr, kv, qw, kw, 1e-6)
+    for got, x, wt in ((q_out, qr, qw), (kv_out, kv, kw)):
+        d = compare.bf16_ulp_distance(got.cpu(), c_oracle.weighted_rmsnorm(x.cpu(), wt.cpu(), 1e-6))
+        assert int(d.max()) <= 1 and float((d != 0).float().mean()) < 1e-3
+
+
+def test_cache_reader_262144_tokens():
+    g = gen(5)
+    reqs, seq, bs = 16, 16384, 64
+    blocks = reqs * seq // bs
+    cache = torch.randint(0, 256, (blocks, bs * 584), generator=g, device=DEV, dtype=torch.uint8)
+    cache[(cache & 0x7F) == 0x7F] = 0x41  # no e4m3 NaN codes
+    region = cache[:, bs * 576 :]
+    region.copy_(torch.randint(100, 140, region.shape, generator=g, device=DEV, dtype=torch.uint8))
+    table = torch.randperm(blocks, generator=g, device=DEV).to(torch.int32).view(reqs, seq // bs).contiguous()
+    lens = torch.randint(seq // 2, seq + 1, (reqs,), generator=g, device=DEV, dtype=torch.int32)
+    out = torch.zeros(reqs, seq, 512, device=DEV, dtype=torch.bfloat16)
+    flaggems_vllm.dequantize_and_gather_k_cache(out, cache, lens, None, table, bs)
+    want = torch.zeros(reqs, seq, 512, dtype=torch.bfloat16)
+    c_oracle.dequantize_and_gather(want, cache.cpu(), lens.cpu(), None, table.cpu(), bs)
+    assert torch.equal(out.cpu().view(torch.int16), want.view(torch.int16))
