@@ -240,11 +240,12 @@ def run_reference(args, rank, world):
 
 def hbm_ceiling(native, nbytes: int, stream):
     """This GPU's streaming rates for the prologue's access pattern without arithmetic
-    (dsv4_hbm_probe): in place (1 read : 1 write, the operator's mix), read-only, write-only."""
+    (dsv4_hbm_probe): in place (1 read : 1 write, the operator's mix), read-only, write-only, and 2 read : 1 write
+    (the mix of the narrowing sibling operators)."""
     rows = max(1, nbytes // 1024)
-    buf = torch.empty(rows * 1024, dtype=torch.uint8, device="cuda")
+    buf = torch.empty(rows * 1536, dtype=torch.uint8, device="cuda")
     lib, out = native.lib(), {}
-    for mode, name, traffic in ((0, "inplace_gbs", 2), (1, "read_gbs", 1), (2, "write_gbs", 1)):
+    for mode, name, traffic in ((0, "inplace_gbs", 2), (1, "read_gbs", 1), (2, "write_gbs", 1), (3, "read2_write1_gbs", 1.5)):
         def fn():
             native.check(lib.dsv4_hbm_probe(mode, buf.data_ptr(), rows, stream.cuda_stream))
         secs = time_steps(fn, 10, 3, stream, torch.cuda.synchronize)
@@ -515,7 +516,8 @@ def main():
     op = flaggems_vllm.fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert
 
     if args.siblings_only:
-        print(json.dumps({"sibling_ops": sibling_ops(args.steps, args.warmup)}), flush=True)
+        print(json.dumps({"sibling_ops": sibling_ops(args.steps, args.warmup),
+                          "hbm_ceiling": hbm_ceiling(_native, 1 << 30, torch.cuda.current_stream(dev))}), flush=True)
         return
     if args.upstream_shapes:
         print(json.dumps({"upstream_benchmark_shapes": upstream_shapes(op)}), flush=True)

@@ -248,7 +248,7 @@ int dsv4_fused_indexer_q_rope_quant(const int64_t* positions, const void* index_
 }
 
 int dsv4_hbm_probe(int mode, void* buffer, int64_t rows, void* cuda_stream) {
-    if (mode < 0 || mode > 2) return DSV4_ERR_BAD_VARIANT;
+    if (mode < 0 || mode > 3) return DSV4_ERR_BAD_VARIANT;
     if (rows < 0 || rows >= (1LL << 31)) return DSV4_ERR_BAD_SIZE;
     if (rows == 0) return DSV4_OK;
     if (!buffer) return DSV4_ERR_NULL_POINTER;

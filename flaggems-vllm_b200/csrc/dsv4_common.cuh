@@ -142,6 +142,14 @@ __device__ __forceinline__ uint32_t max_bf16x2(uint32_t a, uint32_t b) {
     return d;
 }
 
+// Element-wise maximum of the magnitudes of two bf16 pairs; the sign bits of the result are the
+// exclusive-or of the operands' and carry no meaning (one instruction, no separate absolute value).
+__device__ __forceinline__ uint32_t max_abs_bf16x2(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("max.xorsign.abs.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     uint32_t r;
     asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));

@@ -12,6 +12,8 @@ constexpr int kProbeWarps = 4, kProbeRows = 2;
 // mode 0: read a row and write it back in place (1 read : 1 write, like the prologue)
 // mode 1: read only (rows are xor-folded; the result is stored only if it hits a magic value)
 // mode 2: write only
+// mode 3: read a row, write half as many bytes to a second region behind the rows (2 read : 1 write, the
+//         mix of the epilogue quantiser and of the other narrowing operators)
 template <int MODE>
 __global__ void __launch_bounds__(kProbeWarps * 32) hbm_probe_kernel(uint8_t* buf, uint32_t rows, uint32_t* sink) {
     const int lane = threadIdx.x & 31;
@@ -33,6 +35,9 @@ __global__ void __launch_bounds__(kProbeWarps * 32) hbm_probe_kernel(uint8_t* bu
         uint8_t* row = buf + static_cast<uint64_t>(row0 + i) * kRowBytes;
         if (MODE == 1) {
             fold ^= a[i].x ^ a[i].y ^ a[i].z ^ a[i].w ^ b[i].x ^ b[i].y ^ b[i].z ^ b[i].w;
+        } else if (MODE == 3) {
+            uint8_t* half_row = buf + static_cast<uint64_t>(rows) * kRowBytes + static_cast<uint64_t>(row0 + i) * (kRowBytes / 2);
+            st_stream16(half_row + 16 * lane, make_uint4(a[i].x ^ b[i].x, a[i].y ^ b[i].y, a[i].z ^ b[i].z, a[i].w ^ b[i].w));
         } else {
             st_stream16(row + 16 * lane, a[i]);
             st_stream16(row + 512 + 16 * lane, b[i]);
@@ -49,6 +54,7 @@ cudaError_t launch_hbm_probe(int mode, uint8_t* buf, int64_t rows, uint32_t* sin
     const uint32_t n = static_cast<uint32_t>(rows);
     if (mode == 0) hbm_probe_kernel<0><<<grid, kProbeWarps * 32, 0, stream>>>(buf, n, sink);
     else if (mode == 1) hbm_probe_kernel<1><<<grid, kProbeWarps * 32, 0, stream>>>(buf, n, sink);
+    else if (mode == 3) hbm_probe_kernel<3><<<grid, kProbeWarps * 32, 0, stream>>>(buf, n, sink);
     else hbm_probe_kernel<2><<<grid, kProbeWarps * 32, 0, stream>>>(buf, n, sink);
     count_launch();
     return cudaGetLastError();

@@ -46,7 +46,9 @@ __device__ __forceinline__ float div_by_scale(float x, float scale, float recip)
 }
 
 template <bool FAST>
-__device__ __forceinline__ uint2 quant8_by(const float (&x)[8], float scale) {
+__device__ __forceinline__ uint2 quant8_by(const uint4& v, float scale) {
+    float x[8];
+    unpack8(v, x);
     const float recip = FAST ? __frcp_rn(scale) : 0.0f;
     float q[8];
 #pragma unroll
@@ -55,7 +57,9 @@ __device__ __forceinline__ uint2 quant8_by(const float (&x)[8], float scale) {
 }
 
 // 8 values times the exact reciprocal of a power-of-two scale (same result as dividing by it).
-__device__ __forceinline__ uint2 quant8_pow2(const float (&x)[8], uint32_t code) {
+__device__ __forceinline__ uint2 quant8_pow2(const uint4& v, uint32_t code) {
+    float x[8];
+    unpack8(v, x);
     const float inv = __uint_as_float((254u - code) << 23);
     float q[8];
 #pragma unroll
@@ -115,27 +119,24 @@ __global__ void __launch_bounds__(WARPS * 32, MIN_CTAS) inv_rope_fp8_quant_kerne
         for (int u = 0; u < U; ++u) {
             const int head = h0 + u;
             if (head >= head_end) break;
-            float xa[8], xb[8];
-            unpack8(a[u], xa);
-            unpack8(b[u], xb);
             // inverse rotation of the lane's pair, products rounded separately, then to bf16 as the torch path does
             const float e = bf16_lo(tail[u]), o = bf16_hi(tail[u]);
             const uint32_t rot = pack_bf16x2(__fadd_rn(__fmul_rn(e, c), __fmul_rn(o, sn)), __fsub_rn(__fmul_rn(o, c), __fmul_rn(e, sn)));
             const float te = bf16_lo(rot), to = bf16_hi(rot);
-            float ma = 0.0f, mb = 0.0f;
-            const float mt = fmaxf(fabsf(te), fabsf(to));
-#pragma unroll
-            for (int k = 0; k < 8; ++k) ma = fmaxf(ma, fabsf(xa[k])), mb = fmaxf(mb, fabsf(xb[k]));
+            // Group maxima on the packed words: |.| maxima of the even and the odd elements side by side (the sign
+            // bits of the intermediate words are meaningless and cleared at the end).
+            const uint32_t pa = max_abs_bf16x2(max_abs_bf16x2(a[u].x, a[u].y), max_abs_bf16x2(a[u].z, a[u].w));
+            uint32_t pb = max_abs_bf16x2(max_abs_bf16x2(b[u].x, b[u].y), max_abs_bf16x2(b[u].z, b[u].w));
             // Group 3 = B of lanes 16-23 and all of T: the upper half-warp folds its own pair and the pair of the
-            // lane 16 below into its B maximum, so that one packed reduction over 16 lanes serves all four groups
-            // (the maxima are bf16 values, so two of them travel and compare as one bf16x2 word).
-            const float mt_other = __shfl_xor_sync(0xffffffffu, mt, 16);
-            if (lane >= 16) mb = fmaxf(mb, fmaxf(mt, mt_other));
-            uint32_t both = (__float_as_uint(ma) >> 16) | __float_as_uint(mb);
+            // lane 16 below into its B maximum, so that one packed reduction over 16 lanes serves all four groups.
+            const uint32_t rot_other = __shfl_xor_sync(0xffffffffu, rot, 16);
+            if (lane >= 16) pb = max_abs_bf16x2(max_abs_bf16x2(pb, rot), rot_other);
+            // (A even | B even) against (A odd | B odd): the A maximum in the low half, the B maximum in the high half
+            uint32_t both = max_abs_bf16x2(__byte_perm(pa, pb, 0x5410), __byte_perm(pa, pb, 0x7632)) & 0x7fff7fffu;
 #pragma unroll
             for (int m = 1; m <= 8; m <<= 1) both = max_bf16x2(both, __shfl_xor_sync(0xffffffffu, both, m));
             const uint32_t both_other = __shfl_xor_sync(0xffffffffu, both, 16);
-            ma = bf16_lo(both), mb = bf16_hi(both);
+            const float ma = bf16_lo(both), mb = bf16_hi(both);
             const float m3 = lane >= 16 ? mb : bf16_hi(both_other);
             const float sa = __fmul_rn(fmaxf(ma, p.eps), 1.0f / 448.0f), sb = __fmul_rn(fmaxf(mb, p.eps), 1.0f / 448.0f);
             const float s3 = __fmul_rn(fmaxf(m3, p.eps), 1.0f / 448.0f);
@@ -146,8 +147,8 @@ __global__ void __launch_bounds__(WARPS * 32, MIN_CTAS) inv_rope_fp8_quant_kerne
                            static_cast<int64_t>(head_in_group) * (kRowBytes / 2);
             if (PACKED) {
                 const uint32_t code_a = pow2_ceil_code(sa), code_b = pow2_ceil_code(sb), code_3 = pow2_ceil_code(s3);
-                st_global8(out + 8 * lane, quant8_pow2(xa, code_a));
-                if (lane < kFirstRopeLane) st_global8(out + 256 + 8 * lane, quant8_pow2(xb, code_b));
+                st_global8(out + 8 * lane, quant8_pow2(a[u], code_a));
+                if (lane < kFirstRopeLane) st_global8(out + 256 + 8 * lane, quant8_pow2(b[u], code_b));
                 const float inv3 = __uint_as_float((254u - code_3) << 23);
                 *reinterpret_cast<uint16_t*>(out + kNopeDim + 2 * lane) =
                     static_cast<uint16_t>(pack_e4m3x4(__fmul_rn(te, inv3), __fmul_rn(to, inv3), 0.f, 0.f));
@@ -156,8 +157,8 @@ __global__ void __launch_bounds__(WARPS * 32, MIN_CTAS) inv_rope_fp8_quant_kerne
                 const uint32_t word = mine | (__shfl_xor_sync(0xffffffffu, mine, 16) << 8);
                 if (lane == 0) *reinterpret_cast<uint32_t*>(scale_row + head_in_group * p.padded_tokens * 4) = word;
             } else {
-                st_global8(out + 8 * lane, quant8_by<FASTDIV>(xa, sa));
-                if (lane < kFirstRopeLane) st_global8(out + 256 + 8 * lane, quant8_by<FASTDIV>(xb, sb));
+                st_global8(out + 8 * lane, quant8_by<FASTDIV>(a[u], sa));
+                if (lane < kFirstRopeLane) st_global8(out + 256 + 8 * lane, quant8_by<FASTDIV>(b[u], sb));
                 const float r3 = FASTDIV ? __frcp_rn(s3) : 0.0f;
                 *reinterpret_cast<uint16_t*>(out + kNopeDim + 2 * lane) = static_cast<uint16_t>(
                     pack_e4m3x4(div_by_scale<FASTDIV>(te, s3, r3), div_by_scale<FASTDIV>(to, s3, r3), 0.f, 0.f));
@@ -196,10 +197,10 @@ cudaError_t launch_inv_rope_fp8_quant(const void* o, int64_t o_stride_token, int
     make_fast_divisor(static_cast<uint32_t>(tasks_per_token), &tpt_mul, &tpt_shift);
     const unsigned g = static_cast<unsigned>(grid);
     const uint32_t tpt = static_cast<uint32_t>(tasks_per_token);
-    // Heads in flight per warp and CTAs per SM, measured on 1 Mi rows: UE8M0 mode 4 heads / 7 CTAs (72 registers)
-    // 273 us against 283 us for 2 / 8; fp32-scale mode is fastest at 2 / 8.
-    if (packed) inv_rope_fp8_quant_kernel<WARPS, true, false, 4, 7><<<g, WARPS * 32, 0, stream>>>(p, tpt, tpt_mul, tpt_shift);
-    else if (eps == 1e-10f) inv_rope_fp8_quant_kernel<WARPS, false, true, 2, 8><<<g, WARPS * 32, 0, stream>>>(p, tpt, tpt_mul, tpt_shift);
+    // Heads in flight per warp (2) and CTAs per SM, measured on 1 Mi rows: UE8M0 mode 10 CTAs (48 registers) 268 us
+    // against 280 us at 8; fp32-scale mode 9 CTAs (56 registers) 315 us against 322 us at 8 and 339 us at 10.
+    if (packed) inv_rope_fp8_quant_kernel<WARPS, true, false, 2, 10><<<g, WARPS * 32, 0, stream>>>(p, tpt, tpt_mul, tpt_shift);
+    else if (eps == 1e-10f) inv_rope_fp8_quant_kernel<WARPS, false, true, 2, 9><<<g, WARPS * 32, 0, stream>>>(p, tpt, tpt_mul, tpt_shift);
     else inv_rope_fp8_quant_kernel<WARPS, false, false, 2, 8><<<g, WARPS * 32, 0, stream>>>(p, tpt, tpt_mul, tpt_shift);
     count_launch();
     return cudaGetLastError();

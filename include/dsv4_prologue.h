@@ -205,7 +205,9 @@ int dsv4_fused_indexer_q_rope_quant(const int64_t* positions, const void* index_
 /*
  * Bandwidth probe with the prologue's q access pattern and no arithmetic, over `rows` rows of
  * 1 KiB starting at `buffer` (16-byte aligned): mode 0 reads every row and writes it back in
- * place, mode 1 only reads, mode 2 only writes (the buffer's contents are overwritten).  Used by
+ * place, mode 1 only reads, mode 2 only writes (the buffer's contents are overwritten), mode 3 reads
+ * every row and writes 512 bytes per row behind the rows (the buffer then holds rows * 1536 bytes;
+ * 2 read : 1 write, the mix of the narrowing sibling operators).  Used by
  * bench.py to measure, on the GPU at hand, the ceiling the fused kernel is compared with.
  * No counterpart in the reference.
  */
