@@ -17,6 +17,33 @@ ROPE_DIM = 64
 TOKEN_BYTES = 584  # 448 e4m3 + 64 bf16 + 8 scale bytes per cached token
 
 
+def _check_arguments(q, kv, k_cache, slot_mapping, position_ids, cos_sin_cache, cache_block_size):
+    """The reference's checks (:320-333) in its order and with its exception type, then what the reference leaves
+    to chance and a raw-pointer kernel cannot.  Returns (num_tokens, num_heads, num_tokens_insert, device)."""
+    assert q.is_contiguous() and kv.is_contiguous()
+    num_tokens, num_heads, head_dims = q.shape
+    assert head_dims == HEAD_DIM
+    assert kv.shape == (num_tokens, HEAD_DIM)
+    assert q.dtype == torch.bfloat16 and kv.dtype == torch.bfloat16
+    assert k_cache.dtype == torch.uint8
+    assert slot_mapping.dim() == 1
+    num_tokens_insert = slot_mapping.shape[0]
+    assert num_tokens_insert <= num_tokens
+    assert slot_mapping.dtype == torch.int64
+    assert position_ids.shape == (num_tokens,)
+    assert position_ids.dtype == torch.int64
+    assert cos_sin_cache.dim() == 2 and cos_sin_cache.shape[1] == ROPE_DIM
+    assert cos_sin_cache.dtype == torch.float32
+    assert k_cache.dim() == 2 and k_cache.stride(1) == 1, "k_cache must be [num_blocks, block_bytes] with unit byte stride"
+    assert cache_block_size > 0 and k_cache.shape[1] >= cache_block_size * TOKEN_BYTES, "cache block too small"
+    assert slot_mapping.is_contiguous() and position_ids.is_contiguous() and cos_sin_cache.is_contiguous()
+    dev = q.device
+    assert dev.type == "cuda", "this operator has no CPU path: tensors must live on a CUDA device"
+    for t in (kv, k_cache, slot_mapping, position_ids, cos_sin_cache):
+        assert t.device == dev, "all tensors must be on the same device"
+    return num_tokens, num_heads, num_tokens_insert, dev
+
+
 def fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert(
     q: torch.Tensor,
     kv: torch.Tensor,
@@ -45,29 +72,8 @@ def fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert(
         eps: RMSNorm epsilon
         cache_block_size: tokens per cache block
     """
-    # the reference's checks (:320-333), same order, same exception type
-    assert q.is_contiguous() and kv.is_contiguous()
-    num_tokens, num_heads, head_dims = q.shape
-    assert head_dims == HEAD_DIM
-    assert kv.shape == (num_tokens, HEAD_DIM)
-    assert q.dtype == torch.bfloat16 and kv.dtype == torch.bfloat16
-    assert k_cache.dtype == torch.uint8
-    assert slot_mapping.dim() == 1
-    num_tokens_insert = slot_mapping.shape[0]
-    assert num_tokens_insert <= num_tokens
-    assert slot_mapping.dtype == torch.int64
-    assert position_ids.shape == (num_tokens,)
-    assert position_ids.dtype == torch.int64
-    assert cos_sin_cache.dim() == 2 and cos_sin_cache.shape[1] == ROPE_DIM
-    assert cos_sin_cache.dtype == torch.float32
-    # what the reference leaves to chance and a raw-pointer kernel cannot
-    assert k_cache.dim() == 2 and k_cache.stride(1) == 1, "k_cache must be [num_blocks, block_bytes] with unit byte stride"
-    assert cache_block_size > 0 and k_cache.shape[1] >= cache_block_size * TOKEN_BYTES, "cache block too small"
-    assert slot_mapping.is_contiguous() and position_ids.is_contiguous() and cos_sin_cache.is_contiguous()
-    dev = q.device
-    assert dev.type == "cuda", "this operator has no CPU path: tensors must live on a CUDA device"
-    for t in (kv, k_cache, slot_mapping, position_ids, cos_sin_cache):
-        assert t.device == dev, "all tensors must be on the same device"
+    num_tokens, num_heads, num_tokens_insert, dev = _check_arguments(
+        q, kv, k_cache, slot_mapping, position_ids, cos_sin_cache, cache_block_size)
     if num_tokens == 0:
         return
 
@@ -103,21 +109,9 @@ def fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert_padded(
     """The nine-argument, out-of-place form vLLM >= 0.22 uses: q is left untouched and a new tensor
     [num_tokens, padded_heads, 512] is returned whose first num_heads heads hold the normalised, rotated q and
     whose remaining heads are zero; the KV side is the same as in the in-place operator."""
-    assert q.is_contiguous() and kv.is_contiguous()
-    num_tokens, num_heads, head_dims = q.shape
-    assert head_dims == HEAD_DIM and padded_heads >= num_heads
-    assert kv.shape == (num_tokens, HEAD_DIM)
-    assert q.dtype == torch.bfloat16 and kv.dtype == torch.bfloat16 and k_cache.dtype == torch.uint8
-    assert slot_mapping.dim() == 1 and slot_mapping.shape[0] <= num_tokens and slot_mapping.dtype == torch.int64
-    assert position_ids.shape == (num_tokens,) and position_ids.dtype == torch.int64
-    assert cos_sin_cache.dim() == 2 and cos_sin_cache.shape[1] == ROPE_DIM and cos_sin_cache.dtype == torch.float32
-    assert k_cache.dim() == 2 and k_cache.stride(1) == 1 and cache_block_size > 0
-    assert k_cache.shape[1] >= cache_block_size * TOKEN_BYTES, "cache block too small"
-    assert slot_mapping.is_contiguous() and position_ids.is_contiguous() and cos_sin_cache.is_contiguous()
-    dev = q.device
-    assert dev.type == "cuda", "this operator has no CPU path: tensors must live on a CUDA device"
-    for t in (kv, k_cache, slot_mapping, position_ids, cos_sin_cache):
-        assert t.device == dev, "all tensors must be on the same device"
+    num_tokens, num_heads, num_tokens_insert, dev = _check_arguments(
+        q, kv, k_cache, slot_mapping, position_ids, cos_sin_cache, cache_block_size)
+    assert padded_heads >= num_heads
     q_out = torch.empty(num_tokens, padded_heads, HEAD_DIM, dtype=q.dtype, device=dev)
     if num_tokens == 0:
         return q_out
@@ -127,7 +121,7 @@ def fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert_padded(
             _native.lib().dsv4_qnorm_rope_kv_insert_padded(
                 q.data_ptr(), q_out.data_ptr(), kv.data_ptr(), k_cache.data_ptr(), slot_mapping.data_ptr(),
                 position_ids.data_ptr(), cos_sin_cache.data_ptr(), float(eps), num_tokens, num_heads, int(padded_heads),
-                slot_mapping.shape[0], int(cache_block_size), k_cache.stride(0), stream,
+                num_tokens_insert, int(cache_block_size), k_cache.stride(0), stream,
             )
         )
     return q_out
@@ -139,9 +133,8 @@ def fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert_checked(
     """Debug form: same effects, but positions outside the table and slots outside the cache
     are skipped on the device and reported.  Returns a bit mask (bit 0: a bad position, bit 1:
     a bad slot); 0 means every index was in range.  Synchronises to read the mask."""
-    assert q.is_contiguous() and kv.is_contiguous() and q.dim() == 3 and q.shape[2] == HEAD_DIM
-    assert q.device.type == "cuda" and k_cache.dim() == 2 and k_cache.stride(1) == 1
-    num_tokens, num_heads, _ = q.shape
+    num_tokens, num_heads, num_tokens_insert, _ = _check_arguments(
+        q, kv, k_cache, slot_mapping, position_ids, cos_sin_cache, cache_block_size)
     status = torch.zeros(1, dtype=torch.int32, device=q.device)
     if num_tokens == 0:
         return 0
@@ -151,7 +144,7 @@ def fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert_checked(
         _native.check(
             lib.dsv4_qnorm_rope_kv_insert_checked(
                 q.data_ptr(), kv.data_ptr(), k_cache.data_ptr(), slot_mapping.data_ptr(), position_ids.data_ptr(),
-                cos_sin_cache.data_ptr(), float(eps), num_tokens, num_heads, slot_mapping.shape[0],
+                cos_sin_cache.data_ptr(), float(eps), num_tokens, num_heads, num_tokens_insert,
                 int(cache_block_size), k_cache.stride(0), k_cache.shape[0], cos_sin_cache.shape[0],
                 status.data_ptr(), stream,
             )
