@@ -321,6 +321,16 @@ def sibling_ops(steps, warmup):
         secs = time_steps(lambda: flaggems_vllm.indexer_k_quant_and_cache(ik, icache, islots, 128, "ue8m0"), steps, warmup, stream,
                           torch.cuda.synchronize)
         out[key] = {"tokens": nk, "us_per_launch": secs / steps * 1e6, "hbm_gbs": nk * (256 + 132 + 8) * steps / secs / 1e9}
+    del ik
+    # reader of that cache: 16 requests x 64 Ki tokens gathered into token order (132 B read + 132 B written per token)
+    reqs = 16
+    cu = (torch.arange(reqs + 1, device=dev, dtype=torch.int32) * (nk // reqs)).contiguous()
+    btable = table.to(torch.int32).view(reqs, nk // 64 // reqs).contiguous()
+    gk = torch.empty(nk, 128, device=dev, dtype=torch.float8_e4m3fn)
+    gs = torch.empty(nk, 4, device=dev, dtype=torch.uint8)
+    secs = time_steps(lambda: flaggems_vllm.cp_gather_indexer_k_quant_cache(icache, gk, gs, btable, cu), steps, warmup, stream,
+                      torch.cuda.synchronize)
+    out["cp_gather_indexer_k_quant_cache"] = {"tokens": nk, "us_per_launch": secs / steps * 1e6, "hbm_gbs": nk * 264 * steps / secs / 1e9}
     return out
 
 

@@ -218,6 +218,26 @@ int dsv4_indexer_k_quant_and_cache(const void* k, int64_t k_row_stride, int32_t 
                                                    static_cast<cudaStream_t>(cuda_stream)));
 }
 
+int dsv4_cp_gather_indexer_k_quant_cache(const void* k_cache, int64_t cache_block_stride_bytes, void* k_out,
+                                         int64_t k_out_stride_bytes, void* scale_out, int64_t scale_out_stride_bytes,
+                                         const int32_t* block_table, int64_t block_table_stride, const int32_t* cu_seqlen,
+                                         int64_t batch, int64_t num_tokens, int64_t cache_block_size, int64_t head_dim,
+                                         int64_t num_quant_blocks, void* cuda_stream) {
+    if (num_tokens < 0 || num_tokens >= (1LL << 31) || batch < 0 || batch >= (1LL << 31) - 1 || head_dim <= 0 ||
+        head_dim >= (1LL << 24) || num_quant_blocks <= 0 || num_quant_blocks > head_dim || cache_block_size <= 0 ||
+        cache_block_size >= (1LL << 31))
+        return DSV4_ERR_BAD_SIZE;
+    if (num_tokens == 0 || batch == 0) return DSV4_OK;
+    if (!k_cache || !k_out || !scale_out || !block_table || !cu_seqlen) return DSV4_ERR_NULL_POINTER;
+    if (cache_block_stride_bytes < cache_block_size * (head_dim + 4 * num_quant_blocks) || k_out_stride_bytes < head_dim ||
+        scale_out_stride_bytes < 4 * num_quant_blocks)
+        return DSV4_ERR_BAD_SIZE;
+    return static_cast<int>(launch_cp_gather_indexer(k_cache, cache_block_stride_bytes, k_out, k_out_stride_bytes, scale_out,
+                                                     scale_out_stride_bytes, block_table, block_table_stride, cu_seqlen, batch,
+                                                     num_tokens, cache_block_size, static_cast<int>(head_dim),
+                                                     static_cast<int>(num_quant_blocks), static_cast<cudaStream_t>(cuda_stream)));
+}
+
 int dsv4_fused_indexer_q_rope_quant(const int64_t* positions, const void* index_q, int64_t q_stride0, int64_t q_stride1,
                                     const void* cos_sin_cache, int64_t cos_sin_stride, int32_t cos_sin_is_bf16, int64_t rot_dim,
                                     void* q_out, int64_t out_stride0, int64_t out_stride1, void* q_scales_out,

@@ -389,6 +389,10 @@ cudaError_t launch_inv_rope_fp8_quant(const void* o, int64_t o_stride_token, int
 cudaError_t launch_indexer_k_quant(const void* k, int64_t k_stride, int is_fp16, void* cache, int64_t block_stride,
                                    const int64_t* slot_mapping, int64_t num_tokens, int64_t block_size, int head_dim,
                                    int quant_block, int ue8m0, cudaStream_t stream);
+cudaError_t launch_cp_gather_indexer(const void* cache, int64_t block_stride, void* k_out, int64_t k_out_stride, void* scale_out,
+                                     int64_t scale_out_stride, const int32_t* block_table, int64_t block_table_stride,
+                                     const int32_t* cu_seqlen, int64_t batch, int64_t num_tokens, int64_t block_size, int head_dim,
+                                     int num_quant_blocks, cudaStream_t stream);
 cudaError_t launch_indexer_q_rope_quant(const int64_t* positions, const void* q, int64_t q_stride0, int64_t q_stride1,
                                         const void* cos_sin, int64_t cos_sin_stride, int cos_sin_bf16, int rot_dim, void* out,
                                         int64_t out_stride0, int64_t out_stride1, void* scales, int64_t scale_stride0,

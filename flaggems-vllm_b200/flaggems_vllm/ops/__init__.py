@@ -1,4 +1,5 @@
 """Operators of this package (reference: src/flaggems_vllm/ops/__init__.py:61-63,191)."""
+from .cp_gather_indexer_k_quant_cache import cp_gather_indexer_k_quant_cache
 from .deepseek_v4_attention_dequantize_and_gather_k_cache import dequantize_and_gather_k_cache
 from .deepseek_v4_attention_fused_q_kv_rmsnorm import fused_q_kv_rmsnorm
 from .fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert import (
@@ -15,6 +16,7 @@ from .indexer_k_quant_and_cache import indexer_k_quant_and_cache
 __all__ = [
     "fused_indexer_q_rope_quant",
     "indexer_k_quant_and_cache",
+    "cp_gather_indexer_k_quant_cache",
     "fused_inv_rope_fp8_quant",
     "fused_q_kv_rmsnorm",
     "dequantize_and_gather_k_cache",

@@ -181,6 +181,22 @@ int dsv4_indexer_k_quant_and_cache(const void* k, int64_t k_row_stride, int32_t 
                                    int32_t scale_is_ue8m0, void* cuda_stream);
 
 /*
+ * The reader of the sparse-indexer key cache.  Replaces the reference operator
+ *   cp_gather_indexer_k_quant_cache(k_cache, k_fp8, k_fp8_scale, block_table, cu_seqlen)
+ * (src/flaggems_vllm/ops/cp_gather_indexer_k_quant_cache.py:129-190, kernel :24-126): output token t belongs to
+ * the request b with cu_seqlen[b] <= t < cu_seqlen[b+1] (int32 [batch+1], non-decreasing; tokens outside every
+ * request are left untouched); with o = t - cu_seqlen[b] its head_dim value bytes and num_quant_blocks fp32
+ * scales are copied from cache block block_table[b*block_table_stride + o / cache_block_size] (int32), position
+ * o % cache_block_size, to k_out + t*k_out_stride_bytes and scale_out + t*scale_out_stride_bytes.  Cache blocks
+ * are laid out as for dsv4_indexer_k_quant_and_cache.
+ */
+int dsv4_cp_gather_indexer_k_quant_cache(const void* k_cache, int64_t cache_block_stride_bytes, void* k_out,
+                                         int64_t k_out_stride_bytes, void* scale_out, int64_t scale_out_stride_bytes,
+                                         const int32_t* block_table, int64_t block_table_stride, const int32_t* cu_seqlen,
+                                         int64_t batch, int64_t num_tokens, int64_t cache_block_size, int64_t head_dim,
+                                         int64_t num_quant_blocks, void* cuda_stream);
+
+/*
  * The sparse-indexer prologue.  Replaces the reference operator
  *   fused_indexer_q_rope_quant(positions, index_q, index_q_cos_sin_cache, index_weights,
  *                              index_weights_softmax_scale, index_weights_head_scale, use_fp4)

@@ -48,6 +48,8 @@ def lib() -> ctypes.CDLL:
         L.dsv4_oracle_inv_rope_fp8_quant.restype = i32
         L.dsv4_oracle_indexer_k_quant.argtypes = [vp, i64, i32, vp, i64, vp, i64, i64, i64, i64, i32]
         L.dsv4_oracle_indexer_k_quant.restype = i32
+        L.dsv4_oracle_cp_gather_indexer.argtypes = [vp, i64, vp, i64, vp, i64, vp, i64, vp, i64, i64, i64, i64, i64]
+        L.dsv4_oracle_cp_gather_indexer.restype = i32
         L.dsv4_oracle_indexer_q_rope_quant.argtypes = [vp, vp, vp, i64, vp, f32, f32, i64, i64, i64, i32, vp, vp, vp]
         L.dsv4_oracle_indexer_q_rope_quant.restype = i32
         L.dsv4_oracle_check_division_shortcut.argtypes = [f32, vp, vp]
@@ -143,6 +145,23 @@ def indexer_k_quant_and_cache(k, kv_cache, slot_mapping, quant_block_size, scale
                                            k.shape[1], int(quant_block_size), 1 if scale_fmt == "ue8m0" else 0)
     if rc != 0:
         raise ValueError("dsv4_oracle_indexer_k_quant rejected its arguments")
+
+
+def cp_gather_indexer_k_quant_cache(k_cache, k_fp8, k_fp8_scale, block_table, cu_seqlen) -> None:
+    """Same arguments as the reference operator, on CPU tensors; k_fp8 [T, head_dim] (1-byte elements) and k_fp8_scale
+    [T, 4*groups bytes] are written in place for the tokens inside a request."""
+    _cpu(k_cache, torch.uint8), _cpu(block_table, torch.int32), _cpu(cu_seqlen, torch.int32)
+    assert k_cache.dim() == 3 and k_cache.is_contiguous() and k_fp8.device.type == "cpu" and k_fp8_scale.device.type == "cpu"
+    assert k_fp8.element_size() == 1 and k_fp8.stride(1) == 1 and k_fp8_scale.stride(1) == 1 and block_table.stride(1) == 1
+    head_dim = k_fp8.shape[1]
+    scale_bytes = k_fp8_scale.shape[1] * k_fp8_scale.element_size()
+    assert scale_bytes % 4 == 0 and k_cache.shape[2] == head_dim + scale_bytes
+    rc = lib().dsv4_oracle_cp_gather_indexer(k_cache.data_ptr(), k_cache.stride(0), k_fp8.data_ptr(), k_fp8.stride(0),
+                                             k_fp8_scale.data_ptr(), k_fp8_scale.stride(0) * k_fp8_scale.element_size(),
+                                             block_table.data_ptr(), block_table.stride(0), cu_seqlen.data_ptr(),
+                                             block_table.shape[0], k_fp8.shape[0], k_cache.shape[1], head_dim, scale_bytes // 4)
+    if rc != 0:
+        raise ValueError("dsv4_oracle_cp_gather_indexer rejected its arguments")
 
 
 def indexer_q_rope_quant(positions, index_q, cos_sin_cache, weights, softmax_scale, head_scale, use_fp4=False):

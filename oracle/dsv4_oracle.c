@@ -453,6 +453,30 @@ int dsv4_oracle_indexer_k_quant(const uint16_t* k, int64_t k_stride, int is_fp16
     return 0;
 }
 
+/*
+ * Gather of the sparse-indexer keys from their paged cache into token order, the torch statement
+ * tests/test_cp_gather_indexer_k_quant_cache.py:85-116 of src/flaggems_vllm/ops/cp_gather_indexer_k_quant_cache.py:24-190:
+ * request by request, token by token; rows of the outputs outside every request are not written.
+ */
+int dsv4_oracle_cp_gather_indexer(const uint8_t* cache, int64_t block_stride, uint8_t* k_out, int64_t k_out_stride, uint8_t* scale_out,
+                                  int64_t scale_out_stride, const int32_t* block_table, int64_t block_table_stride,
+                                  const int32_t* cu_seqlen, int64_t batch, int64_t num_tokens, int64_t block_size, int64_t head_dim,
+                                  int64_t num_quant_blocks) {
+    if (batch < 0 || block_size <= 0 || head_dim <= 0 || num_quant_blocks <= 0) return -1;
+    for (int64_t b = 0; b < batch; ++b) {
+        for (int64_t t = cu_seqlen[b]; t < cu_seqlen[b + 1]; ++t) {
+            if (t < 0 || t >= num_tokens) return -2;
+            int64_t off = t - cu_seqlen[b];
+            const uint8_t* base = cache + (int64_t)block_table[b * block_table_stride + off / block_size] * block_stride;
+            int64_t in_block = off % block_size;
+            memcpy(k_out + t * k_out_stride, base + in_block * head_dim, (size_t)head_dim);
+            memcpy(scale_out + t * scale_out_stride, base + block_size * head_dim + in_block * num_quant_blocks * 4,
+                   (size_t)(num_quant_blocks * 4));
+        }
+    }
+    return 0;
+}
+
 /* e2m1 code of |v| <= 6 with the tie rule of tests/test_fused_indexer_q_rope_quant.py:81-92 (nearest, ties to even). */
 static inline uint8_t e2m1_code(float v) {
     float a = fabsf(v);

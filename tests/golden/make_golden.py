@@ -271,7 +271,33 @@ def indexer_q_cases() -> None:
             print(name, "ok")
 
 
+def cp_gather_cases() -> None:
+    """Seeded caches and request metadata from the upstream test's own builders through its torch statement
+    `torch_gather` (tests/test_cp_gather_indexer_k_quant_cache.py:85-171), at the test's two parameter sets (:176-179)
+    plus a case with more than 16 requests, one of them empty."""
+    M = ref_loader.load_upstream_helper_test("test_cp_gather_indexer_k_quant_cache.py", "flaggems_vllm.ops",
+                                             ("cp_gather_indexer_k_quant_cache",))
+    cases = (([13, 7, 16], 8, 128, 128, 0), ([17, 1, 33, 9], 16, 512, 128, 5),
+             ([3, 9, 1, 12, 0, 8, 2, 7, 11, 4, 6, 10, 1, 3, 9, 2, 5, 7, 4, 8, 6, 1, 13, 2, 3, 5, 4, 9, 7, 6, 2], 4, 64, 32, 3))
+    for idx, (seq_lens, bs, hd, qbs, extra) in enumerate(cases):
+        torch.manual_seed(500 + idx)
+        table, cu, blocks = M._make_gather_metadata(seq_lens, bs, "cpu")
+        perm = torch.randperm(blocks, dtype=torch.int32)  # scatter the blocks, which the upstream builder leaves in order
+        table = torch.where(table >= 0, perm[table.clamp(min=0).long()], table)
+        cache = M._make_cache(blocks, bs, hd, qbs, torch.float8_e4m3fn, "cpu")
+        tokens = int(cu[-1]) + extra
+        k = torch.full((tokens, hd), 0x7B, dtype=torch.uint8)
+        scale = torch.full((tokens, hd * 4 // qbs), 0x7B, dtype=torch.uint8)
+        M.torch_gather(cache, k.view(torch.float8_e4m3fn), scale, table, cu)
+        name = f"cp_gather_r{len(seq_lens)}_b{bs}_d{hd}_q{qbs}_x{extra}"
+        np.savez_compressed(HERE / f"{name}.npz", cache=cache.numpy(), block_table=table.numpy(), cu_seqlen=cu.numpy(),
+                            k=k.numpy(), scale=scale.numpy(), quant_block_size=qbs)
+        print(name, "ok")
+
+
 if __name__ == "__main__":
+    if len(sys.argv) < 2 or sys.argv[1] == "cp_gather":
+        cp_gather_cases()
     if len(sys.argv) < 2 or sys.argv[1] == "indexer_q":
         indexer_q_cases()
     if len(sys.argv) < 2 or sys.argv[1] == "indexer":

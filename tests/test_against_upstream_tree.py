@@ -68,3 +68,14 @@ def test_sibling_oracles_against_upstream_helpers():
     (p4, s4), w4 = M._reference_mxfp4(q_rot.clone(), wts, 0.09, 0.35)
     out, sc, w_out = c_oracle.indexer_q_rope_quant(pos, q, cs, wts, 0.09, 0.35, use_fp4=True)
     assert torch.equal(out, p4) and torch.equal(sc.view(torch.int32).squeeze(-1), s4) and torch.equal(w_out, w4)
+    # reader of the indexer key cache
+    C = ref_loader.load_upstream_helper_test("test_cp_gather_indexer_k_quant_cache.py", "flaggems_vllm.ops", ("cp_gather_indexer_k_quant_cache",))
+    seq_lens = [37, 0, 5, 64, 129] + [3] * 20
+    table, cu, blocks = C._make_gather_metadata(seq_lens, 16, "cpu")
+    cache = C._make_cache(blocks, 16, 128, 128, torch.float8_e4m3fn, "cpu")
+    tokens = int(cu[-1]) + 4
+    want_k, want_s = torch.full((tokens, 128), 0x7B, dtype=torch.uint8), torch.full((tokens, 4), 0x7B, dtype=torch.uint8)
+    C.torch_gather(cache, want_k.view(torch.float8_e4m3fn), want_s, table, cu)
+    got_k, got_s = torch.full_like(want_k, 0x7B), torch.full_like(want_s, 0x7B)
+    c_oracle.cp_gather_indexer_k_quant_cache(cache, got_k, got_s, table, cu)
+    assert torch.equal(got_k, want_k) and torch.equal(got_s, want_s)

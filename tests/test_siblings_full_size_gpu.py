@@ -84,3 +84,20 @@ def test_cache_reader_262144_tokens():
     want = torch.zeros(reqs, seq, 512, dtype=torch.bfloat16)
     c_oracle.dequantize_and_gather(want, cache.cpu(), lens.cpu(), None, table.cpu(), bs)
     assert torch.equal(out.cpu().view(torch.int16), want.view(torch.int16))
+
+
+def test_indexer_cache_reader_one_million_tokens():
+    g = gen(6)
+    n, reqs, bs = 1 << 20, 16, 64
+    cache = torch.randint(0, 256, (n // bs, bs, 132), generator=g, device=DEV, dtype=torch.uint8)
+    table = torch.randperm(n // bs, generator=g, device=DEV).to(torch.int32).view(reqs, -1).contiguous()
+    lens = torch.randint(n // reqs // 2, n // reqs + 1, (reqs,), generator=g, device=DEV, dtype=torch.int32)
+    cu = torch.zeros(reqs + 1, device=DEV, dtype=torch.int32)
+    cu[1:] = torch.cumsum(lens, 0)
+    tokens = int(cu[-1]) + 5
+    k = torch.full((tokens, 128), 0x7B, device=DEV, dtype=torch.uint8)
+    s = torch.full((tokens, 4), 0x7B, device=DEV, dtype=torch.uint8)
+    flaggems_vllm.cp_gather_indexer_k_quant_cache(cache, k, s, table, cu)
+    want_k, want_s = torch.full((tokens, 128), 0x7B, dtype=torch.uint8), torch.full((tokens, 4), 0x7B, dtype=torch.uint8)
+    c_oracle.cp_gather_indexer_k_quant_cache(cache.cpu(), want_k, want_s, table.cpu(), cu.cpu())
+    assert torch.equal(k.cpu(), want_k) and torch.equal(s.cpu(), want_s)
