@@ -331,6 +331,29 @@ def sibling_ops(steps, warmup):
     secs = time_steps(lambda: flaggems_vllm.cp_gather_indexer_k_quant_cache(icache, gk, gs, btable, cu), steps, warmup, stream,
                       torch.cuda.synchronize)
     out["cp_gather_indexer_k_quant_cache"] = {"tokens": nk, "us_per_launch": secs / steps * 1e6, "hbm_gbs": nk * 264 * steps / secs / 1e9}
+    del icache, gk, gs
+    # index bookkeeping of the sparse attention: 32768 tokens, 16 requests
+    nt, reqs, tk = 32768, 16, 2048
+    local = torch.randint(0, 65536, (nt, tk), generator=g, device=dev, dtype=torch.int32)
+    local[torch.rand(nt, tk, generator=g, device=dev) < 0.1] = -1
+    t2r = torch.randint(0, reqs, (nt,), generator=g, device=dev, dtype=torch.int32)
+    btable = torch.randperm(reqs * 1024, generator=g, device=dev).to(torch.int32).view(reqs, 1024).contiguous()
+    secs = time_steps(lambda: flaggems_vllm.compute_global_topk_indices_and_lens(local, t2r, btable, 64), steps, warmup, stream,
+                      torch.cuda.synchronize)
+    out["compute_global_topk_indices_and_lens"] = {"tokens": nt, "topk": tk, "us_per_launch": secs / steps * 1e6,
+                                                   "hbm_gbs": nt * (8 * tk + 8) * steps / secs / 1e9,
+                                                   "note": "includes torch.empty of the outputs per call"}
+    del local
+    tk, window = 512, 128
+    tki = torch.randint(0, 8192, (nt, tk), generator=g, device=dev, dtype=torch.int32)
+    qsl = (torch.arange(reqs + 1, device=dev, dtype=torch.int32) * (nt // reqs)).contiguous()
+    seq = torch.full((reqs,), 8192, device=dev, dtype=torch.int32)
+    gat = torch.full((reqs,), nt // reqs + window, device=dev, dtype=torch.int32)
+    secs = time_steps(lambda: flaggems_vllm.combine_topk_swa_indices(tki, qsl, seq, gat, window, 4, tk, 8192, 2048), steps, warmup, stream,
+                      torch.cuda.synchronize)
+    out["combine_topk_swa_indices"] = {"tokens": nt, "topk": tk, "window": window, "us_per_launch": secs / steps * 1e6,
+                                       "hbm_gbs": nt * (4 * tk + 4 * (tk + window) + 4) * steps / secs / 1e9,
+                                       "note": "includes torch.empty of the outputs per call; positions 6144-8191, so every row has 512 + 128 entries"}
     return out
 
 

@@ -238,6 +238,40 @@ int dsv4_cp_gather_indexer_k_quant_cache(const void* k_cache, int64_t cache_bloc
                                                      static_cast<int>(num_quant_blocks), static_cast<cudaStream_t>(cuda_stream)));
 }
 
+int dsv4_compute_global_topk_indices_and_lens(const int32_t* topk_indices, int64_t topk_stride, const int32_t* token_to_req,
+                                              const int32_t* block_table, int64_t block_table_stride, const int32_t* is_valid_token,
+                                              int32_t* global_indices, int64_t global_stride, int32_t* lens, int64_t num_tokens,
+                                              int64_t topk, int64_t block_size, void* cuda_stream) {
+    if (num_tokens < 0 || topk < 0 || topk >= (1LL << 31) || block_size <= 0 || block_size >= (1LL << 31) || topk_stride < topk ||
+        global_stride < topk)
+        return DSV4_ERR_BAD_SIZE;
+    if (num_tokens == 0) return DSV4_OK;
+    if (!topk_indices || !token_to_req || !block_table || !global_indices || !lens) return DSV4_ERR_NULL_POINTER;
+    return static_cast<int>(launch_global_topk(topk_indices, topk_stride, token_to_req, block_table, block_table_stride, is_valid_token,
+                                               global_indices, global_stride, lens, num_tokens, static_cast<int>(topk),
+                                               static_cast<int>(block_size), static_cast<cudaStream_t>(cuda_stream)));
+}
+
+int dsv4_combine_topk_swa_indices(const int32_t* topk_indices, int64_t topk_stride, int64_t topk_width,
+                                  const int32_t* query_start_loc, const int32_t* seq_lens, const int32_t* gather_lens,
+                                  int32_t* combined, int64_t combined_stride, int64_t combined_width, int32_t* lens,
+                                  int64_t num_reqs, int64_t num_tokens, int64_t window_size, int64_t compress_ratio, int64_t topk,
+                                  int64_t M, int64_t N, void* cuda_stream) {
+    const int64_t lim = 1LL << 31;
+    if (num_tokens < 0 || num_tokens >= lim || num_reqs < 0 || num_reqs >= lim - 1 || topk < 0 || topk > topk_width ||
+        topk_width >= lim || window_size < 0 || compress_ratio <= 0 || compress_ratio >= lim || combined_width >= lim ||
+        topk + window_size > combined_width || topk_stride < topk_width || combined_stride < combined_width || M <= -lim ||
+        M >= lim || N <= -lim || N >= lim)
+        return DSV4_ERR_BAD_SIZE;
+    if (num_tokens == 0 || num_reqs == 0) return DSV4_OK;
+    if (!topk_indices || !query_start_loc || !seq_lens || !gather_lens || !combined || !lens) return DSV4_ERR_NULL_POINTER;
+    return static_cast<int>(launch_combine_topk_swa(topk_indices, topk_stride, static_cast<int>(topk_width), query_start_loc, seq_lens,
+                                                    gather_lens, combined, combined_stride, static_cast<int>(combined_width), lens,
+                                                    num_reqs, num_tokens, static_cast<int>(window_size),
+                                                    static_cast<int>(compress_ratio), static_cast<int>(topk), static_cast<int>(M),
+                                                    static_cast<int>(N), static_cast<cudaStream_t>(cuda_stream)));
+}
+
 int dsv4_fused_indexer_q_rope_quant(const int64_t* positions, const void* index_q, int64_t q_stride0, int64_t q_stride1,
                                     const void* cos_sin_cache, int64_t cos_sin_stride, int32_t cos_sin_is_bf16, int64_t rot_dim,
                                     void* q_out, int64_t out_stride0, int64_t out_stride1, void* q_scales_out,

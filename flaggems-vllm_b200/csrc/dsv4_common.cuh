@@ -393,6 +393,13 @@ cudaError_t launch_cp_gather_indexer(const void* cache, int64_t block_stride, vo
                                      int64_t scale_out_stride, const int32_t* block_table, int64_t block_table_stride,
                                      const int32_t* cu_seqlen, int64_t batch, int64_t num_tokens, int64_t block_size, int head_dim,
                                      int num_quant_blocks, cudaStream_t stream);
+cudaError_t launch_global_topk(const int32_t* local, int64_t local_stride, const int32_t* token_to_req, const int32_t* block_table,
+                               int64_t block_table_stride, const int32_t* is_valid, int32_t* global, int64_t global_stride,
+                               int32_t* lens, int64_t num_tokens, int topk, int block_size, cudaStream_t stream);
+cudaError_t launch_combine_topk_swa(const int32_t* topk_indices, int64_t topk_stride, int topk_width, const int32_t* query_start_loc,
+                                    const int32_t* seq_lens, const int32_t* gather_lens, int32_t* combined, int64_t combined_stride,
+                                    int combined_width, int32_t* lens, int64_t num_reqs, int64_t num_tokens, int window,
+                                    int compress_ratio, int top_k, int m, int n, cudaStream_t stream);
 cudaError_t launch_indexer_q_rope_quant(const int64_t* positions, const void* q, int64_t q_stride0, int64_t q_stride1,
                                         const void* cos_sin, int64_t cos_sin_stride, int cos_sin_bf16, int rot_dim, void* out,
                                         int64_t out_stride0, int64_t out_stride1, void* scales, int64_t scale_stride0,

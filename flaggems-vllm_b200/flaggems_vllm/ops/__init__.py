@@ -1,5 +1,7 @@
 """Operators of this package (reference: src/flaggems_vllm/ops/__init__.py:61-63,191)."""
 from .cp_gather_indexer_k_quant_cache import cp_gather_indexer_k_quant_cache
+from .deepseek_v4_attention_combine_topk_swa_indices import combine_topk_swa_indices
+from .deepseek_v4_attention_compute_global_topk_indices_and_lens import compute_global_topk_indices_and_lens
 from .deepseek_v4_attention_dequantize_and_gather_k_cache import dequantize_and_gather_k_cache
 from .deepseek_v4_attention_fused_q_kv_rmsnorm import fused_q_kv_rmsnorm
 from .fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert import (
@@ -17,6 +19,8 @@ __all__ = [
     "fused_indexer_q_rope_quant",
     "indexer_k_quant_and_cache",
     "cp_gather_indexer_k_quant_cache",
+    "combine_topk_swa_indices",
+    "compute_global_topk_indices_and_lens",
     "fused_inv_rope_fp8_quant",
     "fused_q_kv_rmsnorm",
     "dequantize_and_gather_k_cache",

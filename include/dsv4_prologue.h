@@ -197,6 +197,37 @@ int dsv4_cp_gather_indexer_k_quant_cache(const void* k_cache, int64_t cache_bloc
                                          int64_t num_quant_blocks, void* cuda_stream);
 
 /*
+ * Top-k positions inside a request -> slots of the paged cache.  Replaces the reference operator
+ *   compute_global_topk_indices_and_lens(topk_indices, token_to_req_indices, block_table, block_size, is_valid_token)
+ * (src/flaggems_vllm/ops/deepseek_v4_attention_compute_global_topk_indices_and_lens.py:128-161, kernel :49-125):
+ * for token t and column i, p = topk_indices[t*topk_stride + i] (int32); global_indices[t*global_stride + i] =
+ * block_table[token_to_req[t]*block_table_stride + p / block_size] * block_size + p % block_size, or -1 when
+ * p < 0; lens[t] = number of non-negative entries of the row, 0 when is_valid_token[t] == 0 (is_valid_token may
+ * be NULL: every token valid).  Strides in elements.
+ */
+int dsv4_compute_global_topk_indices_and_lens(const int32_t* topk_indices, int64_t topk_stride, const int32_t* token_to_req,
+                                              const int32_t* block_table, int64_t block_table_stride, const int32_t* is_valid_token,
+                                              int32_t* global_indices, int64_t global_stride, int32_t* lens, int64_t num_tokens,
+                                              int64_t topk, int64_t block_size, void* cuda_stream);
+
+/*
+ * Rows of indices into the gathered key buffer for sparse prefill.  Replaces the reference operator
+ *   combine_topk_swa_indices(topk_indices, query_start_loc, seq_lens, gather_lens, window_size, compress_ratio, topk, M, N)
+ * (src/flaggems_vllm/ops/deepseek_v4_attention_combine_topk_swa_indices.py:109-161, kernel :30-106): query token t of
+ * request b (query_start_loc[b] - query_start_loc[0] <= t < query_start_loc[b+1] - query_start_loc[0]) sits at position
+ * pos = seq_lens[b] - query_len + (t - start); its row of combined_width int32 holds
+ *   topk_len = min((pos+1)/compress_ratio, topk) entries topk_indices[t, i] + M*b, then
+ *   swa_len = min(pos+1, window_size) entries M*b + N + j + pos - swa_len + 1 - (seq_lens[b] - gather_lens[b]),
+ *   then -1 up to combined_width; lens[t] = topk_len + swa_len.  Rows of tokens no request covers are not written.
+ * Requires topk <= topk_width and topk + window_size <= combined_width.  Strides in elements.
+ */
+int dsv4_combine_topk_swa_indices(const int32_t* topk_indices, int64_t topk_stride, int64_t topk_width,
+                                  const int32_t* query_start_loc, const int32_t* seq_lens, const int32_t* gather_lens,
+                                  int32_t* combined, int64_t combined_stride, int64_t combined_width, int32_t* lens,
+                                  int64_t num_reqs, int64_t num_tokens, int64_t window_size, int64_t compress_ratio, int64_t topk,
+                                  int64_t M, int64_t N, void* cuda_stream);
+
+/*
  * The sparse-indexer prologue.  Replaces the reference operator
  *   fused_indexer_q_rope_quant(positions, index_q, index_q_cos_sin_cache, index_weights,
  *                              index_weights_softmax_scale, index_weights_head_scale, use_fp4)

@@ -50,6 +50,10 @@ def lib() -> ctypes.CDLL:
         L.dsv4_oracle_indexer_k_quant.restype = i32
         L.dsv4_oracle_cp_gather_indexer.argtypes = [vp, i64, vp, i64, vp, i64, vp, i64, vp, i64, i64, i64, i64, i64]
         L.dsv4_oracle_cp_gather_indexer.restype = i32
+        L.dsv4_oracle_global_topk.argtypes = [vp, i64, vp, vp, i64, vp, vp, i64, vp, i64, i64, i64]
+        L.dsv4_oracle_global_topk.restype = i32
+        L.dsv4_oracle_combine_topk_swa.argtypes = [vp, i64, i64, vp, vp, vp, vp, i64, i64, vp, i64, i64, i64, i64, i64, i64, i64]
+        L.dsv4_oracle_combine_topk_swa.restype = i32
         L.dsv4_oracle_indexer_q_rope_quant.argtypes = [vp, vp, vp, i64, vp, f32, f32, i64, i64, i64, i32, vp, vp, vp]
         L.dsv4_oracle_indexer_q_rope_quant.restype = i32
         L.dsv4_oracle_check_division_shortcut.argtypes = [f32, vp, vp]
@@ -162,6 +166,42 @@ def cp_gather_indexer_k_quant_cache(k_cache, k_fp8, k_fp8_scale, block_table, cu
                                              block_table.shape[0], k_fp8.shape[0], k_cache.shape[1], head_dim, scale_bytes // 4)
     if rc != 0:
         raise ValueError("dsv4_oracle_cp_gather_indexer rejected its arguments")
+
+
+def compute_global_topk_indices_and_lens(topk_indices, token_to_req_indices, block_table, block_size, is_valid_token=None):
+    """Same arguments and return values as the reference operator, on CPU int32 tensors."""
+    for t in (topk_indices, token_to_req_indices, block_table) + (() if is_valid_token is None else (is_valid_token,)):
+        _cpu(t, torch.int32)
+    assert topk_indices.dim() == 2 and topk_indices.stride(1) == 1 and block_table.stride(1) == 1
+    out = torch.empty_like(topk_indices, dtype=torch.int32)
+    lens = torch.empty(topk_indices.shape[0], dtype=torch.int32)
+    rc = lib().dsv4_oracle_global_topk(topk_indices.data_ptr(), topk_indices.stride(0), token_to_req_indices.contiguous().data_ptr(),
+                                       block_table.data_ptr(), block_table.stride(0),
+                                       None if is_valid_token is None else is_valid_token.contiguous().data_ptr(), out.data_ptr(),
+                                       out.stride(0), lens.data_ptr(), topk_indices.shape[0], topk_indices.shape[1], int(block_size))
+    if rc != 0:
+        raise ValueError("dsv4_oracle_global_topk rejected its arguments")
+    return out, lens
+
+
+def combine_topk_swa_indices(topk_indices, query_start_loc, seq_lens, gather_lens, window_size, compress_ratio, topk, M, N, fill=None):
+    """Same arguments and return values as the reference operator, on CPU int32 tensors.  Rows that no request covers
+    keep `fill` (the reference leaves them uninitialised)."""
+    for t in (topk_indices, query_start_loc, seq_lens, gather_lens):
+        _cpu(t, torch.int32)
+    assert topk_indices.dim() == 2 and topk_indices.stride(1) == 1
+    width = (topk + window_size + 127) // 128 * 128
+    tokens = topk_indices.shape[0]
+    combined = torch.full((tokens, width), 0 if fill is None else fill, dtype=torch.int32)
+    lens = torch.full((tokens,), 0 if fill is None else fill, dtype=torch.int32)
+    rc = lib().dsv4_oracle_combine_topk_swa(topk_indices.data_ptr(), topk_indices.stride(0), topk_indices.shape[1],
+                                            query_start_loc.contiguous().data_ptr(), seq_lens.contiguous().data_ptr(),
+                                            gather_lens.contiguous().data_ptr(), combined.data_ptr(), combined.stride(0), width,
+                                            lens.data_ptr(), seq_lens.shape[0], tokens, int(window_size), int(compress_ratio), int(topk),
+                                            int(M), int(N))
+    if rc != 0:
+        raise ValueError("dsv4_oracle_combine_topk_swa rejected its arguments")
+    return combined, lens
 
 
 def indexer_q_rope_quant(positions, index_q, cos_sin_cache, weights, softmax_scale, head_scale, use_fp4=False):

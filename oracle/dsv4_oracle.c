@@ -477,6 +477,63 @@ int dsv4_oracle_cp_gather_indexer(const uint8_t* cache, int64_t block_stride, ui
     return 0;
 }
 
+/*
+ * Top-k positions inside a request -> cache slots, the expected-value loop of
+ * tests/test_deepseek_v4_attention_compute_global_topk_indices_and_lens.py:92-108
+ * (operator: src/flaggems_vllm/ops/deepseek_v4_attention_compute_global_topk_indices_and_lens.py:49-161).
+ * is_valid may be NULL (every token valid).  Strides in elements.
+ */
+int dsv4_oracle_global_topk(const int32_t* local, int64_t local_stride, const int32_t* token_to_req, const int32_t* block_table,
+                            int64_t block_table_stride, const int32_t* is_valid, int32_t* global, int64_t global_stride, int32_t* lens,
+                            int64_t num_tokens, int64_t topk, int64_t block_size) {
+    if (num_tokens < 0 || topk < 0 || block_size <= 0) return -1;
+    for (int64_t t = 0; t < num_tokens; ++t) {
+        int64_t req = token_to_req[t];
+        int32_t count = 0;
+        for (int64_t i = 0; i < topk; ++i) {
+            int64_t pos = local[t * local_stride + i];
+            if (pos >= 0) {
+                global[t * global_stride + i] = (int32_t)(block_table[req * block_table_stride + pos / block_size] * block_size + pos % block_size);
+                ++count;
+            } else {
+                global[t * global_stride + i] = -1;
+            }
+        }
+        lens[t] = (!is_valid || is_valid[t]) ? count : 0;
+    }
+    return 0;
+}
+
+/*
+ * Combined top-k / sliding-window index rows, the expected-value loop of
+ * tests/test_deepseek_v4_attention_combine_topk_swa_indices.py:129-152
+ * (operator: src/flaggems_vllm/ops/deepseek_v4_attention_combine_topk_swa_indices.py:30-161).
+ * Rows of tokens that no request covers are not written.  Positions are taken as non-negative.
+ */
+int dsv4_oracle_combine_topk_swa(const int32_t* topk_indices, int64_t topk_stride, int64_t topk_width, const int32_t* query_start_loc,
+                                 const int32_t* seq_lens, const int32_t* gather_lens, int32_t* combined, int64_t combined_stride,
+                                 int64_t combined_width, int32_t* lens, int64_t num_reqs, int64_t num_tokens, int64_t window,
+                                 int64_t compress_ratio, int64_t topk, int64_t m, int64_t n) {
+    if (num_reqs < 0 || compress_ratio <= 0 || topk > topk_width || topk + window > combined_width) return -1;
+    for (int64_t b = 0; b < num_reqs; ++b) {
+        int64_t start = query_start_loc[b] - query_start_loc[0], end = query_start_loc[b + 1] - query_start_loc[0];
+        int64_t start_pos = seq_lens[b] - (end - start), gather_start = seq_lens[b] - gather_lens[b];
+        for (int64_t t = start; t < end; ++t) {
+            if (t < 0 || t >= num_tokens) return -2;
+            int64_t pos = start_pos + (t - start);
+            if (pos < 0) return -3;
+            int64_t topk_len = (pos + 1) / compress_ratio < topk ? (pos + 1) / compress_ratio : topk;
+            int64_t swa_len = pos + 1 < window ? pos + 1 : window;
+            int32_t* row = combined + t * combined_stride;
+            for (int64_t c = 0; c < combined_width; ++c) row[c] = -1;
+            for (int64_t i = 0; i < topk_len; ++i) row[i] = (int32_t)(topk_indices[t * topk_stride + i] + m * b);
+            for (int64_t j = 0; j < swa_len; ++j) row[topk_len + j] = (int32_t)(m * b + n + j + pos - swa_len + 1 - gather_start);
+            lens[t] = (int32_t)(topk_len + swa_len);
+        }
+    }
+    return 0;
+}
+
 /* e2m1 code of |v| <= 6 with the tie rule of tests/test_fused_indexer_q_rope_quant.py:81-92 (nearest, ties to even). */
 static inline uint8_t e2m1_code(float v) {
     float a = fabsf(v);

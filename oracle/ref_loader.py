@@ -68,12 +68,14 @@ def load_upstream_test_module():
 
 
 def load_upstream_helper_test(test_file: str, op_module: str, op_names: tuple[str, ...], package_attrs: dict | None = None,
-                               sibling_modules: dict | None = None):
+                               sibling_modules: dict | None = None, op_bindings: dict | None = None):
     """Execute another upstream test file (e.g. tests/test_deepseek_v4_attention_*.py) with stand-ins for
     the package names it imports, to reach the pure-torch helpers it defines (expected-value builders,
     reference functions).  `op_module` is the dotted module the test imports its operator from;
     `package_attrs` are extra attributes of the stand-in `flaggems_vllm`; `sibling_modules` maps names of
-    modules the test imports relatively (e.g. "accuracy_utils") to attribute dicts."""
+    modules the test imports relatively (e.g. "accuracy_utils") to attribute dicts; `op_bindings` maps operator
+    names to CPU callables that take the operator's place (the way a restatement is run through the upstream
+    test's own expected-value code), the others raise when called."""
     root = upstream_root()
     if root is None or not (root / "tests" / test_file).exists():
         raise FileNotFoundError("upstream tree not present")
@@ -92,17 +94,22 @@ def load_upstream_helper_test(test_file: str, op_module: str, op_names: tuple[st
 
     import torch
 
-    testing = mod("flaggems_vllm.testing", assert_close=lambda a, b, dtype=None, equal_nan=False, **k: torch.testing.assert_close(a, b, equal_nan=equal_nan))
+    def assert_equal(a, b, **_k):
+        assert torch.equal(a, b), "tensors differ"
+
+    testing = mod("flaggems_vllm.testing", assert_equal=assert_equal,
+                  assert_close=lambda a, b, dtype=None, equal_nan=False, **k: torch.testing.assert_close(a, b, equal_nan=equal_nan))
     pkg = mod("flaggems_vllm", device="cpu", vendor_name="nvidia", testing=testing, __path__=[])
     mod("flaggems_vllm.ops", __path__=[])
     ops_pkg = sys.modules["flaggems_vllm.ops"]
+    bound = {n: (op_bindings or {}).get(n, _unbound) for n in op_names}
     for n in op_names:
-        setattr(ops_pkg, n, _unbound)
-        setattr(pkg, n, _unbound)
+        setattr(ops_pkg, n, bound[n])
+        setattr(pkg, n, bound[n])
     for k, v in (package_attrs or {}).items():
         setattr(pkg, k, v)
     if op_module != "flaggems_vllm.ops":
-        mod(op_module, **{n: _unbound for n in op_names})
+        mod(op_module, **bound)
     mod("flaggems_vllm.utils", __path__=[])
     mod("flaggems_vllm.utils.device_info", get_device_capability=lambda: (10, 0))
     mod("_dsv4_upstream_tests", __path__=[])

@@ -295,7 +295,68 @@ def cp_gather_cases() -> None:
         print(name, "ok")
 
 
+def _parameter_sets(test_function):
+    return [m for m in test_function.pytestmark if m.name == "parametrize"][0].args[1]
+
+
+def index_cases() -> None:
+    """The two index operators of the sparse attention.  Their upstream tests compute the expected values inline
+    (tests/test_deepseek_v4_attention_compute_global_topk_indices_and_lens.py:92-111,
+    tests/test_deepseek_v4_attention_combine_topk_swa_indices.py:129-155), so each case is RUN THROUGH THE UPSTREAM
+    TEST FUNCTION with the oracle bound in the operator's place: the function returns only if its own expected values
+    equal the oracle's output, which is then stored.  Cases: the tests' parameter sets and seeded larger ones."""
+    from oracle import c_oracle
+
+    G = ref_loader.load_upstream_helper_test(
+        "test_deepseek_v4_attention_compute_global_topk_indices_and_lens.py",
+        "flaggems_vllm.ops.deepseek_v4_attention_compute_global_topk_indices_and_lens", ("compute_global_topk_indices_and_lens",),
+        op_bindings={"compute_global_topk_indices_and_lens": c_oracle.compute_global_topk_indices_and_lens})
+    check = G.test_compute_global_topk_indices_and_lens_accuracy
+    cases = [tuple(a) for a in _parameter_sets(check)]
+    gen = torch.Generator().manual_seed(600)
+    for tokens, topk, reqs, blocks_per_req, bs in ((9, 12, 3, 5, 4), (17, 128, 4, 9, 64), (6, 33, 2, 7, 12)):
+        local = torch.randint(0, blocks_per_req * bs, (tokens, topk), generator=gen, dtype=torch.int32)
+        local[torch.rand(tokens, topk, generator=gen) < 0.3] = -1
+        local[0] = -1
+        table = torch.randperm(reqs * blocks_per_req, generator=gen).to(torch.int32).view(reqs, blocks_per_req)
+        cases.append((local.tolist(), torch.randint(0, reqs, (tokens,), generator=gen).tolist(), table.tolist(),
+                      (torch.rand(tokens, generator=gen) < 0.7).int().tolist(), bs))
+    for idx, (local, req, table, valid, bs) in enumerate(cases):
+        check(local, req, table, valid, bs)  # raises if the oracle differs from the upstream expectation
+        t = lambda v: torch.tensor(v, dtype=torch.int32)
+        out, lens = c_oracle.compute_global_topk_indices_and_lens(t(local), t(req), t(table), bs, t(valid))
+        np.savez_compressed(HERE / f"global_topk_{idx}.npz", topk_indices=t(local).numpy(), token_to_req=t(req).numpy(),
+                            block_table=t(table).numpy(), is_valid=t(valid).numpy(), block_size=bs, global_indices=out.numpy(),
+                            lens=lens.numpy())
+        print("global_topk", idx, "ok")
+
+    C = ref_loader.load_upstream_helper_test("test_deepseek_v4_attention_combine_topk_swa_indices.py", "flaggems_vllm.ops",
+                                             ("combine_topk_swa_indices",),
+                                             op_bindings={"combine_topk_swa_indices": c_oracle.combine_topk_swa_indices})
+    check = C.test_combine_topk_swa_indices_accuracy
+    cases = [tuple(a) for a in _parameter_sets(check)]
+    gen = torch.Generator().manual_seed(601)
+    for query_lens, window, ratio, topk, width, m, n in (([5, 1, 9], 8, 4, 16, 16, 300, 40), ([3, 7, 2, 12], 128, 4, 64, 64, 4096, 1024),
+                                                         ([20], 5, 3, 6, 9, 50, 7)):
+        tokens = sum(query_lens)
+        start = [100] + (100 + torch.cumsum(torch.tensor(query_lens), 0)).tolist()  # a non-zero first entry is subtracted
+        seq = [q + int(torch.randint(0, 60, (1,), generator=gen)) for q in query_lens]
+        gather = [min(s, q + int(torch.randint(0, 30, (1,), generator=gen))) for s, q in zip(seq, query_lens)]
+        cases.append((torch.randint(0, m - 1, (tokens, width), generator=gen, dtype=torch.int32).tolist(), start, seq, gather, window,
+                      ratio, topk, m, n))
+    for idx, (values, start, seq, gather, window, ratio, topk, m, n) in enumerate(cases):
+        check(values, start, seq, gather, window, ratio, topk, m, n)
+        t = lambda v: torch.tensor(v, dtype=torch.int32)
+        combined, lens = c_oracle.combine_topk_swa_indices(t(values), t(start), t(seq), t(gather), window, ratio, topk, m, n)
+        np.savez_compressed(HERE / f"combine_topk_swa_{idx}.npz", topk_indices=t(values).numpy(), query_start_loc=t(start).numpy(),
+                            seq_lens=t(seq).numpy(), gather_lens=t(gather).numpy(), window_size=window, compress_ratio=ratio, topk=topk,
+                            M=m, N=n, combined=combined.numpy(), lens=lens.numpy())
+        print("combine_topk_swa", idx, "ok")
+
+
 if __name__ == "__main__":
+    if len(sys.argv) < 2 or sys.argv[1] == "index":
+        index_cases()
     if len(sys.argv) < 2 or sys.argv[1] == "cp_gather":
         cp_gather_cases()
     if len(sys.argv) < 2 or sys.argv[1] == "indexer_q":

@@ -79,3 +79,22 @@ def test_sibling_oracles_against_upstream_helpers():
     got_k, got_s = torch.full_like(want_k, 0x7B), torch.full_like(want_s, 0x7B)
     c_oracle.cp_gather_indexer_k_quant_cache(cache, got_k, got_s, table, cu)
     assert torch.equal(got_k, want_k) and torch.equal(got_s, want_s)
+
+
+def test_index_oracles_pass_the_upstream_tests():
+    """The upstream tests of the two index operators compute their expected values inline, so the oracles are bound in
+    the operators' place and the upstream test functions are run on fresh seeded inputs."""
+    g = torch.Generator().manual_seed(77)
+    G = ref_loader.load_upstream_helper_test(
+        "test_deepseek_v4_attention_compute_global_topk_indices_and_lens.py",
+        "flaggems_vllm.ops.deepseek_v4_attention_compute_global_topk_indices_and_lens", ("compute_global_topk_indices_and_lens",),
+        op_bindings={"compute_global_topk_indices_and_lens": c_oracle.compute_global_topk_indices_and_lens})
+    local = torch.randint(-20, 640, (25, 48), generator=g, dtype=torch.int32).clamp(min=-1)
+    G.test_compute_global_topk_indices_and_lens_accuracy(
+        local.tolist(), torch.randint(0, 3, (25,), generator=g).tolist(), torch.randperm(30, generator=g).view(3, 10).tolist(),
+        (torch.rand(25, generator=g) < 0.6).int().tolist(), 64)
+    C = ref_loader.load_upstream_helper_test("test_deepseek_v4_attention_combine_topk_swa_indices.py", "flaggems_vllm.ops",
+                                             ("combine_topk_swa_indices",),
+                                             op_bindings={"combine_topk_swa_indices": c_oracle.combine_topk_swa_indices})
+    C.test_combine_topk_swa_indices_accuracy(torch.randint(0, 900, (30, 32), generator=g, dtype=torch.int32).tolist(), [4, 14, 15, 34],
+                                             [50, 1, 33], [20, 1, 30], 16, 4, 32, 1000, 200)

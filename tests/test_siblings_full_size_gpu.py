@@ -101,3 +101,28 @@ def test_indexer_cache_reader_one_million_tokens():
     want_k, want_s = torch.full((tokens, 128), 0x7B, dtype=torch.uint8), torch.full((tokens, 4), 0x7B, dtype=torch.uint8)
     c_oracle.cp_gather_indexer_k_quant_cache(cache.cpu(), want_k, want_s, table.cpu(), cu.cpu())
     assert torch.equal(k.cpu(), want_k) and torch.equal(s.cpu(), want_s)
+
+
+def test_index_operators_32768_tokens():
+    g = gen(7)
+    n, reqs = 32768, 16
+    local = torch.randint(0, 65536, (n, 2048), generator=g, device=DEV, dtype=torch.int32)
+    local[torch.rand(n, 2048, generator=g, device=DEV) < 0.1] = -1
+    req = torch.randint(0, reqs, (n,), generator=g, device=DEV, dtype=torch.int32)
+    table = torch.randperm(reqs * 1024, generator=g, device=DEV).to(torch.int32).view(reqs, 1024).contiguous()
+    valid = (torch.rand(n, generator=g, device=DEV) < 0.9).to(torch.int32)
+    got, lens = flaggems_vllm.compute_global_topk_indices_and_lens(local, req, table, 64, valid)
+    want, want_lens = c_oracle.compute_global_topk_indices_and_lens(local.cpu(), req.cpu(), table.cpu(), 64, valid.cpu())
+    assert torch.equal(got.cpu(), want) and torch.equal(lens.cpu(), want_lens)
+    del local, got
+    values = torch.randint(0, 8192, (n, 512), generator=g, device=DEV, dtype=torch.int32)
+    cg = torch.Generator().manual_seed(7)
+    q_lens = torch.randint(1, n // reqs, (reqs,), generator=cg)  # ragged requests; the last one takes the rest
+    q_lens[-1] = n - int(q_lens[:-1].sum())
+    start = torch.zeros(reqs + 1, dtype=torch.int32)
+    start[1:] = torch.cumsum(q_lens, 0)
+    seq = (q_lens + torch.randint(0, 3000, (reqs,), generator=cg)).to(torch.int32)
+    gather = torch.minimum(seq, (q_lens + 128).to(torch.int32))
+    got, lens = flaggems_vllm.combine_topk_swa_indices(values, start.to(DEV), seq.to(DEV), gather.to(DEV), 128, 4, 512, 8192, 2048)
+    want, want_lens = c_oracle.combine_topk_swa_indices(values.cpu(), start, seq, gather, 128, 4, 512, 8192, 2048)
+    assert torch.equal(got.cpu(), want) and torch.equal(lens.cpu(), want_lens)
