@@ -295,6 +295,23 @@ def cp_gather_cases() -> None:
         print(name, "ok")
 
 
+def flash_mla_builder_case() -> None:
+    """A cache made by the independent statement of the format and quantiser in the upstream FlashMLA test
+    (`generate_model1_fp8_kv_cache`, tests/test_flash_mla_with_kvcache.py:94-140), with the keys it drew
+    (same seed, same order of draws: 448 unrotated values, then the 64 rotary ones, both randn * 0.1)."""
+    F = ref_loader.load_upstream_helper_test("test_flash_mla_with_kvcache.py", "flaggems_vllm.ops.flash_mla_with_kvcache",
+                                             ("FlashMLASchedMeta", "flash_mla_with_kvcache", "get_mla_metadata"))
+    pages, bs = 3, 16
+    torch.manual_seed(700)
+    cache = F.generate_model1_fp8_kv_cache(pages, bs, device="cpu").view(pages, bs * 584)
+    torch.manual_seed(700)
+    nope = torch.randn(pages * bs, 448, dtype=torch.bfloat16) * 0.1
+    rope = torch.randn(pages * bs, 64, dtype=torch.bfloat16) * 0.1
+    np.savez_compressed(HERE / "flash_mla_builder_cache.npz", kv=u16(torch.cat([nope, rope], dim=1).contiguous()), cache=cache.numpy(),
+                        block_size=bs)
+    print("flash_mla_builder_cache ok")
+
+
 def _parameter_sets(test_function):
     return [m for m in test_function.pytestmark if m.name == "parametrize"][0].args[1]
 
@@ -355,6 +372,8 @@ def index_cases() -> None:
 
 
 if __name__ == "__main__":
+    if len(sys.argv) < 2 or sys.argv[1] == "flash_mla":
+        flash_mla_builder_case()
     if len(sys.argv) < 2 or sys.argv[1] == "index":
         index_cases()
     if len(sys.argv) < 2 or sys.argv[1] == "cp_gather":

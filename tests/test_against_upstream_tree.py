@@ -98,3 +98,25 @@ def test_index_oracles_pass_the_upstream_tests():
                                              op_bindings={"combine_topk_swa_indices": c_oracle.combine_topk_swa_indices})
     C.test_combine_topk_swa_indices_accuracy(torch.randint(0, 900, (30, 32), generator=g, dtype=torch.int32).tolist(), [4, 14, 15, 34],
                                              [50, 1, 33], [20, 1, 30], 16, 4, 32, 1000, 200)
+
+
+def test_prologue_oracles_against_the_upstream_flash_mla_cache_builder():
+    """A second, independent statement of the cache format and of the UE8M0 quantiser lives in the upstream FlashMLA
+    test (tests/test_flash_mla_with_kvcache.py:94-140, `generate_model1_fp8_kv_cache`).  It draws its own keys; the
+    same draws are repeated here, pushed through the oracles with an identity rotation, and the caches compared."""
+    F = ref_loader.load_upstream_helper_test("test_flash_mla_with_kvcache.py", "flaggems_vllm.ops.flash_mla_with_kvcache",
+                                             ("FlashMLASchedMeta", "flash_mla_with_kvcache", "get_mla_metadata"))
+    pages, bs = 5, 64
+    torch.manual_seed(123)
+    want = F.generate_model1_fp8_kv_cache(pages, bs, device="cpu").view(pages, bs * 584)
+    torch.manual_seed(123)
+    nope = torch.randn(pages * bs, 448, dtype=torch.bfloat16) * 0.1
+    rope = torch.randn(pages * bs, 64, dtype=torch.bfloat16) * 0.1
+    kv = torch.cat([nope, rope], dim=1).contiguous()
+    n = pages * bs
+    table = torch.cat([torch.ones(4, 32), torch.zeros(4, 32)], dim=1).contiguous()  # cos = 1, sin = 0: rotation is the identity
+    for run in (c_oracle.prologue, torch_path.prologue):
+        q = torch.randn(n, 1, 512).to(torch.bfloat16)
+        cache = torch.zeros(pages, bs * 584, dtype=torch.uint8)
+        run(q, kv, cache, torch.arange(n), torch.zeros(n, dtype=torch.int64), table, 1e-6, bs)
+        assert torch.equal(cache, want)

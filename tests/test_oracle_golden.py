@@ -122,3 +122,16 @@ def test_gather_dequant_oracle_inverts_the_insert(golden_case):
     # e4m3 keeps 3 mantissa bits: relative error <= 2^-4, plus half a subnormal step (2^-10) of the scale
     err = (rows[:, :448].float() - kv_valid).abs()
     assert bool((err <= kv_valid.abs() * 2.0 ** -4 + scale * 2.0 ** -10 + 1e-30).all())
+
+
+def test_oracles_reproduce_the_upstream_flash_mla_cache_builder():
+    """An independent upstream statement of the cache format and quantiser (the FlashMLA test's cache builder): with an
+    identity rotation (cos 1, sin 0) the oracles must produce its cache byte for byte from the keys it drew."""
+    z = np.load(GOLDEN / "flash_mla_builder_cache.npz")
+    kv = torch.from_numpy(z["kv"].view(np.int16).copy()).view(torch.bfloat16)
+    want, bs, n = torch.from_numpy(z["cache"].copy()), int(z["block_size"]), kv.shape[0]
+    table = torch.cat([torch.ones(2, 32), torch.zeros(2, 32)], dim=1).contiguous()
+    for run in (c_oracle.prologue, torch_path.prologue):
+        cache = torch.zeros_like(want)
+        run(torch.ones(n, 1, 512, dtype=torch.bfloat16), kv, cache, torch.arange(n), torch.zeros(n, dtype=torch.int64), table, 1e-6, bs)
+        assert torch.equal(cache, want)

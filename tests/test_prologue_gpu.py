@@ -487,3 +487,21 @@ def test_direct_c_abi_calls():
     assert torch.equal(kc.cpu(), kc_ref)
     compare.assert_q_close(q.cpu(), q_ref)
     assert lib.dsv4_error_string(-3).decode().startswith("q, kv")
+
+
+def test_kernel_reproduces_the_upstream_flash_mla_cache_builder():
+    """Same independent upstream statement of the cache format (see tests/test_oracle_golden.py), both kernel variants."""
+    z = np.load(GOLDEN / "flash_mla_builder_cache.npz")
+    kv = torch.from_numpy(z["kv"].view(np.int16).copy()).view(torch.bfloat16).to("cuda:0")
+    want, bs, n = torch.from_numpy(z["cache"].copy()), int(z["block_size"]), kv.shape[0]
+    table = torch.cat([torch.ones(2, 32), torch.zeros(2, 32)], dim=1).contiguous().to("cuda:0")
+    for variant in (1, 2):
+        previous = _native.set_variant(variant)
+        try:
+            cache = torch.zeros_like(want).to("cuda:0")
+            flaggems_vllm.fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert(
+                torch.ones(n, 1, 512, dtype=torch.bfloat16, device="cuda:0"), kv, cache, torch.arange(n, device="cuda:0"),
+                torch.zeros(n, dtype=torch.int64, device="cuda:0"), table, 1e-6, bs)
+            assert torch.equal(cache.cpu(), want)
+        finally:
+            _native.set_variant(previous)
