@@ -272,6 +272,40 @@ int dsv4_combine_topk_swa_indices(const int32_t* topk_indices, int64_t topk_stri
                                                     static_cast<int>(N), static_cast<cudaStream_t>(cuda_stream)));
 }
 
+namespace {
+int check_topk_sizes(const float* logits, const int32_t* indices, int64_t num_rows, int64_t vocab, int64_t top_k) {
+    const int64_t lim = 1LL << 31;
+    if (num_rows < 0 || num_rows >= lim || vocab < 0 || vocab >= lim || top_k < 0 || top_k >= lim) return DSV4_ERR_BAD_SIZE;
+    if (num_rows > 0 && top_k > 0 && (!logits || !indices)) return DSV4_ERR_NULL_POINTER;
+    if ((reinterpret_cast<uintptr_t>(logits) & 3u) != 0 || (reinterpret_cast<uintptr_t>(indices) & 3u) != 0) return DSV4_ERR_MISALIGNED;
+    return DSV4_OK;
+}
+}  // namespace
+
+int dsv4_top_k_per_row_decode(const float* logits, int64_t stride0, int64_t stride1, int64_t next_n, const int32_t* seq_lens,
+                              int32_t* indices, int64_t num_rows, int64_t vocab, int64_t top_k, void* cuda_stream) {
+    const int rc = check_topk_sizes(logits, indices, num_rows, vocab, top_k);
+    if (rc != DSV4_OK) return rc;
+    if (next_n <= 0 || next_n >= (1LL << 31)) return DSV4_ERR_BAD_SIZE;
+    if (num_rows == 0 || top_k == 0) return DSV4_OK;
+    if (!seq_lens) return DSV4_ERR_NULL_POINTER;
+    return static_cast<int>(launch_topk_per_row(logits, stride0, stride1, indices, num_rows, static_cast<int>(vocab),
+                                                static_cast<int>(top_k), seq_lens, static_cast<int>(next_n), nullptr, nullptr,
+                                                static_cast<cudaStream_t>(cuda_stream)));
+}
+
+int dsv4_top_k_per_row_prefill(const float* logits, int64_t stride0, int64_t stride1, const int32_t* row_starts,
+                               const int32_t* row_ends, int32_t* indices, int64_t num_rows, int64_t vocab, int64_t top_k,
+                               void* cuda_stream) {
+    const int rc = check_topk_sizes(logits, indices, num_rows, vocab, top_k);
+    if (rc != DSV4_OK) return rc;
+    if (num_rows == 0 || top_k == 0) return DSV4_OK;
+    if (!row_starts || !row_ends) return DSV4_ERR_NULL_POINTER;
+    return static_cast<int>(launch_topk_per_row(logits, stride0, stride1, indices, num_rows, static_cast<int>(vocab),
+                                                static_cast<int>(top_k), nullptr, 1, row_starts, row_ends,
+                                                static_cast<cudaStream_t>(cuda_stream)));
+}
+
 int dsv4_fused_indexer_q_rope_quant(const int64_t* positions, const void* index_q, int64_t q_stride0, int64_t q_stride1,
                                     const void* cos_sin_cache, int64_t cos_sin_stride, int32_t cos_sin_is_bf16, int64_t rot_dim,
                                     void* q_out, int64_t out_stride0, int64_t out_stride1, void* q_scales_out,

@@ -400,6 +400,9 @@ cudaError_t launch_combine_topk_swa(const int32_t* topk_indices, int64_t topk_st
                                     const int32_t* seq_lens, const int32_t* gather_lens, int32_t* combined, int64_t combined_stride,
                                     int combined_width, int32_t* lens, int64_t num_reqs, int64_t num_tokens, int window,
                                     int compress_ratio, int top_k, int m, int n, cudaStream_t stream);
+cudaError_t launch_topk_per_row(const float* logits, int64_t stride0, int64_t stride1, int32_t* indices, int64_t num_rows, int vocab,
+                                int top_k, const int32_t* seq_lens, int next_n, const int32_t* row_starts, const int32_t* row_ends,
+                                cudaStream_t stream);
 cudaError_t launch_indexer_q_rope_quant(const int64_t* positions, const void* q, int64_t q_stride0, int64_t q_stride1,
                                         const void* cos_sin, int64_t cos_sin_stride, int cos_sin_bf16, int rot_dim, void* out,
                                         int64_t out_stride0, int64_t out_stride1, void* scales, int64_t scale_stride0,

@@ -24,6 +24,8 @@ EXPORTS = (
     "dsv4_cp_gather_indexer_k_quant_cache",
     "dsv4_compute_global_topk_indices_and_lens",
     "dsv4_combine_topk_swa_indices",
+    "dsv4_top_k_per_row_decode",
+    "dsv4_top_k_per_row_prefill",
     "dsv4_fused_indexer_q_rope_quant",
     "dsv4_hbm_probe",
     "dsv4_device_error",
@@ -85,6 +87,10 @@ def lib() -> ctypes.CDLL:
     L.dsv4_compute_global_topk_indices_and_lens.restype = i32
     L.dsv4_combine_topk_swa_indices.argtypes = [vp, i64, i64, vp, vp, vp, vp, i64, i64, vp, i64, i64, i64, i64, i64, i64, i64, vp]
     L.dsv4_combine_topk_swa_indices.restype = i32
+    L.dsv4_top_k_per_row_decode.argtypes = [vp, i64, i64, i64, vp, vp, i64, i64, i64, vp]
+    L.dsv4_top_k_per_row_decode.restype = i32
+    L.dsv4_top_k_per_row_prefill.argtypes = [vp, i64, i64, vp, vp, vp, i64, i64, i64, vp]
+    L.dsv4_top_k_per_row_prefill.restype = i32
     L.dsv4_fused_indexer_q_rope_quant.argtypes = [vp, vp, i64, i64, vp, i64, i32, i64, vp, i64, i64, vp, i64, i64, vp, i64, i32,
                                                   vp, i64, f32, f32, i64, i64, i64, i32, vp]
     L.dsv4_fused_indexer_q_rope_quant.restype = i32

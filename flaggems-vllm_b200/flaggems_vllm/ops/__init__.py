@@ -14,6 +14,8 @@ from .fused_inv_rope_fp8_quant import fused_inv_rope_fp8_quant
 from .gather_dequant_k_cache import gather_dequant_k_cache_slots
 from .host_staged import HostStagedPrologue
 from .indexer_k_quant_and_cache import indexer_k_quant_and_cache
+from .top_k_per_row_decode import top_k_per_row_decode
+from .top_k_per_row_prefill import top_k_per_row_prefill
 
 __all__ = [
     "fused_indexer_q_rope_quant",
@@ -21,6 +23,8 @@ __all__ = [
     "cp_gather_indexer_k_quant_cache",
     "combine_topk_swa_indices",
     "compute_global_topk_indices_and_lens",
+    "top_k_per_row_decode",
+    "top_k_per_row_prefill",
     "fused_inv_rope_fp8_quant",
     "fused_q_kv_rmsnorm",
     "dequantize_and_gather_k_cache",

@@ -228,6 +228,24 @@ int dsv4_combine_topk_swa_indices(const int32_t* topk_indices, int64_t topk_stri
                                   int64_t M, int64_t N, void* cuda_stream);
 
 /*
+ * Top-k selection of the sparse indexer.  Replace the reference operators
+ *   top_k_per_row_decode(logits, next_n, seq_lens, indices, num_rows, stride0, stride1, top_k)
+ *   top_k_per_row_prefill(logits, row_starts, row_ends, indices, num_rows, stride0, stride1, top_k)
+ * (src/flaggems_vllm/ops/top_k_per_row_decode.py:1263-1399, src/flaggems_vllm/ops/top_k_per_row_prefill.py, wrapper
+ * `top_k_per_row_prefill`): for row i of logits (fp32 [num_rows, vocab], element strides) and its range
+ * [start, end) - decode: start = 0, end = seq_lens[i / next_n] - next_n + i % next_n + 1; prefill: row_starts[i],
+ * row_ends[i]; both clipped to [0, vocab] - indices[i*top_k + j], j < k = min(top_k, end - start), are the positions
+ * relative to start of the k largest values in any order (ties broken arbitrarily), the remaining entries are -1.
+ * The selection orders values by their bit patterns: a NaN with the sign bit clear ranks above +inf, one with the
+ * sign bit set below -inf.
+ */
+int dsv4_top_k_per_row_decode(const float* logits, int64_t stride0, int64_t stride1, int64_t next_n, const int32_t* seq_lens,
+                              int32_t* indices, int64_t num_rows, int64_t vocab, int64_t top_k, void* cuda_stream);
+int dsv4_top_k_per_row_prefill(const float* logits, int64_t stride0, int64_t stride1, const int32_t* row_starts,
+                               const int32_t* row_ends, int32_t* indices, int64_t num_rows, int64_t vocab, int64_t top_k,
+                               void* cuda_stream);
+
+/*
  * The sparse-indexer prologue.  Replaces the reference operator
  *   fused_indexer_q_rope_quant(positions, index_q, index_q_cos_sin_cache, index_weights,
  *                              index_weights_softmax_scale, index_weights_head_scale, use_fp4)

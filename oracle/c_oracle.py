@@ -54,6 +54,8 @@ def lib() -> ctypes.CDLL:
         L.dsv4_oracle_global_topk.restype = i32
         L.dsv4_oracle_combine_topk_swa.argtypes = [vp, i64, i64, vp, vp, vp, vp, i64, i64, vp, i64, i64, i64, i64, i64, i64, i64]
         L.dsv4_oracle_combine_topk_swa.restype = i32
+        L.dsv4_oracle_top_k_per_row.argtypes = [vp, i64, i64, vp, vp, vp, i64, i64, i64]
+        L.dsv4_oracle_top_k_per_row.restype = i32
         L.dsv4_oracle_indexer_q_rope_quant.argtypes = [vp, vp, vp, i64, vp, f32, f32, i64, i64, i64, i32, vp, vp, vp]
         L.dsv4_oracle_indexer_q_rope_quant.restype = i32
         L.dsv4_oracle_check_division_shortcut.argtypes = [f32, vp, vp]
@@ -202,6 +204,24 @@ def combine_topk_swa_indices(topk_indices, query_start_loc, seq_lens, gather_len
     if rc != 0:
         raise ValueError("dsv4_oracle_combine_topk_swa rejected its arguments")
     return combined, lens
+
+
+def top_k_per_row_prefill(logits, row_starts, row_ends, indices, num_rows, stride0, stride1, top_k) -> None:
+    """Same arguments as the reference operator, on CPU tensors; fills `indices` [num_rows, top_k] int32."""
+    _cpu(row_starts, torch.int32), _cpu(row_ends, torch.int32), _cpu(indices, torch.int32)
+    assert logits.device.type == "cpu" and logits.dtype == torch.float32  # any strides
+    assert indices.is_contiguous() and indices.shape[1] == top_k and logits.dim() == 2 and num_rows == logits.shape[0]
+    rc = lib().dsv4_oracle_top_k_per_row(logits.data_ptr(), logits.stride(0), logits.stride(1), row_starts.contiguous().data_ptr(),
+                                         row_ends.contiguous().data_ptr(), indices.data_ptr(), num_rows, logits.shape[1], int(top_k))
+    if rc != 0:
+        raise ValueError("dsv4_oracle_top_k_per_row rejected its arguments")
+
+
+def top_k_per_row_decode(logits, next_n, seq_lens, indices, num_rows, stride0, stride1, top_k) -> None:
+    """Same arguments as the reference operator, on CPU tensors: row i covers [0, seq_lens[i // next_n] - next_n + i % next_n + 1)."""
+    rows = torch.arange(num_rows)
+    ends = (seq_lens.to(torch.int64)[rows // next_n] - next_n + rows % next_n + 1).to(torch.int32)
+    top_k_per_row_prefill(logits, torch.zeros(num_rows, dtype=torch.int32), ends, indices, num_rows, stride0, stride1, top_k)
 
 
 def indexer_q_rope_quant(positions, index_q, cos_sin_cache, weights, softmax_scale, head_scale, use_fp4=False):

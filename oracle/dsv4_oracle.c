@@ -18,6 +18,7 @@
  */
 #include <math.h>
 #include <stdint.h>
+#include <stdlib.h>
 #include <string.h>
 #ifdef _OPENMP
 #include <omp.h>
@@ -531,6 +532,35 @@ int dsv4_oracle_combine_topk_swa(const int32_t* topk_indices, int64_t topk_strid
             lens[t] = (int32_t)(topk_len + swa_len);
         }
     }
+    return 0;
+}
+
+/*
+ * Top-k positions per row, the torch statements tests/test_top_k_per_row_decode.py:111-124 and
+ * tests/test_top_k_per_row_prefill.py:80-99 (torch.topk on the valid range of each row): the k = min(top_k, len)
+ * largest values by a full sort (ties: lower position first), positions relative to the range start, then -1.
+ * The upstream tests compare the selected VALUES as multisets, not the positions.
+ */
+typedef struct { float v; int32_t i; } oracle_pair;
+static int oracle_pair_desc(const void* a, const void* b) {
+    const oracle_pair *x = (const oracle_pair*)a, *y = (const oracle_pair*)b;
+    if (x->v > y->v) return -1;
+    if (x->v < y->v) return 1;
+    return x->i < y->i ? -1 : (x->i > y->i ? 1 : 0);
+}
+int dsv4_oracle_top_k_per_row(const float* logits, int64_t stride0, int64_t stride1, const int32_t* starts, const int32_t* ends,
+                              int32_t* indices, int64_t num_rows, int64_t vocab, int64_t top_k) {
+    if (num_rows < 0 || vocab < 0 || top_k < 0) return -1;
+    oracle_pair* buf = (oracle_pair*)malloc((size_t)(vocab > 0 ? vocab : 1) * sizeof(oracle_pair));
+    if (!buf) return -2;
+    for (int64_t r = 0; r < num_rows; ++r) {
+        int64_t s = starts[r] < 0 ? 0 : starts[r], e = ends[r] > vocab ? vocab : ends[r];
+        int64_t len = e > s ? e - s : 0, k = len < top_k ? len : top_k;
+        for (int64_t i = 0; i < len; ++i) buf[i].v = logits[r * stride0 + (s + i) * stride1], buf[i].i = (int32_t)i;
+        qsort(buf, (size_t)len, sizeof(oracle_pair), oracle_pair_desc);
+        for (int64_t j = 0; j < top_k; ++j) indices[r * top_k + j] = j < k ? buf[j].i : -1;
+    }
+    free(buf);
     return 0;
 }
 

@@ -312,6 +312,51 @@ def flash_mla_builder_case() -> None:
     print("flash_mla_builder_cache ok")
 
 
+def topk_cases() -> None:
+    """Seeded logits through the upstream tests' torch statements `_torch_topk_ref`
+    (tests/test_top_k_per_row_decode.py:111-124) and `reference_top_k_per_row` (tests/test_top_k_per_row_prefill.py:80-99).
+    Stored: logits, ranges, and the SORTED VALUES the reference selected per row (its tests compare selected values, not
+    positions: ties are broken arbitrarily), with -inf where a row has fewer than top_k valid entries."""
+    D = ref_loader.load_upstream_helper_test("test_top_k_per_row_decode.py", "flaggems_vllm.ops.top_k_per_row_decode", ("top_k_per_row_decode",),
+                                             package_attrs={"runtime": types_namespace()})
+    P = ref_loader.load_upstream_helper_test("test_top_k_per_row_prefill.py", "flaggems_vllm.ops.top_k_per_row_prefill", ("top_k_per_row_prefill",),
+                                             package_attrs={"runtime": types_namespace()})
+
+    def selected_values(logits, idx, starts):
+        out = torch.full(idx.shape, float("-inf"))
+        for r in range(idx.shape[0]):
+            valid = idx[r][idx[r] >= 0].long() + int(starts[r])
+            out[r, : valid.numel()] = logits[r, valid].sort(descending=True).values
+        return out
+
+    gen = torch.Generator().manual_seed(800)
+    for idx_case, (rows, vocab, top_k, next_n) in enumerate(((3, 700, 64, 1), (4, 3000, 512, 2), (2, 5000, 128, 1))):
+        logits = torch.randn(rows, vocab, generator=gen)
+        if idx_case == 2:  # many ties and a block of near-equal values (low 8 bits only differ)
+            logits[0, :3000] = 1.5
+            logits[1] = (0x3F900000 | torch.randint(0, 256, (vocab,), generator=gen, dtype=torch.int32)).view(torch.float32)
+        seq = torch.randint(top_k // 2, vocab, (-(-rows // next_n),), generator=gen, dtype=torch.int32)
+        ref = torch.zeros(rows, top_k, dtype=torch.int32)
+        D._torch_topk_ref(logits.clone(), next_n, seq, ref, rows, logits.stride(0), logits.stride(1), top_k)
+        np.savez_compressed(HERE / f"topk_decode_{idx_case}.npz", logits=logits.numpy(), seq_lens=seq.numpy(), next_n=next_n, top_k=top_k,
+                            values=selected_values(logits, ref, torch.zeros(rows)).numpy())
+        print("topk_decode", idx_case, "ok")
+    for idx_case, (rows, vocab, top_k) in enumerate(((5, 900, 64), (4, 257, 512), (6, 4000, 256))):
+        logits = torch.randn(rows, vocab, generator=gen)
+        starts = torch.randint(0, vocab // 2, (rows,), generator=gen, dtype=torch.int32)
+        ends = torch.minimum(starts + torch.randint(1, vocab, (rows,), generator=gen, dtype=torch.int32), torch.tensor(vocab, dtype=torch.int32))
+        ref = P.reference_top_k_per_row(logits.clone(), starts, ends, top_k)
+        np.savez_compressed(HERE / f"topk_prefill_{idx_case}.npz", logits=logits.numpy(), row_starts=starts.numpy(), row_ends=ends.numpy(),
+                            top_k=top_k, values=selected_values(logits, ref, starts).numpy())
+        print("topk_prefill", idx_case, "ok")
+
+
+def types_namespace():
+    import types
+
+    return types.SimpleNamespace(torch_device_fn=types.SimpleNamespace(is_available=lambda: True, device_count=lambda: 1))
+
+
 def _parameter_sets(test_function):
     return [m for m in test_function.pytestmark if m.name == "parametrize"][0].args[1]
 
@@ -374,6 +419,8 @@ def index_cases() -> None:
 if __name__ == "__main__":
     if len(sys.argv) < 2 or sys.argv[1] == "flash_mla":
         flash_mla_builder_case()
+    if len(sys.argv) < 2 or sys.argv[1] == "topk":
+        topk_cases()
     if len(sys.argv) < 2 or sys.argv[1] == "index":
         index_cases()
     if len(sys.argv) < 2 or sys.argv[1] == "cp_gather":
