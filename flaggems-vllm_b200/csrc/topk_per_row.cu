@@ -8,15 +8,23 @@
 //   decode:  start_i = 0, end_i = seq_lens[i / next_n] - next_n + i % next_n + 1
 //   prefill: start_i = row_starts[i], end_i = row_ends[i]
 //
-// One CTA per row, radix selection in two reads of the row (the second one out of L2):
-//   1. histogram of a coarse, monotone 11-bit code of every value (top bits of its fp16 rounding, which spreads real
-//      logits over hundreds of bins where the top bits of the fp32 pattern would hit a handful);
-//   2. the bin holding the k-th largest value is located; values in higher bins are emitted straight away, the
-//      values of that bin are collected in shared memory with their full 32-bit keys;
-//   3. the collected candidates are reduced by a byte-wise radix selection in shared memory.
-// A bin with more candidates than fit in shared memory (degenerate inputs: thousands of near-equal values) takes a
-// slower route: three more histogram reads of the row on the bits of the fp32 key, then one emitting read.
-// HBM traffic: the row once (4 bytes per value); top_k * 4 bytes written.
+// One CTA per row, or a thread-block cluster of 2 / 4 / 8 CTAs for long rows.  Values are ranked by a coarse, monotone 11-bit code (top bits of the fp16 rounding of the value,
+// which spreads real logits over hundreds of bins where the top bits of the fp32 pattern would hit a handful) and,
+// inside a bin, by the order-preserving 32-bit key of their fp32 pattern.
+//   Fast route, ONE read of the row: a sample of the row (128 runs of 32 values) gives a bin b0 above which k values
+//   plus four standard deviations are expected; the row is streamed once and every value in a bin >= b0 is put
+//   into shared memory with its key and position; if at least k and at most kCandidateCap values were collected, a
+//   radix selection in shared memory finishes the job.  In a cluster every CTA streams its share of the row and hands
+//   its candidates to the first CTA through distributed shared memory (two hardware cluster barriers, no spinning).
+//   Histogram route, two reads (the second mostly out of L2), when the sample misjudged the row or k is too large for
+//   the candidate buffer: 1. histogram of the coarse code over the whole row, 2. the bin of the k-th largest value is
+//   located, values in higher bins are emitted, the values of that bin are collected in shared memory, 3. radix
+//   selection among them.
+//   A bin with more values than fit in shared memory (degenerate inputs: thousands of near-equal values) takes three
+//   more histogram reads of the row on the bits of the fp32 key, then one emitting read.
+// The result does not depend on the route; the sample only decides how fast it is reached.
+// HBM traffic on the fast route: the row once (4 bytes per value); top_k * 4 bytes written.
+#include <cooperative_groups.h>
 #include <cuda_fp16.h>
 
 #include "dsv4_common.cuh"
@@ -24,9 +32,12 @@
 namespace dsv4 {
 namespace {
 
+namespace cg = cooperative_groups;
+
 constexpr int kTopkThreads = 512;
 constexpr int kBins = 2048;
-constexpr int kCandidateCap = 4096;
+constexpr int kCandidateCap = 8192;  // 64 KiB of (key, position) pairs in dynamic shared memory
+constexpr int kSampleChunks = 128;  // x 32 values
 
 struct TopkParams {
     const float* logits;
@@ -114,15 +125,69 @@ __device__ __forceinline__ void add_aggregated(uint32_t* hist, uint32_t bin, boo
     if ((threadIdx.x & 31) == __ffs(peers) - 1) atomicAdd(&hist[bin], __popc(peers));
 }
 
+// The `want` largest of the n candidates (key, position) in shared memory; their positions are appended to out
+// through counters[0], ties at the smallest selected key through counters[2].  Radix selection in digits of up to
+// 11 bits on key - min(key), starting at the highest bit in which the candidates differ at all (they share sign,
+// exponent and leading mantissa bits, which a selection on fixed bit positions would waste passes and atomic
+// conflicts on).
+__device__ __forceinline__ void select_in_shared(const uint2* cand, uint32_t n, uint32_t want, uint32_t* hist, uint32_t* scratch,
+                                                 uint32_t* result, uint32_t* counters, int32_t* out) {
+    const int tid = threadIdx.x;
+    if (want >= n) {
+        for (uint32_t i = tid; i < n; i += kTopkThreads) out[atomicAdd(&counters[0], 1u)] = static_cast<int32_t>(cand[i].y);
+        return;
+    }
+    // range of the keys
+    if (tid == 0) result[0] = 0xffffffffu, result[1] = 0u;
+    __syncthreads();
+    uint32_t lo = 0xffffffffu, hi = 0u;
+    for (uint32_t i = tid; i < n; i += kTopkThreads) {
+        const uint32_t key = cand[i].x;
+        lo = key < lo ? key : lo, hi = key > hi ? key : hi;
+    }
+    lo = __reduce_min_sync(0xffffffffu, lo), hi = __reduce_max_sync(0xffffffffu, hi);
+    if ((tid & 31) == 0) atomicMin(&result[0], lo), atomicMax(&result[1], hi);
+    __syncthreads();
+    const uint32_t base = result[0], range = result[1] - result[0];
+    __syncthreads();
+    uint32_t need = want, prefix = 0u, prefix_mask = 0u;
+    int top = 32 - __clz(range | 1u);  // bits of (key - base) that can be set
+    while (top > 0) {
+        const int shift = top > 11 ? top - 11 : 0;
+        const uint32_t digit_mask = (1u << (top - shift)) - 1u;
+        for (int i = tid; i < kBins; i += kTopkThreads) hist[i] = 0u;
+        __syncthreads();
+        for (uint32_t i = tid; i < n; i += kTopkThreads) {
+            const uint32_t rel = cand[i].x - base;
+            if ((rel & prefix_mask) == prefix) atomicAdd(&hist[(rel >> shift) & digit_mask], 1u);
+        }
+        __syncthreads();
+        const Threshold t = find_threshold(hist, need, scratch, result);
+        prefix |= t.bin << shift;
+        prefix_mask |= digit_mask << shift;
+        need = t.need;
+        top = shift;
+        if (t.need == t.count) break;  // every candidate with this prefix is taken: the lower bits do not matter
+    }
+    // keys above the prefix (on the bits examined) are in; `need` of those equal to it are in
+    for (uint32_t i = tid; i < n; i += kTopkThreads) {
+        const uint2 e = cand[i];
+        const uint32_t rel_hi = (e.x - base) & prefix_mask;
+        if (rel_hi > prefix || (rel_hi == prefix && atomicAdd(&counters[2], 1u) < need)) out[atomicAdd(&counters[0], 1u)] = static_cast<int32_t>(e.y);
+    }
+}
+
 template <bool DECODE>
 __global__ void __launch_bounds__(kTopkThreads) topk_per_row_kernel(const TopkParams p) {
     __shared__ uint32_t hist[kBins];
-    __shared__ uint2 cand[kCandidateCap];  // (order key, position)
+    extern __shared__ uint2 cand[];  // kCandidateCap entries: (order key, position)
     __shared__ uint32_t scratch[32];
     __shared__ uint32_t result[4];
     __shared__ uint32_t counters[4];  // 0: emitted, 1: candidates collected, 2: ties taken
+    cg::cluster_group cluster = cg::this_cluster();
+    const uint32_t ctas = cluster.num_blocks(), rank = cluster.block_rank();  // the CTAs of a cluster share one row
     const int tid = threadIdx.x;
-    const int row = blockIdx.x;
+    const int row = blockIdx.x / ctas;
     int64_t start, end;
     if (DECODE) {
         start = 0;
@@ -136,80 +201,152 @@ __global__ void __launch_bounds__(kTopkThreads) topk_per_row_kernel(const TopkPa
     const int32_t len = end > start ? static_cast<int32_t>(end - start) : 0;
     const int32_t k = len < p.top_k ? len : p.top_k;
     int32_t* out = p.indices + static_cast<int64_t>(row) * p.top_k;
-    for (int i = k + tid; i < p.top_k; i += kTopkThreads) out[i] = -1;
+    // Everything up to the first cluster barrier depends on the row only, so the CTAs of a cluster leave together.
+    if (rank == 0)
+        for (int i = k + tid; i < p.top_k; i += kTopkThreads) out[i] = -1;
     if (len <= p.top_k) {  // everything is selected
-        for (int i = tid; i < len; i += kTopkThreads) out[i] = i;
+        if (rank == 0)
+            for (int i = tid; i < len; i += kTopkThreads) out[i] = i;
         return;
     }
     const float* x = p.logits + static_cast<int64_t>(row) * p.stride0 + start * p.stride1;
     const auto load = [&](int32_t i) { return __uint_as_float(ld_stream4(x + static_cast<int64_t>(i) * p.stride1)); };
+    // Calls visit(position, value) for the elements [from, to) of the row; 16-byte loads where the layout allows.
+    const auto for_each = [&](int32_t from, int32_t to, auto&& visit) {
+        if (p.stride1 == 1) {
+            int32_t head = from + static_cast<int32_t>(((16u - (reinterpret_cast<uintptr_t>(x + from) & 15u)) & 15u) >> 2);  // first 16-byte boundary
+            head = head < to ? head : to;
+            const int32_t vecs = (to - head) >> 2;
+            const float* body = x + head;
+            int32_t v = tid;
+            for (; v + kTopkThreads < vecs; v += 2 * kTopkThreads) {
+                const uint4 a = ld_stream16(body + 4 * v), b = ld_stream16(body + 4 * (v + kTopkThreads));
+                const int32_t ia = head + 4 * v, ib = head + 4 * (v + kTopkThreads);
+                visit(ia, __uint_as_float(a.x)), visit(ia + 1, __uint_as_float(a.y)), visit(ia + 2, __uint_as_float(a.z)), visit(ia + 3, __uint_as_float(a.w));
+                visit(ib, __uint_as_float(b.x)), visit(ib + 1, __uint_as_float(b.y)), visit(ib + 2, __uint_as_float(b.z)), visit(ib + 3, __uint_as_float(b.w));
+            }
+            for (; v < vecs; v += kTopkThreads) {
+                const uint4 a = ld_stream16(body + 4 * v);
+                const int32_t ia = head + 4 * v;
+                visit(ia, __uint_as_float(a.x)), visit(ia + 1, __uint_as_float(a.y)), visit(ia + 2, __uint_as_float(a.z)), visit(ia + 3, __uint_as_float(a.w));
+            }
+            for (int32_t i = from + tid; i < head; i += kTopkThreads) visit(i, load(i));
+            for (int32_t i = head + 4 * vecs + tid; i < to; i += kTopkThreads) visit(i, load(i));
+        } else {
+            for (int32_t i = from + tid; i < to; i += kTopkThreads) visit(i, load(i));
+        }
+    };
 
-    // 1. coarse histogram
+    const bool fast = 2 * k + 512 <= kCandidateCap;
+    if (rank != 0 && (!fast || len <= kCandidateCap)) return;  // these rows are handled by the first CTA alone
     for (int i = tid; i < kBins; i += kTopkThreads) hist[i] = 0u;
     if (tid < 4) counters[tid] = 0u;
     __syncthreads();
-    {
-        int32_t i = tid;
-        for (; i + 3 * kTopkThreads < len; i += 4 * kTopkThreads) {
-            const float a = load(i), b = load(i + kTopkThreads), c = load(i + 2 * kTopkThreads), d = load(i + 3 * kTopkThreads);
-            atomicAdd(&hist[coarse_bin(a)], 1u), atomicAdd(&hist[coarse_bin(b)], 1u);
-            atomicAdd(&hist[coarse_bin(c)], 1u), atomicAdd(&hist[coarse_bin(d)], 1u);
+
+    // ---- fast route -------------------------------------------------------------------------------------------
+    if (fast && len <= kCandidateCap) {
+        // The whole row fits into the candidate buffer: one read fills it and the coarse histogram; values above the
+        // bin of the k-th largest are emitted, the few inside it are ranked separately.
+        for_each(0, len, [&](int32_t i, float v) {
+            cand[i] = make_uint2(order_key(__float_as_uint(v)), static_cast<uint32_t>(i));
+            atomicAdd(&hist[coarse_bin(v)], 1u);
+        });
+        __syncthreads();
+        const Threshold coarse = find_threshold(hist, static_cast<uint32_t>(k), scratch, result);
+        const bool take_all = coarse.need == coarse.count;
+        // the bin's values are moved to the front of the buffer; every thread first takes its entries into registers
+        constexpr int kMine = kCandidateCap / kTopkThreads;
+        uint2 mine[kMine];
+#pragma unroll
+        for (int t = 0; t < kMine; ++t) {
+            const int32_t i = tid + t * kTopkThreads;
+            mine[t] = i < len ? cand[i] : make_uint2(0u, 0xffffffffu);
         }
-        for (; i < len; i += kTopkThreads) atomicAdd(&hist[coarse_bin(load(i))], 1u);
+        __syncthreads();
+#pragma unroll
+        for (int t = 0; t < kMine; ++t) {
+            const uint2 e = mine[t];
+            if (e.y == 0xffffffffu) continue;
+            const uint32_t c = coarse_bin(__uint_as_float((e.x & 0x80000000u) ? e.x & 0x7fffffffu : ~e.x));  // key -> value -> bin
+            if (c > coarse.bin || (take_all && c == coarse.bin)) out[atomicAdd(&counters[0], 1u)] = static_cast<int32_t>(e.y);
+            else if (c == coarse.bin) cand[atomicAdd(&counters[1], 1u)] = e;
+        }
+        __syncthreads();
+        if (!take_all) select_in_shared(cand, coarse.count, coarse.need, hist, scratch, result, counters, out);
+        return;
     }
+    if (fast) {
+        // every CTA of the cluster takes the same sample, hence the same b0: candidates are the values in bins >= b0
+        // the sample: kSampleChunks runs of 32 consecutive values (one 128-byte line each) spread evenly over the row
+        const int32_t stride = (len / kSampleChunks) & ~31;  // len > kCandidateCap, so the runs do not overlap
+        for (int32_t j = tid; j < kSampleChunks * 32; j += kTopkThreads) atomicAdd(&hist[coarse_bin(load((j >> 5) * stride + (j & 31)))], 1u);
+        __syncthreads();
+        // rank inside the sample that stands for k values of the row, plus four standard deviations of that count
+        const float mean = static_cast<float>(k) * (kSampleChunks * 32) / static_cast<float>(len);
+        const uint32_t sample_rank = static_cast<uint32_t>(mean + 4.0f * sqrtf(mean)) + 3u;
+        const uint32_t b0 = find_threshold(hist, sample_rank < kSampleChunks * 32u ? sample_rank : kSampleChunks * 32u, scratch, result).bin;
+        cluster.sync();  // the first CTA's counters are zero before anybody reserves space in its buffer
+        // this CTA's share of the row, a multiple of 4 elements so that the 16-byte loads stay aligned
+        const int32_t share = (((len + static_cast<int32_t>(ctas) - 1) / static_cast<int32_t>(ctas)) + 3) & ~3;
+        const int32_t from = static_cast<int32_t>(rank) * share < len ? static_cast<int32_t>(rank) * share : len;
+        const int32_t to = from + share < len ? from + share : len;
+        for_each(from, to, [&](int32_t i, float v) {
+            if (coarse_bin(v) >= b0) {
+                const uint32_t at = atomicAdd(&counters[1], 1u);
+                if (at < kCandidateCap) cand[at] = make_uint2(order_key(__float_as_uint(v)), static_cast<uint32_t>(i));
+            }
+        });
+        __syncthreads();
+        if (rank != 0) {
+            // hand the candidates over to the first CTA through distributed shared memory
+            const uint32_t mine = counters[1];
+            if (tid == 0) result[3] = atomicAdd(cluster.map_shared_rank(&counters[1], 0), mine);
+            __syncthreads();
+            const uint32_t at = result[3];
+            if (mine <= kCandidateCap && at + mine <= kCandidateCap) {
+                uint2* remote = cluster.map_shared_rank(cand, 0);
+                for (uint32_t j = tid; j < mine; j += kTopkThreads) remote[at + j] = cand[j];
+            }
+        }
+        cluster.sync();  // all candidates have arrived
+        if (rank != 0) return;
+        const uint32_t collected = counters[1];
+        if (collected >= static_cast<uint32_t>(k) && collected <= kCandidateCap) {
+            select_in_shared(cand, collected, static_cast<uint32_t>(k), hist, scratch, result, counters, out);
+            return;
+        }
+        // the sample misjudged the row: the first CTA starts over on the histogram route
+        __syncthreads();
+        for (int i = tid; i < kBins; i += kTopkThreads) hist[i] = 0u;
+        if (tid < 4) counters[tid] = 0u;
+        __syncthreads();
+    }
+
+    // ---- histogram route --------------------------------------------------------------------------------------
+    for_each(0, len, [&](int32_t, float v) { atomicAdd(&hist[coarse_bin(v)], 1u); });
     __syncthreads();
     const Threshold coarse = find_threshold(hist, static_cast<uint32_t>(k), scratch, result);
     const bool collect = coarse.count <= kCandidateCap && coarse.need < coarse.count;
     const bool take_all = coarse.need == coarse.count;  // the whole bin belongs to the top k
-
-    // 2. emit everything above the bin (and the bin itself if it is taken whole); collect the bin's candidates
-    {
-        const auto visit = [&](int32_t i, float v) {
-            const uint32_t c = coarse_bin(v);
-            if (c > coarse.bin || (take_all && c == coarse.bin)) {
-                out[atomicAdd(&counters[0], 1u)] = i;
-            } else if (collect && c == coarse.bin) {
-                cand[atomicAdd(&counters[1], 1u)] = make_uint2(order_key(__float_as_uint(v)), static_cast<uint32_t>(i));
-            }
-        };
-        int32_t i = tid;
-        for (; i + 3 * kTopkThreads < len; i += 4 * kTopkThreads) {
-            const float a = load(i), b = load(i + kTopkThreads), c = load(i + 2 * kTopkThreads), d = load(i + 3 * kTopkThreads);
-            visit(i, a), visit(i + kTopkThreads, b), visit(i + 2 * kTopkThreads, c), visit(i + 3 * kTopkThreads, d);
+    // emit everything above the bin (and the bin itself if it is taken whole); collect the bin's candidates
+    for_each(0, len, [&](int32_t i, float v) {
+        const uint32_t c = coarse_bin(v);
+        if (c > coarse.bin || (take_all && c == coarse.bin)) {
+            out[atomicAdd(&counters[0], 1u)] = i;
+        } else if (collect && c == coarse.bin) {
+            cand[atomicAdd(&counters[1], 1u)] = make_uint2(order_key(__float_as_uint(v)), static_cast<uint32_t>(i));
         }
-        for (; i < len; i += kTopkThreads) visit(i, load(i));
-    }
+    });
     __syncthreads();
     if (take_all) return;
-
-    uint32_t need = coarse.need;  // how many of the bin's elements are still to be emitted
-    uint32_t prefix = 0u, prefix_mask = 0u;
     if (collect) {
-        // 3. byte-wise radix selection among the candidates in shared memory
-        const uint32_t n_cand = coarse.count;
-        for (int shift = 24; shift >= 0; shift -= 8) {
-            for (int i = tid; i < kBins; i += kTopkThreads) hist[i] = 0u;
-            __syncthreads();
-            for (uint32_t i = tid; i < n_cand; i += kTopkThreads) {
-                const uint32_t key = cand[i].x;
-                if ((key & prefix_mask) == prefix) atomicAdd(&hist[(key >> shift) & 0xffu], 1u);
-            }
-            __syncthreads();
-            const Threshold t = find_threshold(hist, need, scratch, result);
-            prefix |= t.bin << shift;
-            prefix_mask |= 0xffu << shift;
-            need = t.need;
-        }
-        // prefix is now the key of the k-th largest value; `need` of the candidates equal to it are taken
-        for (uint32_t i = tid; i < n_cand; i += kTopkThreads) {
-            const uint2 e = cand[i];
-            if (e.x > prefix || (e.x == prefix && atomicAdd(&counters[2], 1u) < need)) out[atomicAdd(&counters[0], 1u)] = static_cast<int32_t>(e.y);
-        }
+        select_in_shared(cand, coarse.count, coarse.need, hist, scratch, result, counters, out);
         return;
     }
 
     // Slow route: the bin is too crowded for shared memory.  Radix selection on the fp32 key over the row itself,
     // restricted to the elements of the bin: bits 31-21, 20-10, 9-0.
+    uint32_t need = coarse.need, prefix = 0u, prefix_mask = 0u;
     const int shifts[3] = {21, 10, 0};
     const uint32_t widths[3] = {11, 11, 10};
     for (int pass = 0; pass < 3; ++pass) {
@@ -251,8 +388,38 @@ cudaError_t launch_topk_per_row(const float* logits, int64_t stride0, int64_t st
     p.logits = logits, p.stride0 = stride0, p.stride1 = stride1, p.indices = indices;
     p.num_rows = static_cast<int32_t>(num_rows), p.vocab = vocab, p.top_k = top_k;
     p.seq_lens = seq_lens, p.next_n = next_n, p.row_starts = row_starts, p.row_ends = row_ends;
-    if (seq_lens) topk_per_row_kernel<true><<<static_cast<unsigned>(num_rows), kTopkThreads, 0, stream>>>(p);
-    else topk_per_row_kernel<false><<<static_cast<unsigned>(num_rows), kTopkThreads, 0, stream>>>(p);
+    constexpr size_t kDynamicBytes = sizeof(uint2) * kCandidateCap;
+    static bool configured[64] = {};  // per device; setting the attribute twice is harmless
+    int dev = 0;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess) return err;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    if (!configured[dev]) {
+        err = cudaFuncSetAttribute(topk_per_row_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kDynamicBytes));
+        if (err != cudaSuccess) return err;
+        err = cudaFuncSetAttribute(topk_per_row_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kDynamicBytes));
+        if (err != cudaSuccess) return err;
+        configured[dev] = true;
+    }
+    // CTAs per row: long rows are shared by a cluster (shorter streaming time per row, no straggling rows at the
+    // end of the grid); the candidates meet in the first CTA's shared memory.
+    // Only while the grid would not fill the GPU otherwise (about 3 CTAs per SM are resident): with many rows the
+    // repeated sample and the barriers cost more than the shorter rows win.
+    int sms = 0;
+    err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (err != cudaSuccess) return err;
+    unsigned ctas = vocab >= 131072 ? 8u : vocab >= 65536 ? 4u : vocab >= 32768 ? 2u : 1u;
+    while (ctas > 1 && num_rows * ctas > 3LL * sms) ctas >>= 1;
+    if (num_rows * ctas > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(static_cast<unsigned>(num_rows * ctas)), config.blockDim = dim3(kTopkThreads);
+    config.dynamicSmemBytes = kDynamicBytes, config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeClusterDimension;
+    attribute[0].val.clusterDim.x = ctas, attribute[0].val.clusterDim.y = 1, attribute[0].val.clusterDim.z = 1;
+    config.attrs = attribute, config.numAttrs = 1;
+    err = seq_lens ? cudaLaunchKernelEx(&config, topk_per_row_kernel<true>, p) : cudaLaunchKernelEx(&config, topk_per_row_kernel<false>, p);
+    if (err != cudaSuccess) return err;
     count_launch();
     return cudaGetLastError();
 }
