@@ -38,12 +38,14 @@ constexpr int kTopkThreads = 512;
 constexpr int kBins = 2048;
 constexpr int kCandidateCap = 8192;  // 64 KiB of (key, position) pairs in dynamic shared memory
 constexpr int kSampleChunks = 128;  // x 32 values
+constexpr int kCountingMax = kBins / 2;  // candidates of one bin ranked by counting (they are kept where the histogram was)
 
 struct TopkParams {
     const float* logits;
     int64_t stride0, stride1;
     int32_t* indices;  // [num_rows, top_k]
     int32_t num_rows, vocab, top_k;
+    uint32_t pair_capacity;  // (key, position) pairs the dynamic shared memory of this launch holds
     // decode
     const int32_t* seq_lens;
     int32_t next_n;
@@ -177,9 +179,60 @@ __device__ __forceinline__ void select_in_shared(const uint2* cand, uint32_t n, 
     }
 }
 
+__device__ __forceinline__ uint32_t coarse_bin_of_key(uint32_t key) {  // key -> value -> bin
+    return coarse_bin(__uint_as_float((key & 0x80000000u) ? key & 0x7fffffffu : ~key));
+}
+
+// The `want` largest of n candidates by counting: a candidate's rank is the number of candidates ahead of it in the
+// total order (key descending, position ascending); one pass, no histogram.
+__device__ __forceinline__ void rank_by_counting(const uint2* dense, uint32_t n, uint32_t want, uint32_t* counters, int32_t* out) {
+    for (uint32_t a = threadIdx.x; a < n; a += kTopkThreads) {
+        const uint2 e = dense[a];
+        uint32_t ahead = 0u;
+#pragma unroll 8
+        for (uint32_t b = 0; b < n; ++b) {
+            const uint2 o = dense[b];  // the same address for all lanes: a broadcast
+            ahead += (o.x > e.x || (o.x == e.x && o.y < e.y)) ? 1u : 0u;
+        }
+        if (ahead < want) out[atomicAdd(&counters[0], 1u)] = static_cast<int32_t>(e.y);
+    }
+}
+
+// The `want` largest of the n <= kCandidateCap candidates in `cand`, in two levels: a histogram of their coarse codes
+// finds the bin of the want-th largest; candidates above it are emitted; those inside it are copied to where the
+// histogram was and ranked by counting: a candidate's rank is the number of them ahead of it in the total order (key
+// descending, position ascending).  A crowded bin goes to the radix selection instead.
+// counters[1] must be zero on entry; `hist_ready` says that hist already holds the histogram.
+__device__ __forceinline__ void select_two_level(const uint2* cand, uint32_t n, uint32_t want, uint32_t* hist, uint32_t* scratch,
+                                                 uint32_t* result, uint32_t* counters, int32_t* out, bool hist_ready) {
+    const int tid = threadIdx.x;
+    if (!hist_ready) {
+        for (int i = tid; i < kBins; i += kTopkThreads) hist[i] = 0u;
+        __syncthreads();
+        for (uint32_t i = tid; i < n; i += kTopkThreads) atomicAdd(&hist[coarse_bin_of_key(cand[i].x)], 1u);
+        __syncthreads();
+    }
+    const Threshold coarse = find_threshold(hist, want, scratch, result);
+    const bool take_all = coarse.need == coarse.count;
+    if (!take_all && coarse.count > kCountingMax) {
+        select_in_shared(cand, n, want, hist, scratch, result, counters, out);
+        return;
+    }
+    uint2* dense = reinterpret_cast<uint2*>(hist);  // the histogram is no longer needed: kBins / 2 entries
+    for (uint32_t i = tid; i < n; i += kTopkThreads) {
+        const uint2 e = cand[i];
+        const uint32_t c = coarse_bin_of_key(e.x);
+        if (c > coarse.bin || (take_all && c == coarse.bin)) out[atomicAdd(&counters[0], 1u)] = static_cast<int32_t>(e.y);
+        else if (c == coarse.bin) dense[atomicAdd(&counters[1], 1u)] = e;
+    }
+    __syncthreads();
+    if (take_all) return;
+    rank_by_counting(dense, coarse.count, coarse.need, counters, out);
+}
+
 template <bool DECODE>
 __global__ void __launch_bounds__(kTopkThreads) topk_per_row_kernel(const TopkParams p) {
-    __shared__ uint32_t hist[kBins];
+    __shared__ __align__(8) uint32_t hist[kBins];
     extern __shared__ uint2 cand[];  // kCandidateCap entries: (order key, position)
     __shared__ uint32_t scratch[32];
     __shared__ uint32_t result[4];
@@ -245,37 +298,31 @@ __global__ void __launch_bounds__(kTopkThreads) topk_per_row_kernel(const TopkPa
 
     // ---- fast route -------------------------------------------------------------------------------------------
     if (fast && len <= kCandidateCap) {
-        // The whole row fits into the candidate buffer: one read fills it and the coarse histogram; values above the
-        // bin of the k-th largest are emitted, the few inside it are ranked separately.
+        // The whole row fits into shared memory (keys only: a value's position is its place in the buffer): one read
+        // fills it and the coarse histogram; values above the bin of the k-th largest are emitted, the few inside it
+        // are copied to where the histogram was and ranked by counting.
+        uint32_t* keys = reinterpret_cast<uint32_t*>(cand);
         for_each(0, len, [&](int32_t i, float v) {
-            cand[i] = make_uint2(order_key(__float_as_uint(v)), static_cast<uint32_t>(i));
+            keys[i] = order_key(__float_as_uint(v));
             atomicAdd(&hist[coarse_bin(v)], 1u);
         });
         __syncthreads();
         const Threshold coarse = find_threshold(hist, static_cast<uint32_t>(k), scratch, result);
         const bool take_all = coarse.need == coarse.count;
-        // the bin's values are moved to the front of the buffer; every thread first takes its entries into registers
-        constexpr int kMine = kCandidateCap / kTopkThreads;
-        uint2 mine[kMine];
-#pragma unroll
-        for (int t = 0; t < kMine; ++t) {
-            const int32_t i = tid + t * kTopkThreads;
-            mine[t] = i < len ? cand[i] : make_uint2(0u, 0xffffffffu);
+        if (take_all || coarse.count <= kCountingMax) {
+            uint2* dense = reinterpret_cast<uint2*>(hist);
+            for (int32_t i = tid; i < len; i += kTopkThreads) {
+                const uint32_t key = keys[i];
+                const uint32_t c = coarse_bin_of_key(key);
+                if (c > coarse.bin || (take_all && c == coarse.bin)) out[atomicAdd(&counters[0], 1u)] = i;
+                else if (c == coarse.bin) dense[atomicAdd(&counters[1], 1u)] = make_uint2(key, static_cast<uint32_t>(i));
+            }
+            __syncthreads();
+            if (!take_all) rank_by_counting(dense, coarse.count, coarse.need, counters, out);
+            return;
         }
-        __syncthreads();
-#pragma unroll
-        for (int t = 0; t < kMine; ++t) {
-            const uint2 e = mine[t];
-            if (e.y == 0xffffffffu) continue;
-            const uint32_t c = coarse_bin(__uint_as_float((e.x & 0x80000000u) ? e.x & 0x7fffffffu : ~e.x));  // key -> value -> bin
-            if (c > coarse.bin || (take_all && c == coarse.bin)) out[atomicAdd(&counters[0], 1u)] = static_cast<int32_t>(e.y);
-            else if (c == coarse.bin) cand[atomicAdd(&counters[1], 1u)] = e;
-        }
-        __syncthreads();
-        if (!take_all) select_in_shared(cand, coarse.count, coarse.need, hist, scratch, result, counters, out);
-        return;
-    }
-    if (fast) {
+        // a crowded bin: over to the histogram route, which has the histogram it needs already
+    } else if (fast) {
         // every CTA of the cluster takes the same sample, hence the same b0: candidates are the values in bins >= b0
         // the sample: kSampleChunks runs of 32 consecutive values (one 128-byte line each) spread evenly over the row
         const int32_t stride = (len / kSampleChunks) & ~31;  // len > kCandidateCap, so the runs do not overlap
@@ -312,7 +359,9 @@ __global__ void __launch_bounds__(kTopkThreads) topk_per_row_kernel(const TopkPa
         if (rank != 0) return;
         const uint32_t collected = counters[1];
         if (collected >= static_cast<uint32_t>(k) && collected <= kCandidateCap) {
-            select_in_shared(cand, collected, static_cast<uint32_t>(k), hist, scratch, result, counters, out);
+            __syncthreads();
+            if (tid == 0) counters[1] = 0u;
+            select_two_level(cand, collected, static_cast<uint32_t>(k), hist, scratch, result, counters, out, false);
             return;
         }
         // the sample misjudged the row: the first CTA starts over on the histogram route
@@ -323,10 +372,12 @@ __global__ void __launch_bounds__(kTopkThreads) topk_per_row_kernel(const TopkPa
     }
 
     // ---- histogram route --------------------------------------------------------------------------------------
-    for_each(0, len, [&](int32_t, float v) { atomicAdd(&hist[coarse_bin(v)], 1u); });
-    __syncthreads();
+    if (!(fast && len <= kCandidateCap)) {  // (a short row arrives with its histogram)
+        for_each(0, len, [&](int32_t, float v) { atomicAdd(&hist[coarse_bin(v)], 1u); });
+        __syncthreads();
+    }
     const Threshold coarse = find_threshold(hist, static_cast<uint32_t>(k), scratch, result);
-    const bool collect = coarse.count <= kCandidateCap && coarse.need < coarse.count;
+    const bool collect = coarse.count <= p.pair_capacity && coarse.need < coarse.count;
     const bool take_all = coarse.need == coarse.count;  // the whole bin belongs to the top k
     // emit everything above the bin (and the bin itself if it is taken whole); collect the bin's candidates
     for_each(0, len, [&](int32_t i, float v) {
@@ -389,6 +440,8 @@ cudaError_t launch_topk_per_row(const float* logits, int64_t stride0, int64_t st
     p.num_rows = static_cast<int32_t>(num_rows), p.vocab = vocab, p.top_k = top_k;
     p.seq_lens = seq_lens, p.next_n = next_n, p.row_starts = row_starts, p.row_ends = row_ends;
     constexpr size_t kDynamicBytes = sizeof(uint2) * kCandidateCap;
+    // rows that fit into the buffer as a whole keep 4-byte keys only: more CTAs per SM for the many-short-rows case
+    const size_t dynamic_bytes = vocab <= kCandidateCap ? sizeof(uint32_t) * static_cast<size_t>(vocab > 256 ? vocab : 256) : kDynamicBytes;
     static bool configured[64] = {};  // per device; setting the attribute twice is harmless
     int dev = 0;
     cudaError_t err = cudaGetDevice(&dev);
@@ -413,7 +466,8 @@ cudaError_t launch_topk_per_row(const float* logits, int64_t stride0, int64_t st
     if (num_rows * ctas > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3(static_cast<unsigned>(num_rows * ctas)), config.blockDim = dim3(kTopkThreads);
-    config.dynamicSmemBytes = kDynamicBytes, config.stream = stream;
+    config.dynamicSmemBytes = dynamic_bytes, config.stream = stream;
+    p.pair_capacity = static_cast<uint32_t>(dynamic_bytes / sizeof(uint2));
     cudaLaunchAttribute attribute[1];
     attribute[0].id = cudaLaunchAttributeClusterDimension;
     attribute[0].val.clusterDim.x = ctas, attribute[0].val.clusterDim.y = 1, attribute[0].val.clusterDim.z = 1;
