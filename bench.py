@@ -354,6 +354,38 @@ def sibling_ops(steps, warmup):
     out["combine_topk_swa_indices"] = {"tokens": nt, "topk": tk, "window": window, "us_per_launch": secs / steps * 1e6,
                                        "hbm_gbs": nt * (4 * tk + 4 * (tk + window) + 4) * steps / secs / 1e9,
                                        "note": "includes torch.empty of the outputs per call; positions 6144-8191, so every row has 512 + 128 entries"}
+    del tki
+    # top-k selection over the indexer logits: one decode row, a decode batch, a prefill chunk (rotating inputs larger than L2)
+    try:
+        import vllm._custom_ops  # noqa: F401  (loads torch.ops._C)
+
+        library = torch.ops._C.top_k_per_row_decode if hasattr(torch.ops._C, "top_k_per_row_decode") else None
+    except Exception:
+        library = None
+    for rows, vocab, tk in ((1, 262144, 512), (496, 262144, 512), (4096, 32768, 2048)):
+        sets = max(1, min(8, (1 << 30) // (rows * vocab * 4)))
+        logits = [torch.randn(rows, vocab, generator=g, device=dev) for _ in range(sets)]
+        seq = torch.full((rows,), vocab, device=dev, dtype=torch.int32)
+        idx = torch.empty(rows, tk, device=dev, dtype=torch.int32)
+        turn = [0]
+
+        def ours():
+            turn[0] += 1
+            x = logits[turn[0] % sets]
+            flaggems_vllm.top_k_per_row_decode(x, 1, seq, idx, rows, x.stride(0), x.stride(1), tk)
+
+        def theirs():
+            turn[0] += 1
+            x = logits[turn[0] % sets]
+            library(x, 1, seq, idx, rows, x.stride(0), x.stride(1), tk)
+
+        secs = time_steps(ours, steps, warmup, stream, torch.cuda.synchronize)
+        entry = {"rows": rows, "vocab": vocab, "top_k": tk, "us_per_launch": secs / steps * 1e6,
+                 "hbm_gbs": rows * (vocab + tk) * 4 * steps / secs / 1e9}
+        if library is not None:
+            entry["vllm_kernel_us_per_launch"] = time_steps(theirs, steps, warmup, stream, torch.cuda.synchronize) / steps * 1e6
+        out[f"top_k_per_row_decode[{rows}x{vocab}, k={tk}]"] = entry
+        del logits
     return out
 
 

@@ -120,3 +120,28 @@ def test_prologue_oracles_against_the_upstream_flash_mla_cache_builder():
         cache = torch.zeros(pages, bs * 584, dtype=torch.uint8)
         run(q, kv, cache, torch.arange(n), torch.zeros(n, dtype=torch.int64), table, 1e-6, bs)
         assert torch.equal(cache, want)
+
+
+def test_top_k_oracle_against_upstream_torch_statements():
+    """`_torch_topk_ref` (decode) and `reference_top_k_per_row` (prefill) of the upstream tests on fresh logits, compared
+    the way those tests compare: the selected values of every row as a sorted list."""
+    import types
+
+    runtime = types.SimpleNamespace(torch_device_fn=types.SimpleNamespace(is_available=lambda: True, device_count=lambda: 1))
+    D = ref_loader.load_upstream_helper_test("test_top_k_per_row_decode.py", "flaggems_vllm.ops.top_k_per_row_decode", ("top_k_per_row_decode",),
+                                             package_attrs={"runtime": runtime})
+    P = ref_loader.load_upstream_helper_test("test_top_k_per_row_prefill.py", "flaggems_vllm.ops.top_k_per_row_prefill", ("top_k_per_row_prefill",),
+                                             package_attrs={"runtime": runtime})
+    g = torch.Generator().manual_seed(55)
+    logits = torch.randn(6, 20000, generator=g)
+    logits[0, :9000] = 0.5
+    seq = torch.tensor([20000, 15000, 300], dtype=torch.int32)
+    ref, got = torch.zeros(6, 256, dtype=torch.int32), torch.zeros(6, 256, dtype=torch.int32)
+    D._torch_topk_ref(logits.clone(), 2, seq, ref, 6, logits.stride(0), 1, 256)
+    c_oracle.top_k_per_row_decode(logits, 2, seq, got, 6, logits.stride(0), 1, 256)
+    assert D.check_topk_values_match(logits, got, ref, 256)
+    starts = torch.tensor([0, 5, 1000, 19000, 7, 7], dtype=torch.int32)
+    ends = torch.tensor([20000, 105, 18000, 20000, 7, 9000], dtype=torch.int32)
+    ref = P.reference_top_k_per_row(logits.clone(), starts, ends, 256)
+    c_oracle.top_k_per_row_prefill(logits, starts, ends, got, 6, logits.stride(0), 1, 256)
+    assert P.check_topk_values_match(logits, got, ref, starts, 256)

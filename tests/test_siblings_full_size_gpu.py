@@ -126,3 +126,24 @@ def test_index_operators_32768_tokens():
     got, lens = flaggems_vllm.combine_topk_swa_indices(values, start.to(DEV), seq.to(DEV), gather.to(DEV), 128, 4, 512, 8192, 2048)
     want, want_lens = c_oracle.combine_topk_swa_indices(values.cpu(), start, seq, gather, 128, 4, 512, 8192, 2048)
     assert torch.equal(got.cpu(), want) and torch.equal(lens.cpu(), want_lens)
+
+
+@pytest.mark.parametrize("rows,vocab,top_k", [(1, 262144, 512), (496, 262144, 512), (4096, 32768, 2048), (8192, 8192, 512)])
+def test_top_k_selection_at_bench_sizes(rows, vocab, top_k):
+    """Too large for the sorting oracle on every row: the values selected on every row must equal, as a sorted list, the
+    values torch.topk returns on the device (the property the upstream tests check), and 8 rows go through the oracle."""
+    g = gen(8)
+    logits = torch.randn(rows, vocab, generator=g, device=DEV)
+    seq = torch.full((rows,), vocab, device=DEV, dtype=torch.int32)
+    idx = torch.full((rows, top_k), -7, device=DEV, dtype=torch.int32)
+    flaggems_vllm.top_k_per_row_decode(logits, 1, seq, idx, rows, logits.stride(0), logits.stride(1), top_k)
+    assert int(idx.min()) >= 0 and int(idx.max()) < vocab
+    got = logits.gather(1, idx.long()).sort(dim=1, descending=True).values
+    want = torch.topk(logits, top_k, dim=1, sorted=True).values
+    assert torch.equal(got, want)
+    assert int((idx.sort(dim=1).values.diff(dim=1) == 0).sum()) == 0  # no position twice
+    pick = torch.linspace(0, rows - 1, min(rows, 8)).long()
+    sub = logits[pick.to(DEV)].cpu()
+    ref = torch.zeros(pick.numel(), top_k, dtype=torch.int32)
+    c_oracle.top_k_per_row_decode(sub, 1, torch.full((pick.numel(),), vocab, dtype=torch.int32), ref, pick.numel(), sub.stride(0), 1, top_k)
+    assert torch.equal(sub.gather(1, ref.long()).sort(dim=1, descending=True).values, got[pick.to(DEV)].cpu())
