@@ -272,11 +272,15 @@ __global__ void __launch_bounds__(kTopkThreads) topk_per_row_kernel(const TopkPa
             const int32_t vecs = (to - head) >> 2;
             const float* body = x + head;
             int32_t v = tid;
-            for (; v + kTopkThreads < vecs; v += 2 * kTopkThreads) {
-                const uint4 a = ld_stream16(body + 4 * v), b = ld_stream16(body + 4 * (v + kTopkThreads));
-                const int32_t ia = head + 4 * v, ib = head + 4 * (v + kTopkThreads);
-                visit(ia, __uint_as_float(a.x)), visit(ia + 1, __uint_as_float(a.y)), visit(ia + 2, __uint_as_float(a.z)), visit(ia + 3, __uint_as_float(a.w));
-                visit(ib, __uint_as_float(b.x)), visit(ib + 1, __uint_as_float(b.y)), visit(ib + 2, __uint_as_float(b.z)), visit(ib + 3, __uint_as_float(b.w));
+            for (; v + 3 * kTopkThreads < vecs; v += 4 * kTopkThreads) {  // four 16-byte loads per thread in flight
+                uint4 q[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) q[u] = ld_stream16(body + 4 * (v + u * kTopkThreads));
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int32_t i = head + 4 * (v + u * kTopkThreads);
+                    visit(i, __uint_as_float(q[u].x)), visit(i + 1, __uint_as_float(q[u].y)), visit(i + 2, __uint_as_float(q[u].z)), visit(i + 3, __uint_as_float(q[u].w));
+                }
             }
             for (; v < vecs; v += kTopkThreads) {
                 const uint4 a = ld_stream16(body + 4 * v);
