@@ -300,7 +300,7 @@ int dsv4_top_k_per_row_prefill(const float* logits, int64_t stride0, int64_t str
     const int rc = check_topk_sizes(logits, indices, num_rows, vocab, top_k);
     if (rc != DSV4_OK) return rc;
     if (num_rows == 0 || top_k == 0) return DSV4_OK;
-    if (!row_starts || !row_ends) return DSV4_ERR_NULL_POINTER;
+    if (!row_ends) return DSV4_ERR_NULL_POINTER;
     return static_cast<int>(launch_topk_per_row(logits, stride0, stride1, indices, num_rows, static_cast<int>(vocab),
                                                 static_cast<int>(top_k), nullptr, 1, row_starts, row_ends,
                                                 static_cast<cudaStream_t>(cuda_stream)));

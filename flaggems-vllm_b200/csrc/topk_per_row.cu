@@ -50,7 +50,7 @@ struct TopkParams {
     const int32_t* seq_lens;
     int32_t next_n;
     // prefill
-    const int32_t* row_starts;
+    const int32_t* row_starts;  // null: every range starts at 0
     const int32_t* row_ends;
 };
 
@@ -246,7 +246,7 @@ __global__ void __launch_bounds__(kTopkThreads) topk_per_row_kernel(const TopkPa
         start = 0;
         end = static_cast<int64_t>(p.seq_lens[row / p.next_n]) - p.next_n + row % p.next_n + 1;
     } else {
-        start = p.row_starts[row];
+        start = p.row_starts ? p.row_starts[row] : 0;
         end = p.row_ends[row];
     }
     start = start < 0 ? 0 : start;

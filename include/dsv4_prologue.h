@@ -236,6 +236,10 @@ int dsv4_combine_topk_swa_indices(const int32_t* topk_indices, int64_t topk_stri
  * [start, end) - decode: start = 0, end = seq_lens[i / next_n] - next_n + i % next_n + 1; prefill: row_starts[i],
  * row_ends[i]; both clipped to [0, vocab] - indices[i*top_k + j], j < k = min(top_k, end - start), are the positions
  * relative to start of the k largest values in any order (ties broken arbitrarily), the remaining entries are -1.
+ * row_starts may be NULL (every range starts at 0), which is the call shape of the reference's
+ *   persistent_topk(logits, lengths, output, workspace, k, max_seq_len)
+ * (src/flaggems_vllm/ops/persistent_topk.py:2179-2342) with row_ends = lengths; its workspace is not needed here: the
+ * kernel keeps its state in shared memory.
  * The selection orders values by their bit patterns: a NaN with the sign bit clear ranks above +inf, one with the
  * sign bit set below -inf.
  */

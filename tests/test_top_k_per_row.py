@@ -157,6 +157,27 @@ def test_decode_rows_share_sequence_lengths_and_strided_logits():
     assert torch.equal(selected_values(logits, got, torch.zeros(6), ends, 128), selected_values(logits, want, torch.zeros(6), ends, 128))
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("lengths,k,two_d", [([70000, 512, 100, 65536, 0, 33000], 512, False), ([32773, 32774], 1024, True), ([262144] * 3, 2048, False)])
+def test_persistent_topk_call_shape(lengths, k, two_d):
+    """vLLM's `persistent_topk(logits, lengths, output, workspace, k, max_seq_len)`: rows padded with -inf as in the
+    upstream test, lengths 1-D or [batch, next_n], the workspace left untouched."""
+    g = torch.Generator().manual_seed(len(lengths) + k)
+    width = max(max(lengths), k) + 64
+    logits = torch.full((len(lengths), width), float("-inf"))
+    for r, n in enumerate(lengths):
+        logits[r, :n] = torch.randn(n, generator=g)
+    lens = torch.tensor(lengths, dtype=torch.int32)
+    want = torch.zeros(len(lengths), k, dtype=torch.int32)
+    c_oracle.top_k_per_row_prefill(logits, torch.zeros(len(lengths), dtype=torch.int32), lens, want, len(lengths), logits.stride(0), 1, k)
+    got = torch.full((len(lengths), k), 7, dtype=torch.int32, device=DEV)
+    workspace = torch.full((1 << 16,), 0x5A, dtype=torch.uint8, device=DEV)
+    flaggems_vllm.persistent_topk(logits.to(DEV), (lens.view(1, -1) if two_d else lens).to(DEV), got, workspace, k=k, max_seq_len=max(lengths))
+    starts = torch.zeros(len(lengths))
+    assert torch.equal(selected_values(logits, got, starts, lens, k), selected_values(logits, want, starts, lens, k))
+    assert bool((workspace == 0x5A).all())
+
+
 def test_host_checks_without_gpu():
     logits, idx = torch.zeros(2, 100), torch.zeros(2, 8, dtype=torch.int32)
     with pytest.raises(AssertionError, match="no CPU path"):
