@@ -355,6 +355,13 @@ def sibling_ops(steps, warmup):
                                        "hbm_gbs": nt * (4 * tk + 4 * (tk + window) + 4) * steps / secs / 1e9,
                                        "note": "includes torch.empty of the outputs per call; positions 6144-8191, so every row has 512 + 128 entries"}
     del tki
+    # activation quantiser in front of the FP8 projections: 32768 tokens x 7168, groups of 128
+    xa = torch.randn(32768, 7168, generator=g, device=dev).to(torch.bfloat16)
+    for ue8m0, key in ((True, "per_token_group_quant_fp8[ue8m0 scales]"), (False, "per_token_group_quant_fp8[fp32 scales]")):
+        secs = time_steps(lambda: flaggems_vllm.per_token_group_quant_fp8(xa, 128, scale_ue8m0=ue8m0), steps, warmup, stream, torch.cuda.synchronize)
+        out[key] = {"tokens": 32768, "columns": 7168, "us_per_launch": secs / steps * 1e6,
+                    "hbm_gbs": xa.numel() * (2 + 1 + 4 / 128) * steps / secs / 1e9, "note": "includes torch.empty of the two outputs per call"}
+    del xa
     # top-k selection over the indexer logits: one decode row, a decode batch, a prefill chunk (rotating inputs larger than L2)
     try:
         import vllm._custom_ops  # noqa: F401  (loads torch.ops._C)

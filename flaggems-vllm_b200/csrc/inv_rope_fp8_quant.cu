@@ -27,46 +27,6 @@ struct InvRopeParams {
     uint32_t hpg_mul, hpg_shift;      // fast division of a head index by heads_per_group
 };
 
-// Power-of-two scale >= s as (exponent byte, value): ceil(log2(max(s, 1e-10))) from the bit pattern.
-__device__ __forceinline__ uint32_t pow2_ceil_code(float s) {
-    const uint32_t u = __float_as_uint(fmaxf(s, 1e-10f));
-    return ((u >> 23) & 0xffu) + ((u & 0x7fffffu) ? 1u : 0u);
-}
-
-// x / scale for a scale that is not a power of two.  FAST: y = RN(1/scale) once, then per value q0 = x*y,
-// r = fma(-scale, q0, x), q = fma(r, y, q0) - three instructions instead of an IEEE division.  q can differ from
-// RN(x/scale) in the last fp32 bit, but never in the e4m3 byte: a CPU test enumerates every bf16 group maximum
-// (hence every reachable scale, for the reference's eps = 1e-10) against every bf16 value below it - 5.3e8 pairs,
-// zero differing bytes.  For any other eps the kernel divides.
-template <bool FAST>
-__device__ __forceinline__ float div_by_scale(float x, float scale, float recip) {
-    if (!FAST) return __fdiv_rn(x, scale);
-    const float q0 = __fmul_rn(x, recip);
-    return fmaf(fmaf(-scale, q0, x), recip, q0);
-}
-
-template <bool FAST>
-__device__ __forceinline__ uint2 quant8_by(const uint4& v, float scale) {
-    float x[8];
-    unpack8(v, x);
-    const float recip = FAST ? __frcp_rn(scale) : 0.0f;
-    float q[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) q[i] = div_by_scale<FAST>(x[i], scale, recip);  // the e4m3 conversion saturates at +-448
-    return make_uint2(pack_e4m3x4(q[0], q[1], q[2], q[3]), pack_e4m3x4(q[4], q[5], q[6], q[7]));
-}
-
-// 8 values times the exact reciprocal of a power-of-two scale (same result as dividing by it).
-__device__ __forceinline__ uint2 quant8_pow2(const uint4& v, uint32_t code) {
-    float x[8];
-    unpack8(v, x);
-    const float inv = __uint_as_float((254u - code) << 23);
-    float q[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) q[i] = __fmul_rn(x[i], inv);
-    return make_uint2(pack_e4m3x4(q[0], q[1], q[2], q[3]), pack_e4m3x4(q[4], q[5], q[6], q[7]));
-}
-
 // PACKED: power-of-two scales, the 4 UE8M0 bytes of a head packed into one int32.
 // A warp owns kHeadsPerTask consecutive heads of one token and walks them U at a time.  Rows are held in the
 // A/B/T layout (A: 16 B per lane, B: 16 B in lanes 0-23, T: the 4-byte rotary pair 448+2l, 449+2l of lane l), so

@@ -24,6 +24,7 @@ EXPORTS = (
     "dsv4_cp_gather_indexer_k_quant_cache",
     "dsv4_compute_global_topk_indices_and_lens",
     "dsv4_combine_topk_swa_indices",
+    "dsv4_per_token_group_quant_fp8",
     "dsv4_top_k_per_row_decode",
     "dsv4_top_k_per_row_prefill",
     "dsv4_fused_indexer_q_rope_quant",
@@ -87,6 +88,8 @@ def lib() -> ctypes.CDLL:
     L.dsv4_compute_global_topk_indices_and_lens.restype = i32
     L.dsv4_combine_topk_swa_indices.argtypes = [vp, i64, i64, vp, vp, vp, vp, i64, i64, vp, i64, i64, i64, i64, i64, i64, i64, vp]
     L.dsv4_combine_topk_swa_indices.restype = i32
+    L.dsv4_per_token_group_quant_fp8.argtypes = [vp, i64, vp, vp, i64, i64, i64, i64, i64, f32, i32, vp]
+    L.dsv4_per_token_group_quant_fp8.restype = i32
     L.dsv4_top_k_per_row_decode.argtypes = [vp, i64, i64, i64, vp, vp, i64, i64, i64, vp]
     L.dsv4_top_k_per_row_decode.restype = i32
     L.dsv4_top_k_per_row_prefill.argtypes = [vp, i64, i64, vp, vp, vp, i64, i64, i64, vp]

@@ -14,6 +14,7 @@ from .fused_inv_rope_fp8_quant import fused_inv_rope_fp8_quant
 from .gather_dequant_k_cache import gather_dequant_k_cache_slots
 from .host_staged import HostStagedPrologue
 from .indexer_k_quant_and_cache import indexer_k_quant_and_cache
+from .per_token_group_quant_fp8 import per_token_group_quant_fp8
 from .persistent_topk import persistent_topk
 from .top_k_per_row_decode import top_k_per_row_decode
 from .top_k_per_row_prefill import top_k_per_row_prefill
@@ -24,6 +25,7 @@ __all__ = [
     "cp_gather_indexer_k_quant_cache",
     "combine_topk_swa_indices",
     "compute_global_topk_indices_and_lens",
+    "per_token_group_quant_fp8",
     "persistent_topk",
     "top_k_per_row_decode",
     "top_k_per_row_prefill",

@@ -250,6 +250,20 @@ int dsv4_top_k_per_row_prefill(const float* logits, int64_t stride0, int64_t str
                                void* cuda_stream);
 
 /*
+ * The activation quantiser in front of the FP8 projections.  Replaces the reference operator
+ *   per_token_group_quant_fp8(x, group_size, eps, dtype, column_major_scales, scale_ue8m0)
+ * (src/flaggems_vllm/ops/per_token_group_quant_fp8.py:226-330, kernels :25-215) for bf16 x [num_rows, num_cols]
+ * (row stride in elements, unit inner stride) and e4m3fn output (contiguous [num_rows, num_cols] bytes): per group of
+ * group_size consecutive values scale = max(amax, eps) * (1/448), made 2^ceil(log2(scale)) when scale_is_ue8m0, and
+ * bytes = e4m3(x / scale).  The fp32 scale of (row, group) goes to scales[row*scale_stride_row +
+ * group*scale_stride_group] (row-major [num_rows, num_cols/group_size]: strides (num_cols/group_size, 1); the
+ * reference's column-major layout: (1, num_rows)).
+ */
+int dsv4_per_token_group_quant_fp8(const void* x, int64_t x_row_stride, void* out, float* scales, int64_t scale_stride_row,
+                                   int64_t scale_stride_group, int64_t num_rows, int64_t num_cols, int64_t group_size, float eps,
+                                   int32_t scale_is_ue8m0, void* cuda_stream);
+
+/*
  * The sparse-indexer prologue.  Replaces the reference operator
  *   fused_indexer_q_rope_quant(positions, index_q, index_q_cos_sin_cache, index_weights,
  *                              index_weights_softmax_scale, index_weights_head_scale, use_fp4)

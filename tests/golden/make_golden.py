@@ -357,6 +357,28 @@ def types_namespace():
     return types.SimpleNamespace(torch_device_fn=types.SimpleNamespace(is_available=lambda: True, device_count=lambda: 1))
 
 
+def group_quant_cases() -> None:
+    """Seeded activations through the upstream test's torch statement `native_per_token_group_quant_fp8`
+    (tests/test_per_token_group_quant_fp8.py:53-89), at the test's group sizes (64 ... 512), both scale formats, with the
+    test's uniform inputs and with normal ones that include a zero group, a tiny group and an exact-power-of-two maximum."""
+    M = ref_loader.load_upstream_helper_test("test_per_token_group_quant_fp8.py", "flaggems_vllm.ops", ("per_token_group_quant_fp8",),
+                                             sibling_modules={"accuracy_utils": {"FP8_QUANT_SHAPES": {"SEEDS": [0], "GROUP_SIZE": [64], "DTYPES": [torch.bfloat16], "D": [512], "NUM_TOKENS": [7]},
+                                                                                 "to_reference": lambda t: t, "gems_assert_close": None, "to_cpu": lambda a, b: a}})
+    idx = 0
+    for tokens, cols, group in ((7, 512, 64), (7, 512, 128), (5, 1024, 256), (3, 1024, 512)):
+        for ue8m0 in (False, True):
+            torch.manual_seed(900 + idx)
+            x = torch.rand(tokens, cols, dtype=torch.bfloat16) if idx % 4 < 2 else torch.randn(tokens, cols).to(torch.bfloat16)
+            x[0, :group] = 0
+            x[1, :group] *= 1e-12
+            x[2, 0] = 448.0
+            q, sc = M.native_per_token_group_quant_fp8(x, group, dtype=torch.float8_e4m3fn, scale_ue8m0=ue8m0)
+            np.savez_compressed(HERE / f"group_quant_t{tokens}_k{cols}_g{group}_{'ue8m0' if ue8m0 else 'fp32'}.npz", x=u16(x), group_size=group,
+                                ue8m0=int(ue8m0), bytes=q.view(torch.uint8).numpy(), scales=sc.numpy())
+            print("group_quant", tokens, cols, group, ue8m0, "ok")
+            idx += 1
+
+
 def _parameter_sets(test_function):
     return [m for m in test_function.pytestmark if m.name == "parametrize"][0].args[1]
 
@@ -419,6 +441,8 @@ def index_cases() -> None:
 if __name__ == "__main__":
     if len(sys.argv) < 2 or sys.argv[1] == "flash_mla":
         flash_mla_builder_case()
+    if len(sys.argv) < 2 or sys.argv[1] == "group_quant":
+        group_quant_cases()
     if len(sys.argv) < 2 or sys.argv[1] == "topk":
         topk_cases()
     if len(sys.argv) < 2 or sys.argv[1] == "index":

@@ -145,3 +145,17 @@ def test_top_k_oracle_against_upstream_torch_statements():
     ref = P.reference_top_k_per_row(logits.clone(), starts, ends, 256)
     c_oracle.top_k_per_row_prefill(logits, starts, ends, got, 6, logits.stride(0), 1, 256)
     assert P.check_topk_values_match(logits, got, ref, starts, 256)
+
+
+def test_group_quant_oracle_against_upstream_torch_statement():
+    M = ref_loader.load_upstream_helper_test(
+        "test_per_token_group_quant_fp8.py", "flaggems_vllm.ops", ("per_token_group_quant_fp8",),
+        sibling_modules={"accuracy_utils": {"FP8_QUANT_SHAPES": {"SEEDS": [0], "GROUP_SIZE": [64], "DTYPES": [torch.bfloat16], "D": [512], "NUM_TOKENS": [7]},
+                                            "to_reference": lambda t: t, "gems_assert_close": None, "to_cpu": lambda a, b: a}})
+    g = torch.Generator().manual_seed(66)
+    x = (torch.randn(50, 2048, generator=g) * torch.logspace(-13, 3, 50)[:, None]).to(torch.bfloat16)
+    for group in (64, 128, 256, 512):
+        for ue8m0 in (False, True):
+            want_q, want_s = M.native_per_token_group_quant_fp8(x, group, dtype=torch.float8_e4m3fn, scale_ue8m0=ue8m0)
+            q, s = c_oracle.per_token_group_quant_fp8(x, group, scale_ue8m0=ue8m0)
+            assert torch.equal(q, want_q.view(torch.uint8)) and torch.equal(s.view(torch.int32), want_s.view(torch.int32))
