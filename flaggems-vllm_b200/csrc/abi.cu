@@ -306,9 +306,10 @@ int dsv4_top_k_per_row_prefill(const float* logits, int64_t stride0, int64_t str
                                                 static_cast<cudaStream_t>(cuda_stream)));
 }
 
-int dsv4_per_token_group_quant_fp8(const void* x, int64_t x_row_stride, void* out, float* scales, int64_t scale_stride_row,
-                                   int64_t scale_stride_group, int64_t num_rows, int64_t num_cols, int64_t group_size, float eps,
-                                   int32_t scale_is_ue8m0, void* cuda_stream) {
+namespace {
+int group_quant(const void* x, int64_t x_row_stride, void* out, float* scales, int64_t scale_stride_row, int64_t scale_stride_group,
+                int64_t num_rows, int64_t num_cols, int64_t group_size, float eps, int32_t scale_is_ue8m0, int act_quant_rules,
+                void* cuda_stream) {
     if (num_rows < 0 || num_cols < 0 || group_size <= 0 || group_size >= (1LL << 24) || num_cols % group_size != 0 ||
         x_row_stride < num_cols)
         return DSV4_ERR_BAD_SIZE;
@@ -316,8 +317,22 @@ int dsv4_per_token_group_quant_fp8(const void* x, int64_t x_row_stride, void* ou
     if (!x || !out || !scales) return DSV4_ERR_NULL_POINTER;
     if ((reinterpret_cast<uintptr_t>(x) & 1u) != 0 || (reinterpret_cast<uintptr_t>(scales) & 3u) != 0) return DSV4_ERR_MISALIGNED;
     return static_cast<int>(launch_group_quant_fp8(x, x_row_stride, out, scales, scale_stride_row, scale_stride_group, num_rows, num_cols,
-                                                   static_cast<int>(group_size), eps, scale_is_ue8m0 ? 1 : 0,
+                                                   static_cast<int>(group_size), eps, scale_is_ue8m0 ? 1 : 0, act_quant_rules,
                                                    static_cast<cudaStream_t>(cuda_stream)));
+}
+}  // namespace
+
+int dsv4_per_token_group_quant_fp8(const void* x, int64_t x_row_stride, void* out, float* scales, int64_t scale_stride_row,
+                                   int64_t scale_stride_group, int64_t num_rows, int64_t num_cols, int64_t group_size, float eps,
+                                   int32_t scale_is_ue8m0, void* cuda_stream) {
+    return group_quant(x, x_row_stride, out, scales, scale_stride_row, scale_stride_group, num_rows, num_cols, group_size, eps,
+                       scale_is_ue8m0, 0, cuda_stream);
+}
+
+int dsv4_act_quant(const void* x, int64_t x_row_stride, void* out, float* scales, int64_t num_rows, int64_t num_cols, int64_t block_size,
+                   int32_t round_scale, void* cuda_stream) {
+    return group_quant(x, x_row_stride, out, scales, block_size > 0 ? num_cols / block_size : 0, 1, num_rows, num_cols, block_size, 1e-4f,
+                       round_scale, 1, cuda_stream);
 }
 
 int dsv4_fused_indexer_q_rope_quant(const int64_t* positions, const void* index_q, int64_t q_stride0, int64_t q_stride1,

@@ -309,26 +309,30 @@ __device__ __forceinline__ uint32_t pow2_ceil_code(float s) {
     return ((u >> 23) & 0xffu) + ((u & 0x7fffffu) ? 1u : 0u);
 }
 
-// x / scale for a scale that is not a power of two.  FAST: y = RN(1/scale) once, then per value q0 = x*y,
-// r = fma(-scale, q0, x), q = fma(r, y, q0) - three instructions instead of an IEEE division.  q can differ from
-// RN(x/scale) in the last fp32 bit, but never in the e4m3 byte: a CPU test enumerates every bf16 group maximum
-// (hence every reachable scale, for the reference's eps = 1e-10) against every bf16 value below it - 5.3e8 pairs,
-// zero differing bytes.  For any other eps the kernel divides.
-template <bool FAST>
+// How x / scale is formed for a scale that is not a power of two.
+enum : int { kDivideIeee = 0, kDivideFast = 1, kMultiplyReciprocal = 2 };
+
+// kDivideFast: y = RN(1/scale) once, then per value q0 = x*y, r = fma(-scale, q0, x), q = fma(r, y, q0) - three
+// instructions instead of an IEEE division.  q can differ from RN(x/scale) in the last fp32 bit, but never in the
+// e4m3 byte: a CPU test enumerates every bf16 group maximum (hence every reachable scale, for the reference's
+// eps = 1e-10) against every bf16 value below it - 5.3e8 pairs, zero differing bytes.  For any other eps the
+// kernels divide.  kMultiplyReciprocal: x * RN(1/scale), which is what the statement of `act_quant` computes.
+template <int MODE>
 __device__ __forceinline__ float div_by_scale(float x, float scale, float recip) {
-    if (!FAST) return __fdiv_rn(x, scale);
+    if (MODE == kDivideIeee) return __fdiv_rn(x, scale);
     const float q0 = __fmul_rn(x, recip);
+    if (MODE == kMultiplyReciprocal) return q0;
     return fmaf(fmaf(-scale, q0, x), recip, q0);
 }
 
-template <bool FAST>
+template <int MODE>
 __device__ __forceinline__ uint2 quant8_by(const uint4& v, float scale) {
     float x[8];
     unpack8(v, x);
-    const float recip = FAST ? __frcp_rn(scale) : 0.0f;
+    const float recip = MODE != kDivideIeee ? __frcp_rn(scale) : 0.0f;
     float q[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) q[i] = div_by_scale<FAST>(x[i], scale, recip);  // the e4m3 conversion saturates at +-448
+    for (int i = 0; i < 8; ++i) q[i] = div_by_scale<MODE>(x[i], scale, recip);  // the e4m3 conversion saturates at +-448
     return make_uint2(pack_e4m3x4(q[0], q[1], q[2], q[3]), pack_e4m3x4(q[4], q[5], q[6], q[7]));
 }
 
@@ -446,7 +450,7 @@ cudaError_t launch_topk_per_row(const float* logits, int64_t stride0, int64_t st
                                 cudaStream_t stream);
 cudaError_t launch_group_quant_fp8(const void* x, int64_t x_stride, void* out, float* scales, int64_t scale_stride_row,
                                    int64_t scale_stride_group, int64_t num_rows, int64_t num_cols, int group_size, float eps, int ue8m0,
-                                   cudaStream_t stream);
+                                   int act_quant_rules, cudaStream_t stream);
 cudaError_t launch_indexer_q_rope_quant(const int64_t* positions, const void* q, int64_t q_stride0, int64_t q_stride1,
                                         const void* cos_sin, int64_t cos_sin_stride, int cos_sin_bf16, int rot_dim, void* out,
                                         int64_t out_stride0, int64_t out_stride1, void* scales, int64_t scale_stride0,

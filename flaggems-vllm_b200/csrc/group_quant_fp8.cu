@@ -5,6 +5,8 @@
 // tests/test_per_token_group_quant_fp8.py:53-89:
 //   scale = max(amax, eps) * (1/448), rounded up to a power of two when scale_ue8m0; x_q = e4m3(clamp(x / scale)).
 //   The statement clamps the maximum while it still has the input's type, so eps takes effect rounded to bf16.
+// Also `act_quant_triton` (src/flaggems_vllm/ops/act_quant.py:22-175, statement tests/test_act_quant.py:49-99): the same
+// operator with the maximum clamped at 1e-4 in fp32 and x * (1/scale) in place of the division.
 // HBM traffic: 2 bytes read, 1 byte + 4/group_size bytes written per value.
 #include <cstring>
 
@@ -26,9 +28,9 @@ struct GroupQuantParams {
 };
 
 // LANES adjacent lanes per group, CHUNKS x 8 values per lane (group_size = LANES * CHUNKS * 8), U groups per lane
-// group in flight.  UE8M0: power-of-two scales (exact reciprocal multiply); FASTDIV: the verified
-// reciprocal-and-correct division for the default eps.
-template <int WARPS, int LANES, int CHUNKS, int U, bool UE8M0, bool FASTDIV>
+// group in flight.  UE8M0: power-of-two scales (exact reciprocal multiply); DIVISION: how x / scale is formed otherwise
+// (IEEE division, the verified reciprocal-and-correct division for the default eps, or x * (1/scale) for `act_quant`).
+template <int WARPS, int LANES, int CHUNKS, int U, bool UE8M0, int DIVISION>
 __global__ void __launch_bounds__(WARPS * 32) group_quant_fp8_kernel(const GroupQuantParams p) {
     constexpr int kGroups = 32 / LANES;
     const int lane = threadIdx.x & 31;
@@ -73,14 +75,14 @@ __global__ void __launch_bounds__(WARPS * 32) group_quant_fp8_kernel(const Group
         uint8_t* dst = p.out + g * p.group_size;
 #pragma unroll
         for (int c = 0; c < CHUNKS; ++c)
-            st_global8(dst + 8 * (sub + c * LANES), UE8M0 ? quant8_pow2(v[u][c], code) : quant8_by<FASTDIV>(v[u][c], scale));
+            st_global8(dst + 8 * (sub + c * LANES), UE8M0 ? quant8_pow2(v[u][c], code) : quant8_by<DIVISION>(v[u][c], scale));
         if (sub == 0) p.scales[row[u] * p.scale_stride_row + col[u] * p.scale_stride_group] = scale;
     }
 }
 
 // Any group size and alignment: one warp per group, element by element.
 template <int WARPS>
-__global__ void __launch_bounds__(WARPS * 32) group_quant_fp8_scalar_kernel(const GroupQuantParams p, const int ue8m0) {
+__global__ void __launch_bounds__(WARPS * 32) group_quant_fp8_scalar_kernel(const GroupQuantParams p, const int ue8m0, const int reciprocal) {
     const int lane = threadIdx.x & 31;
     const int64_t g = static_cast<int64_t>(blockIdx.x) * WARPS + (threadIdx.x >> 5);
     if (g >= p.num_groups) return;
@@ -94,26 +96,28 @@ __global__ void __launch_bounds__(WARPS * 32) group_quant_fp8_scalar_kernel(cons
     float scale = __fmul_rn(fmaxf(amax, p.eps), 1.0f / 448.0f);
     if (ue8m0) scale = __uint_as_float(pow2_ceil_code(scale) << 23);
     uint8_t* dst = p.out + g * p.group_size;
+    const float recip = __frcp_rn(scale);
     for (int i = lane; i < p.group_size; i += 32)
-        dst[i] = static_cast<uint8_t>(pack_e4m3x4(__fdiv_rn(bf16_lo(src[i]), scale), 0.0f, 0.0f, 0.0f) & 0xffu);
+        dst[i] = static_cast<uint8_t>(pack_e4m3x4(reciprocal ? __fmul_rn(bf16_lo(src[i]), recip) : __fdiv_rn(bf16_lo(src[i]), scale), 0.0f, 0.0f, 0.0f) & 0xffu);
     if (lane == 0) p.scales[row * p.scale_stride_row + col * p.scale_stride_group] = scale;
 }
 
 template <int LANES, int CHUNKS>
-void launch_vector(const GroupQuantParams& p, bool ue8m0, bool fastdiv, cudaStream_t stream) {
+void launch_vector(const GroupQuantParams& p, bool ue8m0, int division, cudaStream_t stream) {
     constexpr int WARPS = 4, U = CHUNKS == 1 ? 4 : 2;
     const int64_t per_cta = static_cast<int64_t>(WARPS) * (32 / LANES) * U;
     const unsigned grid = static_cast<unsigned>((p.num_groups + per_cta - 1) / per_cta);
-    if (ue8m0) group_quant_fp8_kernel<WARPS, LANES, CHUNKS, U, true, false><<<grid, WARPS * 32, 0, stream>>>(p);
-    else if (fastdiv) group_quant_fp8_kernel<WARPS, LANES, CHUNKS, U, false, true><<<grid, WARPS * 32, 0, stream>>>(p);
-    else group_quant_fp8_kernel<WARPS, LANES, CHUNKS, U, false, false><<<grid, WARPS * 32, 0, stream>>>(p);
+    if (ue8m0) group_quant_fp8_kernel<WARPS, LANES, CHUNKS, U, true, kDivideIeee><<<grid, WARPS * 32, 0, stream>>>(p);
+    else if (division == kDivideFast) group_quant_fp8_kernel<WARPS, LANES, CHUNKS, U, false, kDivideFast><<<grid, WARPS * 32, 0, stream>>>(p);
+    else if (division == kMultiplyReciprocal) group_quant_fp8_kernel<WARPS, LANES, CHUNKS, U, false, kMultiplyReciprocal><<<grid, WARPS * 32, 0, stream>>>(p);
+    else group_quant_fp8_kernel<WARPS, LANES, CHUNKS, U, false, kDivideIeee><<<grid, WARPS * 32, 0, stream>>>(p);
 }
 
 }  // namespace
 
 cudaError_t launch_group_quant_fp8(const void* x, int64_t x_stride, void* out, float* scales, int64_t scale_stride_row,
                                    int64_t scale_stride_group, int64_t num_rows, int64_t num_cols, int group_size, float eps, int ue8m0,
-                                   cudaStream_t stream) {
+                                   int act_quant_rules, cudaStream_t stream) {
     const int64_t groups_per_row = num_cols / group_size;
     const int64_t num_groups = num_rows * groups_per_row;
     if (num_groups == 0) return cudaSuccess;
@@ -122,7 +126,8 @@ cudaError_t launch_group_quant_fp8(const void* x, int64_t x_stride, void* out, f
     p.x = static_cast<const uint8_t*>(x), p.x_stride = x_stride, p.out = static_cast<uint8_t*>(out), p.scales = scales;
     p.scale_stride_row = scale_stride_row, p.scale_stride_group = scale_stride_group, p.num_groups = num_groups;
     p.groups_per_row = static_cast<int32_t>(groups_per_row), p.group_size = group_size;
-    {  // eps rounded to bf16 (nearest even), as a clamp of a bf16 tensor applies it
+    p.eps = eps;
+    if (!act_quant_rules) {  // eps rounded to bf16 (nearest even), as a clamp of a bf16 tensor applies it
         uint32_t bits;
         memcpy(&bits, &eps, 4);
         bits = (bits + 0x7fffu + ((bits >> 16) & 1u)) & 0xffff0000u;
@@ -132,18 +137,18 @@ cudaError_t launch_group_quant_fp8(const void* x, int64_t x_stride, void* out, f
     const auto addr = [](const void* q) { return reinterpret_cast<uintptr_t>(q); };
     const bool vec = addr(x) % 16 == 0 && x_stride % 8 == 0 && addr(out) % 8 == 0 &&
                      (group_size == 64 || group_size == 128 || group_size == 256 || group_size == 512);
-    const bool fastdiv = eps == 1e-10f;
+    const int division = act_quant_rules ? kMultiplyReciprocal : (eps == 1e-10f ? kDivideFast : kDivideIeee);
     if (!vec) {
         constexpr int WARPS = 4;
-        group_quant_fp8_scalar_kernel<WARPS><<<static_cast<unsigned>((num_groups + WARPS - 1) / WARPS), WARPS * 32, 0, stream>>>(p, ue8m0);
+        group_quant_fp8_scalar_kernel<WARPS><<<static_cast<unsigned>((num_groups + WARPS - 1) / WARPS), WARPS * 32, 0, stream>>>(p, ue8m0, act_quant_rules);
     } else if (group_size == 64) {
-        launch_vector<8, 1>(p, ue8m0 != 0, fastdiv, stream);
+        launch_vector<8, 1>(p, ue8m0 != 0, division, stream);
     } else if (group_size == 128) {
-        launch_vector<16, 1>(p, ue8m0 != 0, fastdiv, stream);
+        launch_vector<16, 1>(p, ue8m0 != 0, division, stream);
     } else if (group_size == 256) {
-        launch_vector<32, 1>(p, ue8m0 != 0, fastdiv, stream);
+        launch_vector<32, 1>(p, ue8m0 != 0, division, stream);
     } else {
-        launch_vector<32, 2>(p, ue8m0 != 0, fastdiv, stream);
+        launch_vector<32, 2>(p, ue8m0 != 0, division, stream);
     }
     count_launch();
     return cudaGetLastError();

@@ -117,11 +117,11 @@ __global__ void __launch_bounds__(WARPS * 32, MIN_CTAS) inv_rope_fp8_quant_kerne
                 const uint32_t word = mine | (__shfl_xor_sync(0xffffffffu, mine, 16) << 8);
                 if (lane == 0) *reinterpret_cast<uint32_t*>(scale_row + head_in_group * p.padded_tokens * 4) = word;
             } else {
-                st_global8(out + 8 * lane, quant8_by<FASTDIV>(a[u], sa));
-                if (lane < kFirstRopeLane) st_global8(out + 256 + 8 * lane, quant8_by<FASTDIV>(b[u], sb));
+                st_global8(out + 8 * lane, quant8_by<FASTDIV ? kDivideFast : kDivideIeee>(a[u], sa));
+                if (lane < kFirstRopeLane) st_global8(out + 256 + 8 * lane, quant8_by<FASTDIV ? kDivideFast : kDivideIeee>(b[u], sb));
                 const float r3 = FASTDIV ? __frcp_rn(s3) : 0.0f;
                 *reinterpret_cast<uint16_t*>(out + kNopeDim + 2 * lane) = static_cast<uint16_t>(
-                    pack_e4m3x4(div_by_scale<FASTDIV>(te, s3, r3), div_by_scale<FASTDIV>(to, s3, r3), 0.f, 0.f));
+                    pack_e4m3x4(div_by_scale<FASTDIV ? kDivideFast : kDivideIeee>(te, s3, r3), div_by_scale<FASTDIV ? kDivideFast : kDivideIeee>(to, s3, r3), 0.f, 0.f));
                 if ((lane & 15) == 0) {
                     const int k = head_in_group * 4 + (lane >> 4);
                     *reinterpret_cast<float*>(scale_row + k * p.padded_tokens * 4) = sa;

@@ -25,6 +25,7 @@ EXPORTS = (
     "dsv4_compute_global_topk_indices_and_lens",
     "dsv4_combine_topk_swa_indices",
     "dsv4_per_token_group_quant_fp8",
+    "dsv4_act_quant",
     "dsv4_top_k_per_row_decode",
     "dsv4_top_k_per_row_prefill",
     "dsv4_fused_indexer_q_rope_quant",
@@ -90,6 +91,8 @@ def lib() -> ctypes.CDLL:
     L.dsv4_combine_topk_swa_indices.restype = i32
     L.dsv4_per_token_group_quant_fp8.argtypes = [vp, i64, vp, vp, i64, i64, i64, i64, i64, f32, i32, vp]
     L.dsv4_per_token_group_quant_fp8.restype = i32
+    L.dsv4_act_quant.argtypes = [vp, i64, vp, vp, i64, i64, i64, i32, vp]
+    L.dsv4_act_quant.restype = i32
     L.dsv4_top_k_per_row_decode.argtypes = [vp, i64, i64, i64, vp, vp, i64, i64, i64, vp]
     L.dsv4_top_k_per_row_decode.restype = i32
     L.dsv4_top_k_per_row_prefill.argtypes = [vp, i64, i64, vp, vp, vp, i64, i64, i64, vp]

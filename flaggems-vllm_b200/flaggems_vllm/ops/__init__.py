@@ -1,4 +1,5 @@
 """Operators of this package (reference: src/flaggems_vllm/ops/__init__.py:61-63,191)."""
+from .act_quant import act_quant_triton
 from .cp_gather_indexer_k_quant_cache import cp_gather_indexer_k_quant_cache
 from .deepseek_v4_attention_combine_topk_swa_indices import combine_topk_swa_indices
 from .deepseek_v4_attention_compute_global_topk_indices_and_lens import compute_global_topk_indices_and_lens
@@ -26,6 +27,7 @@ __all__ = [
     "combine_topk_swa_indices",
     "compute_global_topk_indices_and_lens",
     "per_token_group_quant_fp8",
+    "act_quant_triton",
     "persistent_topk",
     "top_k_per_row_decode",
     "top_k_per_row_prefill",

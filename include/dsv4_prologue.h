@@ -264,6 +264,16 @@ int dsv4_per_token_group_quant_fp8(const void* x, int64_t x_row_stride, void* ou
                                    int32_t scale_is_ue8m0, void* cuda_stream);
 
 /*
+ * Block-wise activation quantisation, DeepSeek's `act_quant`.  Replaces the reference operator
+ *   act_quant_triton(x, block_size, scale_fmt)
+ * (src/flaggems_vllm/ops/act_quant.py:113-175, kernel :46-110): as dsv4_per_token_group_quant_fp8 with row-major scales
+ * [num_rows, num_cols/block_size], except that the maximum is clamped at 1e-4 in fp32 and the bytes are
+ * e4m3(x * (1/scale)); round_scale (scale_fmt is not None) makes the scale 2^ceil(log2(scale)).
+ */
+int dsv4_act_quant(const void* x, int64_t x_row_stride, void* out, float* scales, int64_t num_rows, int64_t num_cols, int64_t block_size,
+                   int32_t round_scale, void* cuda_stream);
+
+/*
  * The sparse-indexer prologue.  Replaces the reference operator
  *   fused_indexer_q_rope_quant(positions, index_q, index_q_cos_sin_cache, index_weights,
  *                              index_weights_softmax_scale, index_weights_head_scale, use_fp4)

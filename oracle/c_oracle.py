@@ -56,7 +56,7 @@ def lib() -> ctypes.CDLL:
         L.dsv4_oracle_combine_topk_swa.restype = i32
         L.dsv4_oracle_top_k_per_row.argtypes = [vp, i64, i64, vp, vp, vp, i64, i64, i64]
         L.dsv4_oracle_top_k_per_row.restype = i32
-        L.dsv4_oracle_group_quant_fp8.argtypes = [vp, i64, vp, vp, i64, i64, i64, i64, i64, f32, i32]
+        L.dsv4_oracle_group_quant_fp8.argtypes = [vp, i64, vp, vp, i64, i64, i64, i64, i64, f32, i32, i32]
         L.dsv4_oracle_group_quant_fp8.restype = i32
         L.dsv4_oracle_indexer_q_rope_quant.argtypes = [vp, vp, vp, i64, vp, f32, f32, i64, i64, i64, i32, vp, vp, vp]
         L.dsv4_oracle_indexer_q_rope_quant.restype = i32
@@ -226,7 +226,7 @@ def top_k_per_row_decode(logits, next_n, seq_lens, indices, num_rows, stride0, s
     top_k_per_row_prefill(logits, torch.zeros(num_rows, dtype=torch.int32), ends, indices, num_rows, stride0, stride1, top_k)
 
 
-def per_token_group_quant_fp8(x, group_size, eps=1e-10, column_major_scales=False, scale_ue8m0=False):
+def per_token_group_quant_fp8(x, group_size, eps=1e-10, column_major_scales=False, scale_ue8m0=False, act_quant_rules=False):
     """(bytes uint8 shaped like x, scales fp32 [M, K / group_size]) on a CPU bf16 tensor [M, K] with unit inner stride;
     `column_major_scales` returns the scales with transposed storage, as the reference does."""
     assert x.device.type == "cpu" and x.dtype == torch.bfloat16 and x.dim() == 2 and x.stride(1) == 1
@@ -235,10 +235,15 @@ def per_token_group_quant_fp8(x, group_size, eps=1e-10, column_major_scales=Fals
     groups = cols // group_size
     scales = torch.empty(groups, rows).permute(1, 0) if column_major_scales else torch.empty(rows, groups)
     rc = lib().dsv4_oracle_group_quant_fp8(x.data_ptr(), x.stride(0), out.data_ptr(), scales.data_ptr(), scales.stride(0), scales.stride(1),
-                                           rows, cols, int(group_size), float(eps), 1 if scale_ue8m0 else 0)
+                                           rows, cols, int(group_size), float(eps), 1 if scale_ue8m0 else 0, 1 if act_quant_rules else 0)
     if rc != 0:
         raise ValueError("dsv4_oracle_group_quant_fp8 rejected its arguments")
     return out, scales
+
+
+def act_quant(x, block_size=128, scale_fmt=None):
+    """(bytes uint8, scales fp32) of the reference's `act_quant_triton` on a CPU bf16 tensor [M, N]."""
+    return per_token_group_quant_fp8(x, block_size, eps=1e-4, scale_ue8m0=scale_fmt is not None, act_quant_rules=True)
 
 
 def indexer_q_rope_quant(positions, index_q, cos_sin_cache, weights, softmax_scale, head_scale, use_fp4=False):

@@ -569,14 +569,17 @@ int dsv4_oracle_top_k_per_row(const float* logits, int64_t stride0, int64_t stri
  * src/flaggems_vllm/ops/per_token_group_quant_fp8.py:25-330: scale = max(amax, eps) * (1/448) in fp32, made
  * exp2(ceil(log2(max(scale, 1e-10)))) when ue8m0; bytes = e4m3(clamp(x / scale, -448, 448)).  The statement clamps the
  * maximum while it still has the input's type (:68), so eps takes effect rounded to bf16 (1e-10 -> 1.0004e-10).
+ * act_quant_rules: the statement of `act_quant` instead (tests/test_act_quant.py:49-99 of src/flaggems_vllm/ops/act_quant.py):
+ * eps applied in fp32 and bytes = e4m3(clamp(x * (1/scale))).
  * x bf16 [rows, cols] with a row stride in elements; out contiguous; scale of (row, group) at
  * row*scale_stride_row + group*scale_stride_group.
  */
 int dsv4_oracle_group_quant_fp8(const uint16_t* x, int64_t x_stride, uint8_t* out, float* scales, int64_t scale_stride_row,
-                                int64_t scale_stride_group, int64_t rows, int64_t cols, int64_t group_size, float eps, int ue8m0) {
+                                int64_t scale_stride_group, int64_t rows, int64_t cols, int64_t group_size, float eps, int ue8m0,
+                                int act_quant_rules) {
     if (rows < 0 || cols < 0 || group_size <= 0 || cols % group_size != 0) return -1;
     const float inv_max = 1.0f / 448.0f;
-    eps = bf16_bits_to_f32(f32_to_bf16_bits(eps));
+    if (!act_quant_rules) eps = bf16_bits_to_f32(f32_to_bf16_bits(eps));
     for (int64_t r = 0; r < rows; ++r) {
         for (int64_t g = 0; g < cols / group_size; ++g) {
             const uint16_t* src = x + r * x_stride + g * group_size;
@@ -588,7 +591,7 @@ int dsv4_oracle_group_quant_fp8(const uint16_t* x, int64_t x_stride, uint8_t* ou
             float scale = (amax > eps ? amax : eps) * inv_max;
             if (ue8m0) scale = exp2f(ceilf(log2f(scale > 1e-10f ? scale : 1e-10f)));
             for (int64_t i = 0; i < group_size; ++i) {
-                float q = bf16_bits_to_f32(src[i]) / scale;
+                float q = act_quant_rules ? bf16_bits_to_f32(src[i]) * (1.0f / scale) : bf16_bits_to_f32(src[i]) / scale;
                 q = q > 448.0f ? 448.0f : (q < -448.0f ? -448.0f : q);
                 out[r * cols + g * group_size + i] = f32_to_e4m3_bits(q);
             }

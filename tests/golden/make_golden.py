@@ -379,6 +379,25 @@ def group_quant_cases() -> None:
             idx += 1
 
 
+def act_quant_cases() -> None:
+    """Seeded activations through the upstream test's torch statement `torch_act_quant` (tests/test_act_quant.py:49-99)."""
+    M = ref_loader.load_upstream_helper_test("test_act_quant.py", "flaggems_vllm.ops", ("act_quant_triton",),
+                                             sibling_modules={"accuracy_utils": {"TO_CPU": False, "gems_assert_close": None}})
+    idx = 0
+    for rows, cols, block in ((40, 128, 128), (7, 896, 64), (5, 2048, 128)):
+        for fmt in (None, "ue8m0"):
+            torch.manual_seed(950 + idx)
+            x = torch.randn(rows, cols).to(torch.bfloat16)
+            x[0, :block] = 0
+            x[1, :block] *= 1e-6
+            x[2, 0] = 448.0
+            y, sc = M.torch_act_quant(x, block_size=block, scale_fmt=fmt)
+            np.savez_compressed(HERE / f"act_quant_m{rows}_n{cols}_b{block}_{fmt or 'fp32'}.npz", x=u16(x), block_size=block, round_scale=int(fmt is not None),
+                                bytes=y.view(torch.uint8).numpy(), scales=sc.numpy())
+            print("act_quant", rows, cols, block, fmt, "ok")
+            idx += 1
+
+
 def _parameter_sets(test_function):
     return [m for m in test_function.pytestmark if m.name == "parametrize"][0].args[1]
 
@@ -441,6 +460,8 @@ def index_cases() -> None:
 if __name__ == "__main__":
     if len(sys.argv) < 2 or sys.argv[1] == "flash_mla":
         flash_mla_builder_case()
+    if len(sys.argv) < 2 or sys.argv[1] == "act_quant":
+        act_quant_cases()
     if len(sys.argv) < 2 or sys.argv[1] == "group_quant":
         group_quant_cases()
     if len(sys.argv) < 2 or sys.argv[1] == "topk":

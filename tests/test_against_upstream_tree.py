@@ -159,3 +159,15 @@ def test_group_quant_oracle_against_upstream_torch_statement():
             want_q, want_s = M.native_per_token_group_quant_fp8(x, group, dtype=torch.float8_e4m3fn, scale_ue8m0=ue8m0)
             q, s = c_oracle.per_token_group_quant_fp8(x, group, scale_ue8m0=ue8m0)
             assert torch.equal(q, want_q.view(torch.uint8)) and torch.equal(s.view(torch.int32), want_s.view(torch.int32))
+
+
+def test_act_quant_oracle_against_upstream_torch_statement():
+    M = ref_loader.load_upstream_helper_test("test_act_quant.py", "flaggems_vllm.ops", ("act_quant_triton",),
+                                             sibling_modules={"accuracy_utils": {"TO_CPU": False, "gems_assert_close": None}})
+    g = torch.Generator().manual_seed(67)
+    x = (torch.randn(60, 1024, generator=g) * torch.logspace(-8, 3, 60)[:, None]).to(torch.bfloat16)
+    for block in (64, 128):
+        for fmt in (None, "ue8m0"):
+            want_q, want_s = M.torch_act_quant(x, block_size=block, scale_fmt=fmt)
+            q, s = c_oracle.act_quant(x, block, fmt)
+            assert torch.equal(q, want_q.view(torch.uint8)) and torch.equal(s.view(torch.int32), want_s.view(torch.int32))
