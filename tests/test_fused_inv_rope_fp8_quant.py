@@ -45,6 +45,10 @@ def test_division_shortcut_never_changes_a_byte():
     division.  Every reachable (scale, value) pair for bf16 inputs and the reference's eps: no e4m3 byte differs."""
     pairs, byte_mismatches, _ = c_oracle.check_division_shortcut(1e-10)
     assert pairs > 5e8 and byte_mismatches == 0
+    # per_token_group_quant_fp8 uses the same shortcut with eps rounded to bf16 (its statement clamps a bf16 tensor)
+    eps_bf16 = float(torch.tensor(1e-10).to(torch.bfloat16))
+    pairs, byte_mismatches, _ = c_oracle.check_division_shortcut(eps_bf16)
+    assert pairs > 5e8 and byte_mismatches == 0
 
 
 @pytest.mark.parametrize("packed", [False, True])
