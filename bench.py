@@ -158,6 +158,20 @@ def time_steps(fn, steps: int, warmup: int, stream, sync_all):
     return t0.elapsed_time(t1) * 1e-3
 
 
+def per_launch_times(fn, launches: int, stream, sync_all):
+    """Every launch between its own pair of CUDA events (after the timed region, not part of it): median and best, the
+    statistics the reference's harness reports, beside the mean over back-to-back launches that `value` uses."""
+    events = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(launches)]
+    sync_all()
+    for a, b in events:
+        a.record(stream)
+        fn()
+        b.record(stream)
+    sync_all()
+    ms = sorted(a.elapsed_time(b) for a, b in events)
+    return {"launches": launches, "median_ms": ms[len(ms) // 2], "best_ms": ms[0], "worst_ms": ms[-1]}
+
+
 def cpu_baseline(workload, budget_s: float = 12.0):
     """The CPU torch statement of the reference path (oracle/torch_path.py) on the first
     CPU_SAMPLE_TOKENS tokens of the workload, all host threads; best of >= 5 runs within a budget."""
@@ -619,6 +633,7 @@ def main():
     secs = time_steps(step, args.steps, args.warmup, stream, sync_all)
     launches = _native.launch_count() - launches0 - args.warmup
     clocks = sampler.stop() if sampler else None
+    launch_stats = per_launch_times(step, 30, stream, sync_all)
     my_bytes = w.algorithmic_bytes()
     agg = sharding.aggregate(secs, w.num_tokens, my_bytes, launches, status=_native.device_error(), device=dev)
     secs_max, tokens, nbytes, launches_total = agg["seconds"], float(agg["tokens"]), float(agg["bytes"]), agg["launches"]
@@ -657,7 +672,7 @@ def main():
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": traffic, "peak_source": f"{peak_kind} copy bandwidth",
                      "algorithmic_bytes_per_launch": int(largest_bytes),
-                     "kernel_ms": secs_max / args.steps * 1e3},
+                     "kernel_ms": secs_max / args.steps * 1e3, "kernel_ms_per_launch_rank0": launch_stats},
         "clocks": clocks, "gpu_launches": launches_total, "e2e": e2e,
         "host_numa_binding": (f"rank 0 bound to {len(numa_cores)} cores next to its GPU" if numa_cores else None),
     }
