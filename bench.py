@@ -572,6 +572,21 @@ def side_measurement(name, steps, warmup, op, native):
         gsecs = time_steps(graph.replay, replays, 2, stream, torch.cuda.synchronize)
         out["us_per_launch_cuda_graph"] = gsecs / (replays * sets) * 1e6
         out["hbm_gbs_cuda_graph"] = nbytes * replays * sets / gsecs / 1e9
+        # the same graph with programmatic dependent launch: each launch fetches its positions and table rows while
+        # the launch before it still runs (positions and table are not written inside the graph)
+        previous = native.set_pdl(True)
+        try:
+            with torch.cuda.stream(side):
+                side.wait_stream(stream)
+                graph_pdl = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph_pdl, stream=side):
+                    for _ in range(sets):
+                        fn()
+            stream.wait_stream(side)
+            psecs = time_steps(graph_pdl.replay, replays, 2, stream, torch.cuda.synchronize)
+            out["us_per_launch_cuda_graph_pdl"] = psecs / (replays * sets) * 1e6
+        finally:
+            native.set_pdl(previous)
     return out
 
 

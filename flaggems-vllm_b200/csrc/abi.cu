@@ -10,6 +10,7 @@ namespace dsv4 {
 namespace {
 std::atomic<int64_t> g_launches{0};
 std::atomic<int> g_variant{-1};  // -1: not initialised from the environment yet
+std::atomic<int> g_pdl{-1};      // programmatic dependent launch of the rows variant; -1: not initialised yet
 
 int current_variant() {
     int v = g_variant.load(std::memory_order_relaxed);
@@ -20,6 +21,16 @@ int current_variant() {
             if (parsed >= DSV4_VARIANT_AUTO && parsed <= DSV4_VARIANT_BULK) v = parsed;
         }
         g_variant.store(v, std::memory_order_relaxed);
+    }
+    return v;
+}
+
+int current_pdl() {
+    int v = g_pdl.load(std::memory_order_relaxed);
+    if (v < 0) {
+        const char* e = std::getenv("DSV4_PDL");
+        v = (e && std::atoi(e) != 0) ? 1 : 0;
+        g_pdl.store(v, std::memory_order_relaxed);
     }
     return v;
 }
@@ -65,6 +76,7 @@ PrologueParams make_params(void* q, const void* kv, void* k_cache, const int64_t
     p.block_stride = kv_block_stride_bytes;
     p.cache_aligned16 = aligned16(k_cache) && (kv_block_stride_bytes % 16 == 0);
     make_fast_divisor(static_cast<uint32_t>(num_heads > 0 ? num_heads : 1), &p.heads_mul, &p.heads_shift);
+    p.pdl = current_pdl();
     return p;
 }
 }  // namespace
@@ -390,6 +402,12 @@ int dsv4_set_variant(int variant) {
 }
 
 int dsv4_get_variant(void) { return current_variant(); }
+
+int dsv4_set_pdl(int enabled) {
+    const int previous = current_pdl();
+    g_pdl.store(enabled ? 1 : 0, std::memory_order_relaxed);
+    return previous;
+}
 
 int64_t dsv4_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 

@@ -53,6 +53,9 @@ struct PrologueParams {
     // heads num_heads..out_heads-1 of every token are zero-filled; q itself is then left untouched
     uint8_t* q_out;
     int64_t out_heads;
+    // programmatic dependent launch: read position_ids / slot_mapping / cos_sin before the preceding kernel of the
+    // stream has finished, wait for it only before touching q and kv (rows variant; 0 = ordinary launch)
+    int pdl;
 };
 
 // floor(n / d) for n < 2^31 via the multiplier the host derived with make_fast_divisor().

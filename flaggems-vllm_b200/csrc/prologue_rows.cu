@@ -18,7 +18,13 @@ namespace {
 
 // PADDED: out-of-place form (vLLM >= 0.22 calls the operator that way): rows go to p.q_out with out_heads heads per
 // token and the CTAs after the q tiles zero-fill the extra heads.
-template <int RPW, int WARPS, int MIN_CTAS, bool CHECKED, bool PADDED>
+// Programmatic dependent launch (sm_90+): the kernel may start while the preceding kernel of the stream still runs;
+// `wait` returns once that kernel has completed and its writes are visible (a no-op for an ordinary launch), and
+// `launch_dependents` lets the next kernel of the stream start its own independent part.
+__device__ __forceinline__ void wait_for_preceding_kernel() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void let_next_kernel_start() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <int RPW, int WARPS, int MIN_CTAS, bool CHECKED, bool PADDED, bool PDL = false>
 __global__ void __launch_bounds__(WARPS * 32, MIN_CTAS) prologue_rows_kernel(const PrologueParams p, const int64_t kv_ctas) {
     constexpr int TILE = RPW * WARPS;
     constexpr int MAX_TOKENS = TILE + 1;  // a tile of TILE rows touches at most TILE tokens (+1 slack)
@@ -42,15 +48,17 @@ __global__ void __launch_bounds__(WARPS * 32, MIN_CTAS) prologue_rows_kernel(con
                 return;
             }
         }
-        const uint8_t* row = p.kv + t * kRowBytes;
-        const uint4 a = ld_stream16(row + 16 * lane);
-        const uint4 b = ld_stream16(row + 512 + 16 * lane);
         float4 c = make_float4(0.f, 0.f, 0.f, 0.f), s = c;
         if (lane >= kFirstRopeLane) {
             const float* cs = p.cos_sin + pos * kRopeDim + 4 * (lane - kFirstRopeLane);
             c = ld_readonly_f4(cs);
             s = ld_readonly_f4(cs + 32);
         }
+        if (PDL) wait_for_preceding_kernel();  // kv (and the cache) may still be written by it
+        const uint8_t* row = p.kv + t * kRowBytes;
+        const uint4 a = ld_stream16(row + 16 * lane);
+        const uint4 b = ld_stream16(row + 512 + 16 * lane);
+        if (PDL) let_next_kernel_start();
         const int64_t block = slot / p.block_size, in_block = slot - block * p.block_size;
         uint8_t* base = p.k_cache + block * p.block_stride;
         kv_row_to_cache(a, b, lane, c, s, base + in_block * kTokenDataBytes,
@@ -80,38 +88,51 @@ __global__ void __launch_bounds__(WARPS * 32, MIN_CTAS) prologue_rows_kernel(con
         return;
     }
 
-    // 1. every row load of the CTA goes out first (A/B/T layout, 16 + 16 + 4 bytes per lane)
+    // 1. the row loads of the CTA (A/B/T layout, 16 + 16 + 4 bytes per lane)
     uint4 a[RPW], b[RPW];
     uint32_t tail[RPW];
+    const auto issue_row_loads = [&]() {
 #pragma unroll
-    for (int i = 0; i < RPW; ++i) {
-        a[i] = b[i] = make_uint4(0u, 0u, 0u, 0u);
-        tail[i] = 0u;
-        if (row0 + i < total_rows) {
-            const uint8_t* row = p.q + static_cast<uint64_t>(row0 + i) * kRowBytes;
-            a[i] = ld_stream16(row + 16 * lane);
-            if (lane < kFirstRopeLane) b[i] = ld_stream16(row + 512 + 16 * lane);
-            tail[i] = ld_stream4(row + 2 * kNopeDim + 4 * lane);
+        for (int i = 0; i < RPW; ++i) {
+            a[i] = b[i] = make_uint4(0u, 0u, 0u, 0u);
+            tail[i] = 0u;
+            if (row0 + i < total_rows) {
+                const uint8_t* row = p.q + static_cast<uint64_t>(row0 + i) * kRowBytes;
+                a[i] = ld_stream16(row + 16 * lane);
+                if (lane < kFirstRopeLane) b[i] = ld_stream16(row + 512 + 16 * lane);
+                tail[i] = ld_stream4(row + 2 * kNopeDim + 4 * lane);
+            }
         }
-    }
-
-    // 2. while they fly: cos|sin rows of the tokens this tile touches -> shared memory
-    //    (16 threads per token, 16 bytes each)
+    };
+    // 2. cos|sin rows of the tokens this tile touches -> shared memory (16 threads per token, 16 bytes each)
     const uint32_t first_token = fast_div(tile_row0, p.heads_mul, p.heads_shift);
     const uint32_t last_row = (tile_row0 + TILE < total_rows ? tile_row0 + TILE : total_rows) - 1;
     const int n_tokens = static_cast<int>(fast_div(last_row, p.heads_mul, p.heads_shift) - first_token) + 1;
-    for (int j = threadIdx.x >> 4; j < n_tokens; j += WARPS * 2) {
-        const int part = threadIdx.x & 15;
-        int64_t pos = p.position_ids[first_token + j];
-        if (CHECKED) {
-            const bool bad = pos < 0 || pos >= p.max_pos;
-            if (part == 0) {
-                bad_token[j] = bad ? 1 : 0;
-                if (bad) atomicOr(p.status, 1);
+    const auto stage_cos_sin = [&]() {
+        for (int j = threadIdx.x >> 4; j < n_tokens; j += WARPS * 2) {
+            const int part = threadIdx.x & 15;
+            int64_t pos = p.position_ids[first_token + j];
+            if (CHECKED) {
+                const bool bad = pos < 0 || pos >= p.max_pos;
+                if (part == 0) {
+                    bad_token[j] = bad ? 1 : 0;
+                    if (bad) atomicOr(p.status, 1);
+                }
+                if (bad) pos = 0;
             }
-            if (bad) pos = 0;
+            *reinterpret_cast<float4*>(&cs_smem[j][4 * part]) = ld_readonly_f4(p.cos_sin + pos * kRopeDim + 4 * part);
         }
-        *reinterpret_cast<float4*>(&cs_smem[j][4 * part]) = ld_readonly_f4(p.cos_sin + pos * kRopeDim + 4 * part);
+    };
+    if (PDL) {
+        // the table rows first (they do not depend on the preceding kernel), q only once that kernel has finished
+        stage_cos_sin();
+        wait_for_preceding_kernel();
+        issue_row_loads();
+        let_next_kernel_start();
+    } else {
+        // every row load goes out first; the table rows are fetched while they fly
+        issue_row_loads();
+        stage_cos_sin();
     }
     __syncthreads();
 
@@ -144,10 +165,20 @@ cudaError_t launch(const PrologueParams& p, bool checked, cudaStream_t stream) {
     const int64_t grid = kv_ctas + q_ctas;
     if (grid == 0) return cudaSuccess;
     if (grid > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
-    if (checked)
+    if (checked) {
         prologue_rows_kernel<RPW, WARPS, MIN_CTAS, true, false><<<static_cast<unsigned>(grid), WARPS * 32, 0, stream>>>(p, kv_ctas);
-    else
+    } else if (p.pdl) {
+        cudaLaunchConfig_t config = {};
+        config.gridDim = dim3(static_cast<unsigned>(grid)), config.blockDim = dim3(WARPS * 32), config.stream = stream;
+        cudaLaunchAttribute attribute[1];
+        attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attribute[0].val.programmaticStreamSerializationAllowed = 1;
+        config.attrs = attribute, config.numAttrs = 1;
+        const cudaError_t err = cudaLaunchKernelEx(&config, prologue_rows_kernel<RPW, WARPS, MIN_CTAS, false, false, true>, p, kv_ctas);
+        if (err != cudaSuccess) return err;
+    } else {
         prologue_rows_kernel<RPW, WARPS, MIN_CTAS, false, false><<<static_cast<unsigned>(grid), WARPS * 32, 0, stream>>>(p, kv_ctas);
+    }
     count_launch();
     return cudaGetLastError();
 }

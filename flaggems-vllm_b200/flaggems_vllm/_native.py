@@ -33,6 +33,7 @@ EXPORTS = (
     "dsv4_device_error",
     "dsv4_set_variant",
     "dsv4_get_variant",
+    "dsv4_set_pdl",
     "dsv4_launch_count",
     "dsv4_error_string",
     "dsv4_version",
@@ -104,6 +105,8 @@ def lib() -> ctypes.CDLL:
     L.dsv4_hbm_probe.restype = i32
     L.dsv4_device_error.argtypes = [vp]
     L.dsv4_device_error.restype = i32
+    L.dsv4_set_pdl.argtypes = [i32]
+    L.dsv4_set_pdl.restype = i32
     L.dsv4_set_variant.argtypes = [i32]
     L.dsv4_set_variant.restype = i32
     L.dsv4_get_variant.restype = i32
@@ -136,6 +139,11 @@ def set_variant(variant: int) -> int:
     if prev < 0:
         raise Dsv4Error(prev, lib().dsv4_error_string(prev).decode())
     return prev
+
+
+def set_pdl(enabled: bool) -> bool:
+    """Programmatic dependent launch of the prologue (see dsv4_set_pdl); returns the previous setting."""
+    return bool(lib().dsv4_set_pdl(1 if enabled else 0))
 
 
 def version() -> str:

@@ -320,6 +320,13 @@ int dsv4_device_error(int32_t* value_host);
 int dsv4_set_variant(int variant);
 int dsv4_get_variant(void);
 
+/* Programmatic dependent launch for dsv4_qnorm_rope_kv_insert (rows variant; also read once from the environment
+ * variable DSV4_PDL; off by default).  When on, the kernel is launched so that it may start before the preceding kernel
+ * of the stream has finished: it fetches position_ids, slot_mapping and the cos/sin rows at once and waits for that
+ * kernel only before it touches q, kv and the cache.  The caller promises that position_ids, slot_mapping and
+ * cos_sin_cache are not written by the kernel that precedes the call in the stream.  Returns the previous setting. */
+int dsv4_set_pdl(int enabled);
+
 /* Number of kernels this library has launched in this process (all entry points). */
 int64_t dsv4_launch_count(void);
 

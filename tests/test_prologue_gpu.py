@@ -505,3 +505,40 @@ def test_kernel_reproduces_the_upstream_flash_mla_cache_builder():
             assert torch.equal(cache.cpu(), want)
         finally:
             _native.set_variant(previous)
+
+
+def test_programmatic_dependent_launch_gives_the_same_result():
+    """With dsv4_set_pdl(1) the kernel may start before the kernel in front of it has finished and waits for it only
+    before touching q / kv / cache: a producer of q and kv directly in front of it, eager and replayed from a CUDA graph,
+    must give the bytes of the ordinary launch."""
+    q0, kv0, kc0, slots, pos, cs = random_case(300, 16, 64, 12, seed=77)
+    want_q, want_kv, want_kc = q0.clone(), kv0.clone(), kc0.clone()
+    op(want_q, want_kv, want_kc, slots, pos, cs, 1e-6, 64)
+    q_ref, kc_ref = oracle_of(q0, kv0, kc0, slots, pos, cs, 1e-6, 64)
+    assert torch.equal(want_kc.cpu(), kc_ref)
+    previous = _native.set_pdl(True)
+    try:
+        q, kv, kc = torch.empty_like(q0), torch.empty_like(kv0), kc0.clone()
+
+        def produce_then_consume():
+            q.copy_(q0)  # the producers of q and kv are the kernels right in front of the prologue
+            kv.copy_(kv0)
+            op(q, kv, kc, slots, pos, cs, 1e-6, 64)
+
+        produce_then_consume()
+        torch.cuda.synchronize()
+        assert torch.equal(q, want_q) and torch.equal(kc, want_kc)
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=s):
+                produce_then_consume()
+                produce_then_consume()
+            q.zero_(), kc.copy_(kc0)
+            graph.replay()
+        s.synchronize()
+        assert torch.equal(q, want_q) and torch.equal(kc, want_kc)
+    finally:
+        _native.set_pdl(previous)
+    assert _native.set_pdl(previous) == previous
