@@ -1,7 +1,8 @@
-"""Properties of the prologue's KV path that hold for any input, checked on the C oracle with generated cases (CPU):
-they pin down the cache format independently of any stored vector."""
+"""Properties of the prologue's KV path that hold for any input, checked on the C oracle with generated cases (CPU) and,
+on fixed cases, on the CUDA kernel: they pin down the cache format independently of any stored vector."""
 from __future__ import annotations
 
+import pytest
 import torch
 from hypothesis import given, settings
 from hypothesis import strategies as st
@@ -13,12 +14,22 @@ BS = 16
 TABLE = workloads.cos_sin_table(256)
 
 
+BACKEND = {"device": None}  # None: the C oracle; "cuda:0": the CUDA kernel through the Python entry point
+
+
 def run(kv, slots, positions, blocks=4, fill=0x5A):
     n = kv.shape[0]
     cache = torch.full((blocks, BS * 584), fill, dtype=torch.uint8)
     q = torch.ones(n, 1, 512, dtype=torch.bfloat16)
-    c_oracle.prologue(q, kv, cache, slots, positions, TABLE, 1e-6, BS)
-    return cache
+    dev = BACKEND["device"]
+    if dev is None:
+        c_oracle.prologue(q, kv, cache, slots, positions, TABLE, 1e-6, BS)
+        return cache
+    import flaggems_vllm
+
+    cache = cache.to(dev)
+    flaggems_vllm.fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert(q.to(dev), kv.to(dev), cache, slots.to(dev), positions.to(dev), TABLE.to(dev), 1e-6, BS)
+    return cache.cpu()
 
 
 def records(cache, slots):
@@ -117,3 +128,20 @@ def test_reader_inverts_the_quantiser_within_half_a_step(case):
             # e4m3 keeps 4 significant bits: the error is at most 1/16 of the value's power of two, in units of the scale; bf16 rounding of the product adds 2^-8
             bound = torch.maximum(x.abs() / 16.0, torch.tensor(step * 2.0**-10)) * 1.01 + x.abs() * 2.0**-8
             assert bool(((x - y).abs() <= bound).all())
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("n,seed", [(1, 1), (5, 2), (12, 3), (9, 4)])
+def test_the_same_properties_hold_for_the_cuda_kernel(n, seed):
+    BACKEND["device"] = "cuda:0"
+    try:
+        test_power_of_two_input_scaling_moves_only_the_scale_codes.hypothesis.inner_test((n, seed), 3)
+        test_power_of_two_input_scaling_moves_only_the_scale_codes.hypothesis.inner_test((n, seed), -5)
+        test_a_record_depends_only_on_its_token.hypothesis.inner_test((n, seed))
+        test_skipped_tokens_and_free_slots_keep_their_bytes.hypothesis.inner_test((n, seed), 0xA7)
+        kv, slots, positions = make(n, seed, spread=False)
+        on_device = run(kv, slots, positions)
+        BACKEND["device"] = None
+        assert torch.equal(on_device, run(kv, slots, positions))
+    finally:
+        BACKEND["device"] = None
