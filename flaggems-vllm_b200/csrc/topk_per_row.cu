@@ -34,7 +34,10 @@ namespace {
 
 namespace cg = cooperative_groups;
 
-constexpr int kTopkThreads = 512;
+#ifndef DSV4_TOPK_THREADS
+#define DSV4_TOPK_THREADS 512
+#endif
+constexpr int kTopkThreads = DSV4_TOPK_THREADS;
 constexpr int kBins = 2048;
 constexpr int kCandidateCap = 8192;  // 64 KiB of (key, position) pairs in dynamic shared memory
 constexpr int kSampleChunks = 128;  // x 32 values
