@@ -178,6 +178,32 @@ def test_persistent_topk_call_shape(lengths, k, two_d):
     assert bool((workspace == 0x5A).all())
 
 
+@pytest.mark.gpu
+def test_cluster_launch_replays_from_a_cuda_graph():
+    """Decode steps run from CUDA graphs: the cluster launch (4 rows of 65536 -> 4 CTAs per row) must be capturable and a
+    replay on new logits must select the new rows' values."""
+    g = torch.Generator().manual_seed(9)
+    logits = torch.randn(4, 65536, generator=g).to(DEV)
+    seq = torch.tensor([65536, 40000, 9000, 300], dtype=torch.int32, device=DEV)
+    idx = torch.zeros(4, 512, dtype=torch.int32, device=DEV)
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        flaggems_vllm.top_k_per_row_decode(logits, 1, seq, idx, 4, logits.stride(0), 1, 512)  # warm-up outside the capture
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=s):
+            flaggems_vllm.top_k_per_row_decode(logits, 1, seq, idx, 4, logits.stride(0), 1, 512)
+        fresh = torch.randn(4, 65536, generator=g)
+        logits.copy_(fresh)
+        idx.zero_()
+        graph.replay()
+    s.synchronize()
+    want = torch.zeros(4, 512, dtype=torch.int32)
+    c_oracle.top_k_per_row_decode(fresh, 1, seq.cpu(), want, 4, fresh.stride(0), 1, 512)
+    ends = decode_ends(seq.cpu(), 1, 4)
+    assert torch.equal(selected_values(fresh, idx, torch.zeros(4), ends, 512), selected_values(fresh, want, torch.zeros(4), ends, 512))
+
+
 def test_host_checks_without_gpu():
     logits, idx = torch.zeros(2, 100), torch.zeros(2, 8, dtype=torch.int32)
     with pytest.raises(AssertionError, match="no CPU path"):
