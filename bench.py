@@ -661,6 +661,21 @@ def main():
     if not args.no_e2e:
         e2e = measure_e2e(flaggems_vllm, w, args, dev, stream, sync_all, tokens)
 
+    # ---- the same total with EVEN shards (N > 1 only): what the uneven split of the headline costs
+    even = None
+    num_heads, cache_blocks = w.num_heads, int(w.k_cache.shape[0])
+    if distributed and not args.no_extra:
+        del w
+        torch.cuda.empty_cache()
+        w_even = workloads.make("long_prefill", device=dev, seed=rank)  # 32768 tokens x 128 heads on every rank
+        even_steps = min(args.steps, 50)
+        even_secs = time_steps(lambda: op(*w_even.args()), even_steps, max(args.warmup, 3), stream, sync_all)
+        even_agg = sharding.aggregate(even_secs, w_even.num_tokens, w_even.algorithmic_bytes(), even_steps, status=_native.device_error(), device=dev)
+        even = {"tokens_total": int(even_agg["tokens"]), "tokens_per_rank": w_even.num_tokens, "steps": even_steps,
+                "ms_per_step": even_agg["seconds"] / even_steps * 1e3, "value": float(even_agg["tokens"]) * even_steps / even_agg["seconds"],
+                "note": "same kernel and total token count, every rank 32768 tokens; the headline uses the uneven split BASELINE asks for"}
+        del w_even
+
     if rank != 0:
         if distributed:
             dist.destroy_process_group()
@@ -670,14 +685,14 @@ def main():
     # the kernel on the rank with the most bytes is the one the step waits for
     achieved = largest_bytes / (secs_max / args.steps) / 1e9
     traffic = None
-    if NCU_DRAM_BYTES_PER_TOKEN is not None and w.num_heads == 128:
+    if NCU_DRAM_BYTES_PER_TOKEN is not None and num_heads == 128:
         traffic = NCU_DRAM_BYTES_PER_TOKEN * largest_tokens
     line = {
         "metric": METRIC, "value": tokens * args.steps / secs_max, "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": secs_max / args.steps * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": name, "num_heads": w.num_heads, "tokens_total": int(tokens),
-                   "tokens_largest_shard": int(largest_tokens), "cache_blocks_per_gpu": int(w.k_cache.shape[0]),
+        "config": {"workload": name, "num_heads": num_heads, "tokens_total": int(tokens),
+                   "tokens_largest_shard": int(largest_tokens), "cache_blocks_per_gpu": cache_blocks,
                    "cache_block_size": 64, "parallelism": f"token-sharded x{world}, no collective",
                    "l2": "inputs (>= 1 GiB of q per GPU) exceed the 126 MB L2; no flush between steps",
                    "variant": _native.lib().dsv4_get_variant()},
@@ -688,7 +703,7 @@ def main():
                      "traffic": traffic, "peak_source": f"{peak_kind} copy bandwidth",
                      "algorithmic_bytes_per_launch": int(largest_bytes),
                      "kernel_ms": secs_max / args.steps * 1e3, "kernel_ms_per_launch_rank0": launch_stats},
-        "clocks": clocks, "gpu_launches": launches_total, "e2e": e2e,
+        "clocks": clocks, "gpu_launches": launches_total, "e2e": e2e, "even_shards": even,
         "host_numa_binding": (f"rank 0 bound to {len(numa_cores)} cores next to its GPU" if numa_cores else None),
     }
     if not args.no_cpu_baseline and world == 1:
