@@ -301,7 +301,7 @@ int dsv4_top_k_per_row_decode(const float* logits, int64_t stride0, int64_t stri
     if (next_n <= 0 || next_n >= (1LL << 31)) return DSV4_ERR_BAD_SIZE;
     if (num_rows == 0 || top_k == 0) return DSV4_OK;
     if (!seq_lens) return DSV4_ERR_NULL_POINTER;
-    return static_cast<int>(launch_topk_per_row(logits, stride0, stride1, indices, num_rows, static_cast<int>(vocab),
+    return static_cast<int>((vocab <= 8192 ? launch_topk_per_row_short : launch_topk_per_row)(logits, stride0, stride1, indices, num_rows, static_cast<int>(vocab),
                                                 static_cast<int>(top_k), seq_lens, static_cast<int>(next_n), nullptr, nullptr,
                                                 static_cast<cudaStream_t>(cuda_stream)));
 }
@@ -313,7 +313,7 @@ int dsv4_top_k_per_row_prefill(const float* logits, int64_t stride0, int64_t str
     if (rc != DSV4_OK) return rc;
     if (num_rows == 0 || top_k == 0) return DSV4_OK;
     if (!row_ends) return DSV4_ERR_NULL_POINTER;
-    return static_cast<int>(launch_topk_per_row(logits, stride0, stride1, indices, num_rows, static_cast<int>(vocab),
+    return static_cast<int>((vocab <= 8192 ? launch_topk_per_row_short : launch_topk_per_row)(logits, stride0, stride1, indices, num_rows, static_cast<int>(vocab),
                                                 static_cast<int>(top_k), nullptr, 1, row_starts, row_ends,
                                                 static_cast<cudaStream_t>(cuda_stream)));
 }

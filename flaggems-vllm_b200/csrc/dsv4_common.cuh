@@ -451,6 +451,9 @@ cudaError_t launch_combine_topk_swa(const int32_t* topk_indices, int64_t topk_st
 cudaError_t launch_topk_per_row(const float* logits, int64_t stride0, int64_t stride1, int32_t* indices, int64_t num_rows, int vocab,
                                 int top_k, const int32_t* seq_lens, int next_n, const int32_t* row_starts, const int32_t* row_ends,
                                 cudaStream_t stream);
+cudaError_t launch_topk_per_row_short(const float* logits, int64_t stride0, int64_t stride1, int32_t* indices, int64_t num_rows, int vocab,
+                                int top_k, const int32_t* seq_lens, int next_n, const int32_t* row_starts, const int32_t* row_ends,
+                                cudaStream_t stream);  // 256 threads per CTA: rows up to 8192 wide
 cudaError_t launch_group_quant_fp8(const void* x, int64_t x_stride, void* out, float* scales, int64_t scale_stride_row,
                                    int64_t scale_stride_group, int64_t num_rows, int64_t num_cols, int group_size, float eps, int ue8m0,
                                    int act_quant_rules, cudaStream_t stream);

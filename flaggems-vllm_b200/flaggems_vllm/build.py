@@ -15,7 +15,7 @@ PKG = Path(__file__).resolve().parent
 CSRC = PKG.parent / "csrc"
 OUT = PKG / "libdsv4_prologue.so"
 SOURCES = ("abi.cu", "prologue_rows.cu", "prologue_bulk.cu", "gather_dequant.cu", "hbm_probe.cu", "q_kv_rmsnorm.cu", "inv_rope_fp8_quant.cu", "indexer_k_quant.cu",
-           "indexer_q_rope_quant.cu", "cp_gather_indexer.cu", "topk_indices.cu", "topk_per_row.cu", "group_quant_fp8.cu")
+           "indexer_q_rope_quant.cu", "cp_gather_indexer.cu", "topk_indices.cu", "topk_per_row.cu", "topk_per_row_short.cu", "group_quant_fp8.cu")
 HEADERS = ("dsv4_common.cuh", "../../include/dsv4_prologue.h")
 
 
