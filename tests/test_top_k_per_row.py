@@ -179,6 +179,33 @@ def test_persistent_topk_call_shape(lengths, k, two_d):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("layout", ["odd_offset", "odd_row_stride", "transposed"])
+def test_rows_that_are_not_16_byte_aligned_or_not_contiguous(layout):
+    """The streaming loop uses 16-byte loads from the first aligned element on and single loads around them; logits with
+    a unit column stride but odd offsets or row strides, and logits with a non-unit column stride, take the other paths."""
+    g = torch.Generator().manual_seed(21)
+    rows, width, top_k = 5, 40000, 256
+    if layout == "odd_offset":
+        base = torch.randn(rows, width + 16, generator=g)
+        view = lambda t: t[:, 3 : 3 + width]
+    elif layout == "odd_row_stride":
+        base = torch.randn(rows, width + 1, generator=g)
+        view = lambda t: t[:, :width]
+    else:
+        base = torch.randn(width, rows, generator=g)
+        view = lambda t: t.t()
+    logits = view(base)
+    starts = torch.tensor([0, 1, 2, 3, 17], dtype=torch.int32)
+    ends = torch.tensor([width, width - 1, 30001, 9000, 18], dtype=torch.int32)
+    want = torch.zeros(rows, top_k, dtype=torch.int32)
+    c_oracle.top_k_per_row_prefill(logits, starts, ends, want, rows, logits.stride(0), logits.stride(1), top_k)
+    dev = view(base.to(DEV))
+    got = torch.full((rows, top_k), 7, dtype=torch.int32, device=DEV)
+    flaggems_vllm.top_k_per_row_prefill(dev, starts.to(DEV), ends.to(DEV), got, rows, dev.stride(0), dev.stride(1), top_k)
+    assert torch.equal(selected_values(logits, got, starts, ends, top_k), selected_values(logits, want, starts, ends, top_k))
+
+
+@pytest.mark.gpu
 def test_cluster_launch_replays_from_a_cuda_graph():
     """Decode steps run from CUDA graphs: the cluster launch (4 rows of 65536 -> 4 CTAs per row) must be capturable and a
     replay on new logits must select the new rows' values."""
