@@ -172,10 +172,32 @@ def per_launch_times(fn, launches: int, stream, sync_all):
     return {"launches": launches, "median_ms": ms[len(ms) // 2], "best_ms": ms[0], "worst_ms": ms[-1]}
 
 
+def reference_cpu_path():
+    """The reference's CPU implementation of the operator as (function, kind, description).  kind "reference": the
+    upstream project's own torch function `ref_impl`, loaded from its unmodified test file (from an upstream checkout,
+    or from the digest-checked copy that oracle/make_ref.py places under oracle/_ref/).  kind "port": the restatement
+    in oracle/torch_path.py, used only where neither is present.  `ref_impl` rotates the kv tensor it is given, so the
+    wrapper hands it a copy (the operator leaves kv untouched)."""
+    from oracle import ref_loader, torch_path
+
+    found = ref_loader.hot_path_test_root()
+    if found is not None:
+        try:
+            upstream = ref_loader.load_upstream_test_module()
+
+            def ref(q, kv, cache, slots, pos, cs, eps, bs):
+                upstream.ref_impl(q, kv.clone(), cache, slots, pos, cs, eps, bs)
+
+            return ref, "reference", f"upstream ref_impl (torch CPU path of the reference's own test file, {found[1]})"
+        except Exception as e:  # an unreadable copy must not silently become the reference
+            print(f"# upstream ref_impl could not be loaded ({e!r}); timing the restatement instead", file=sys.stderr)
+    return torch_path.prologue, "port", "restatement of the reference's torch CPU path (oracle/torch_path.py)"
+
+
 def cpu_baseline(workload, budget_s: float = 12.0):
-    """The CPU torch statement of the reference path (oracle/torch_path.py) on the first
-    CPU_SAMPLE_TOKENS tokens of the workload, all host threads; best of >= 5 runs within a budget."""
-    from oracle import torch_path
+    """The reference's CPU torch path (see reference_cpu_path) on the first CPU_SAMPLE_TOKENS tokens of the workload,
+    all host threads; best of >= 5 runs within a budget."""
+    cpu_path, kind, what = reference_cpu_path()
 
     n = min(CPU_SAMPLE_TOKENS, workload.num_tokens)
     n_ins = min(n, workload.slot_mapping.shape[0])
@@ -194,11 +216,11 @@ def cpu_baseline(workload, budget_s: float = 12.0):
     while runs < 5 or (time.perf_counter() - t_start < budget_s and runs < 50):
         qq = q.clone()
         t = time.perf_counter()
-        torch_path.prologue(qq, kv, cache, compact, pos, cs, workload.eps, 64)
+        cpu_path(qq, kv, cache, compact, pos, cs, workload.eps, 64)
         best = min(best, time.perf_counter() - t)
         runs += 1
-    out = {"value": n / best, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
-           "sample": f"first {n} tokens x {workload.num_heads} heads of the workload, torch CPU path, best of {runs} runs",
+    out = {"value": n / best, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": kind,
+           "sample": f"first {n} tokens x {workload.num_heads} heads of the workload, {what}, best of {runs} runs",
            "ms_per_sample": best * 1e3}
     # for scale: the plain-C oracle (OpenMP over tokens) on the same sample
     from oracle import c_oracle
@@ -214,12 +236,12 @@ def cpu_baseline(workload, budget_s: float = 12.0):
 
 
 def run_reference(args, rank, world):
-    """--impl reference: the reference's CPU torch path (restated in oracle/torch_path.py; the
-    upstream tree does not travel to the GPU box) on a bounded sample per step."""
+    """--impl reference: the reference's CPU torch path (see reference_cpu_path) on a bounded sample per step."""
     if rank != 0:
         return
     from flaggems_vllm.testing import workloads
-    from oracle import torch_path
+
+    cpu_path, kind, what = reference_cpu_path()
 
     name = args.workload or ("long_prefill" if world == 1 else "sharded")
     n = CPU_SAMPLE_TOKENS
@@ -233,20 +255,20 @@ def run_reference(args, rank, world):
     def step():
         q = q0.clone()
         t = time.perf_counter()
-        torch_path.prologue(q, w.kv, w.k_cache, w.slot_mapping, w.position_ids, w.cos_sin_cache, w.eps, 64)
+        cpu_path(q, w.kv, w.k_cache, w.slot_mapping, w.position_ids, w.cos_sin_cache, w.eps, 64)
         return time.perf_counter() - t
 
     for _ in range(args.warmup):
         step()
     total = sum(step() for _ in range(args.steps))
     value = n * args.steps / total
-    sample = f"{n} tokens x {w.num_heads} heads per step (bounded sample of the workload), torch CPU path"
+    sample = f"{n} tokens x {w.num_heads} heads per step (bounded sample of the workload), {what}"
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": total / args.steps * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": name, "num_heads": w.num_heads, "sample_tokens": n},
-        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port", "sample": sample},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": kind, "sample": sample},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }), flush=True)

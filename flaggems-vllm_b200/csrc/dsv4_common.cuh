@@ -93,7 +93,24 @@ inline void make_fast_divisor(uint32_t d, uint32_t* mul, uint32_t* shift) {
 
 // ---- memory access ---------------------------------------------------------
 
-// Streaming 16-byte load: data is touched once, keep it out of L1.
+// Streaming loads of memory the SAME kernel also writes (q is normalised in place): the ordinary, coherent global
+// path, kept out of L1.  The non-coherent path below promises that the data stays read-only while the kernel runs.
+__device__ __forceinline__ uint4 ld_inplace16(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ uint32_t ld_inplace4(const void* p) {
+    uint32_t v;
+    asm volatile("ld.global.L1::no_allocate.u32 %0, [%1];" : "=r"(v) : "l"(p));
+    return v;
+}
+
+// Streaming 16-byte load of read-only data (never written by the kernel that loads it): touched once, non-coherent
+// path, kept out of L1.
 __device__ __forceinline__ uint4 ld_stream16(const void* p) {
     uint4 v;
     asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"

@@ -25,8 +25,9 @@ __global__ void __launch_bounds__(kProbeWarps * 32) hbm_probe_kernel(uint8_t* bu
         a[i] = b[i] = make_uint4(row0, lane, i, 0u);
         if (MODE != 2 && row0 + i < rows) {
             const uint8_t* row = buf + static_cast<uint64_t>(row0 + i) * kRowBytes;
-            a[i] = ld_stream16(row + 16 * lane);
-            b[i] = ld_stream16(row + 512 + 16 * lane);
+            // mode 0 rewrites what it reads, so it must not use the non-coherent (read-only) path
+            a[i] = MODE == 0 ? ld_inplace16(row + 16 * lane) : ld_stream16(row + 16 * lane);
+            b[i] = MODE == 0 ? ld_inplace16(row + 512 + 16 * lane) : ld_stream16(row + 512 + 16 * lane);
         }
     }
 #pragma unroll

@@ -98,9 +98,9 @@ __global__ void __launch_bounds__(WARPS * 32, MIN_CTAS) prologue_rows_kernel(con
             tail[i] = 0u;
             if (row0 + i < total_rows) {
                 const uint8_t* row = p.q + static_cast<uint64_t>(row0 + i) * kRowBytes;
-                a[i] = ld_stream16(row + 16 * lane);
-                if (lane < kFirstRopeLane) b[i] = ld_stream16(row + 512 + 16 * lane);
-                tail[i] = ld_stream4(row + 2 * kNopeDim + 4 * lane);
+                a[i] = ld_inplace16(row + 16 * lane);
+                if (lane < kFirstRopeLane) b[i] = ld_inplace16(row + 512 + 16 * lane);
+                tail[i] = ld_inplace4(row + 2 * kNopeDim + 4 * lane);
             }
         }
     };

@@ -1,8 +1,10 @@
 """Loads the upstream test file and hands out its own torch reference functions.
 
-TEST INFRASTRUCTURE ONLY, and usable only where the upstream source tree is
-present: it is how the golden vectors under tests/golden/ were produced and how
-the restatements in this folder are checked against the real thing.  The upstream
+TEST INFRASTRUCTURE ONLY, and usable only where the upstream source tree, or the
+verified copy of its test files that oracle/make_ref.py places under oracle/_ref/,
+is present: it is how the golden vectors under tests/golden/ were produced, how
+the restatements in this folder are checked against the real thing, and how the
+CPU baseline of bench.py reaches the upstream `ref_impl`.  The upstream
 package itself cannot be imported without a GPU and its SQL dependency, so the
 test module is executed with small stand-in modules for the names it imports;
 its pure-torch reference functions (`ref_impl` and helpers) need nothing else.
@@ -10,26 +12,38 @@ its pure-torch reference functions (`ref_impl` and helpers) need nothing else.
 from __future__ import annotations
 
 import importlib.util
-import os
 import sys
 import types
 from pathlib import Path
 
-UPSTREAM_ENV = "DSV4_UPSTREAM_ROOT"  # where the upstream source tree is checked out
-DEFAULT_ROOT = os.path.join(os.path.sep, "root", "reference")
-OP = "fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert"
+from . import make_ref
+
+UPSTREAM_ENV = make_ref.UPSTREAM_ENV  # names the directory of an upstream checkout
+OP = make_ref.OP
 
 
 def upstream_root() -> Path | None:
-    root = Path(os.environ.get(UPSTREAM_ENV, DEFAULT_ROOT))
-    return root if (root / "tests" / f"test_{OP}.py").exists() else None
+    """An upstream checkout ($DSV4_UPSTREAM_ROOT, else a folder `reference` beside this repository), or None."""
+    return make_ref.find_upstream()
+
+
+def hot_path_test_root() -> tuple[Path, str] | None:
+    """Where the upstream test file of the hot path can be read: (root, kind).  kind "checkout" = an upstream
+    checkout; "copy" = the verified byte-for-byte copy oracle/make_ref.py placed under oracle/_ref/."""
+    root = upstream_root()
+    if root is not None:
+        return root, "checkout"
+    if make_ref.present():
+        return make_ref.OUT, "copy"
+    return None
 
 
 def load_upstream_test_module():
     """The upstream test module object (has ref_impl, make_cos_sin_cache, k_cache_compare...)."""
-    root = upstream_root()
-    if root is None:
-        raise FileNotFoundError("upstream tree not present")
+    found = hot_path_test_root()
+    if found is None:
+        raise FileNotFoundError("neither an upstream checkout nor oracle/_ref is present")
+    root = found[0]
     saved = {k: sys.modules.get(k) for k in list(sys.modules) if k == "flaggems_vllm" or k.startswith("flaggems_vllm.")}
     for k in saved:
         del sys.modules[k]
