@@ -278,12 +278,14 @@ def hbm_ceiling(native, nbytes: int, stream):
     """This GPU's streaming rates for the prologue's access pattern without arithmetic
     (dsv4_hbm_probe): in place (1 read : 1 write, the operator's mix), read-only, write-only, and 2 read : 1 write
     (the mix of the narrowing sibling operators)."""
+    from flaggems_vllm.testing import hbm_probe
+
     rows = max(1, nbytes // 1024)
     buf = torch.empty(rows * 1536, dtype=torch.uint8, device="cuda")
-    lib, out = native.lib(), {}
+    out = {}
     for mode, name, traffic in ((0, "inplace_gbs", 2), (1, "read_gbs", 1), (2, "write_gbs", 1), (3, "read2_write1_gbs", 1.5)):
         def fn():
-            native.check(lib.dsv4_hbm_probe(mode, buf.data_ptr(), rows, stream.cuda_stream))
+            hbm_probe.probe(mode, buf.data_ptr(), rows, stream.cuda_stream)
         secs = time_steps(fn, 10, 3, stream, torch.cuda.synchronize)
         out[name] = traffic * rows * 1024 * 10 / secs / 1e9
     out["buffer_bytes"] = rows * 1024
@@ -466,16 +468,62 @@ def measure_e2e(flaggems_vllm, w, args, dev, stream, sync_all, tokens_all_ranks)
     secs = t0.elapsed_time(t1) * 1e-3 / e2e_steps
     h2d = hq.numel() * 2 + hkv.numel() * 2 + hslots.numel() * 8 + hpos.numel() * 8
     d2h = hq.numel() * 2
+    my_secs, my_h2d, my_d2h = secs, h2d, d2h
     es = torch.tensor([secs, float(h2d), float(d2h)], dtype=torch.float64, device=dev)
-    if distributed and dist.get_world_size() > 1:
+    world = dist.get_world_size() if distributed else 1
+    if world > 1:
         em, esum = es.clone(), es.clone()
         dist.all_reduce(em, op=dist.ReduceOp.MAX)
         dist.all_reduce(esum, op=dist.ReduceOp.SUM)
         secs, h2d, d2h = float(em[0]), float(esum[1]), float(esum[2])
-    return {"value": tokens_all_ranks / secs, "unit": "tokens/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
-            "ms_per_step": secs * 1e3, "chunk_tokens": 1024, "launches_per_step": pipe.launches,
-            "note": "q/kv/slots/positions from pinned host memory, rewritten q back to the same pinned buffer; "
-                    "K cache and cos/sin table device-resident"}
+    out = {"value": tokens_all_ranks / secs, "unit": "tokens/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
+           "ms_per_step": secs * 1e3, "chunk_tokens": 1024, "launches_per_step": pipe.launches,
+           "note": "q/kv/slots/positions from pinned host memory, rewritten q back to the same pinned buffer; "
+                   "K cache and cos/sin table device-resident"}
+    if world > 1:
+        # What the host side of this box can move with no kernel and no pipeline at all: every rank copies half of its
+        # pinned q to the device while the other half comes back (then the halves swap), all ranks at once.  Beside
+        # it, what the staged pipeline moved per rank in the timed region above.  Equal figures mean the box's host
+        # memory / PCIe fabric is the limit of `e2e`, not the pipeline.
+        bare = bare_copy_rates(hq, w.q, dev, sync_all)
+        mine = torch.tensor([my_h2d / my_secs / 1e9, my_d2h / my_secs / 1e9, bare[0], bare[1], float(w.num_tokens)],
+                            dtype=torch.float64, device=dev)
+        every = [torch.zeros_like(mine) for _ in range(world)]
+        dist.all_gather(every, mine)
+        rows = [[round(float(v), 2) for v in t.tolist()] for t in every]
+        out["staged_gbs_per_rank"] = [[r[0], r[1]] for r in rows]
+        out["bare_copy_gbs_per_rank"] = [[r[2], r[3]] for r in rows]
+        out["tokens_per_rank"] = [int(r[4]) for r in rows]
+        out["bare_copy_gbs_all_ranks"] = [round(sum(r[2] for r in rows), 1), round(sum(r[3] for r in rows), 1)]
+        out["staged_gbs_all_ranks"] = [round(h2d / secs / 1e9, 1), round(d2h / secs / 1e9, 1)]
+        out["bare_copy_note"] = ("[host->device, device->host] GB/s; bare = plain cudaMemcpyAsync of pinned q in both directions at "
+                                 "once on every rank at once, no kernel, measured after the timed region")
+    return out
+
+
+def bare_copy_rates(hq, dq, dev, sync_all, passes: int = 2):
+    """(host->device GB/s, device->host GB/s) of this rank while all ranks copy at once: one half of the pinned
+    buffer goes to the device while the other half comes back, then the halves swap; each direction on its own
+    stream between its own events.  `dq` is a device buffer of the same shape whose contents are no longer needed."""
+    half = hq.shape[0] // 2
+    if half == 0:
+        return 0.0, 0.0
+    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(2)] for _ in range(2)]
+    sync_all()
+    ev[0][0].record(s_in), ev[1][0].record(s_out)
+    for k in range(passes):
+        up, down = (slice(0, half), slice(half, 2 * half)) if k % 2 == 0 else (slice(half, 2 * half), slice(0, half))
+        with torch.cuda.stream(s_in):
+            dq[up].copy_(hq[up], non_blocking=True)
+        with torch.cuda.stream(s_out):
+            hq[down].copy_(dq[down], non_blocking=True)
+        # the halves swap only when both copies of this pass are done
+        s_in.wait_stream(s_out), s_out.wait_stream(s_in)
+    ev[0][1].record(s_in), ev[1][1].record(s_out)
+    sync_all()
+    nbytes = passes * half * hq[0].numel() * hq.element_size()
+    return nbytes / (ev[0][0].elapsed_time(ev[0][1]) * 1e-3) / 1e9, nbytes / (ev[1][0].elapsed_time(ev[1][1]) * 1e-3) / 1e9
 
 
 def library_kernel_time(w, steps, warmup, stream):
@@ -607,8 +655,29 @@ def side_measurement(name, steps, warmup, op, native):
             stream.wait_stream(side)
             psecs = time_steps(graph_pdl.replay, replays, 2, stream, torch.cuda.synchronize)
             out["us_per_launch_cuda_graph_pdl"] = psecs / (replays * sets) * 1e6
+            # and through the Python entry point, launch by launch
+            esecs = time_steps(fn, steps, warmup, stream, torch.cuda.synchronize)
+            out["us_per_launch_pdl"] = esecs / steps * 1e6
         finally:
             native.set_pdl(previous)
+        # The ceiling for a launch of THIS size: the arithmetic-free in-place copy with the same row access pattern
+        # over the same number of q rows, rotating over as many buffers, replayed from a CUDA graph the same way.
+        # A launch this short is bounded by launch, ramp-up and drain as much as by bandwidth; the probe pays the same.
+        from flaggems_vllm.testing import hbm_probe
+
+        rows = w.num_tokens * w.num_heads
+        with torch.cuda.stream(side):
+            side.wait_stream(stream)
+            for q in q_sets[:2]:
+                hbm_probe.probe(0, q.data_ptr(), rows, side.cuda_stream)
+            graph_probe = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph_probe, stream=side):
+                for q in q_sets:
+                    hbm_probe.probe(0, q.data_ptr(), rows, torch.cuda.current_stream().cuda_stream)
+        stream.wait_stream(side)
+        csecs = time_steps(graph_probe.replay, replays, 2, stream, torch.cuda.synchronize)
+        out["copy_probe_us_per_launch_cuda_graph"] = csecs / (replays * sets) * 1e6
+        out["frac_of_copy_probe_same_size"] = out["copy_probe_us_per_launch_cuda_graph"] / out["us_per_launch_cuda_graph"]
     return out
 
 
@@ -696,6 +765,10 @@ def main():
         even = {"tokens_total": int(even_agg["tokens"]), "tokens_per_rank": w_even.num_tokens, "steps": even_steps,
                 "ms_per_step": even_agg["seconds"] / even_steps * 1e3, "value": float(even_agg["tokens"]) * even_steps / even_agg["seconds"],
                 "note": "same kernel and total token count, every rank 32768 tokens; the headline uses the uneven split BASELINE asks for"}
+        if not args.no_e2e:
+            even_e2e = measure_e2e(flaggems_vllm, w_even, args, dev, stream, sync_all, float(even_agg["tokens"]))
+            even["e2e"] = {k: even_e2e.get(k) for k in ("value", "unit", "ms_per_step", "h2d_bytes_per_step", "d2h_bytes_per_step",
+                                                         "staged_gbs_all_ranks", "bare_copy_gbs_all_ranks", "unavailable") if k in even_e2e}
         del w_even
 
     if rank != 0:

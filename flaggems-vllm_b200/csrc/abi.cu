@@ -35,6 +35,26 @@ int current_pdl() {
     return v;
 }
 
+// Where the rows variant takes the cos|sin rows from: -1 = by launch size (per-warp fetch up to kPerWarpTableRows rows
+// of q, shared-memory staging above), 0 = always per warp, 1 = always staged.
+std::atomic<int> g_table_staging{-2};  // -2: not initialised from the environment yet
+constexpr int64_t kPerWarpTableRows = 65536;
+
+int current_table_staging() {
+    int v = g_table_staging.load(std::memory_order_relaxed);
+    if (v < -1) {
+        const char* e = std::getenv("DSV4_TABLE_STAGING");
+        v = e ? std::atoi(e) : -1;
+        if (v < -1 || v > 1) v = -1;
+        g_table_staging.store(v, std::memory_order_relaxed);
+    }
+    return v;
+}
+
+// Bulk variant: SM cycles a wait on a shared-memory barrier may take before the kernel gives up.  A tile load is a few
+// microseconds; 2e8 cycles are about a tenth of a second at B200 clocks.
+std::atomic<long long> g_bulk_wait_cycles{200000000LL};
+
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 int validate(const void* q, const void* kv, const void* k_cache, const int64_t* slot_mapping,
@@ -77,6 +97,10 @@ PrologueParams make_params(void* q, const void* kv, void* k_cache, const int64_t
     p.cache_aligned16 = aligned16(k_cache) && (kv_block_stride_bytes % 16 == 0);
     make_fast_divisor(static_cast<uint32_t>(num_heads > 0 ? num_heads : 1), &p.heads_mul, &p.heads_shift);
     p.pdl = current_pdl();
+    p.wait_cycles = g_bulk_wait_cycles.load(std::memory_order_relaxed);
+    p.short_tile = 0xffffffffu;
+    const int staging = current_table_staging();
+    p.table_staging = staging < 0 ? (num_tokens * num_heads > kPerWarpTableRows ? 1 : 0) : staging;
     return p;
 }
 }  // namespace
@@ -376,16 +400,6 @@ int dsv4_fused_indexer_q_rope_quant(const int64_t* positions, const void* index_
         static_cast<int>(head_dim), use_fp4 ? 1 : 0, static_cast<cudaStream_t>(cuda_stream)));
 }
 
-int dsv4_hbm_probe(int mode, void* buffer, int64_t rows, void* cuda_stream) {
-    if (mode < 0 || mode > 3) return DSV4_ERR_BAD_VARIANT;
-    if (rows < 0 || rows >= (1LL << 31)) return DSV4_ERR_BAD_SIZE;
-    if (rows == 0) return DSV4_OK;
-    if (!buffer) return DSV4_ERR_NULL_POINTER;
-    if (!aligned16(buffer)) return DSV4_ERR_MISALIGNED;
-    return static_cast<int>(launch_hbm_probe(mode, static_cast<uint8_t*>(buffer), rows, nullptr,
-                                             static_cast<cudaStream_t>(cuda_stream)));
-}
-
 int dsv4_device_error(int32_t* value_host) {
     if (!value_host) return DSV4_ERR_NULL_POINTER;
     int v = 0;
@@ -406,6 +420,32 @@ int dsv4_get_variant(void) { return current_variant(); }
 int dsv4_set_pdl(int enabled) {
     const int previous = current_pdl();
     g_pdl.store(enabled ? 1 : 0, std::memory_order_relaxed);
+    return previous;
+}
+
+int64_t dsv4_set_bulk_wait_cycles(int64_t cycles) {
+    const long long previous = g_bulk_wait_cycles.load(std::memory_order_relaxed);
+    if (cycles > 0) g_bulk_wait_cycles.store(cycles > 2000000000LL ? 2000000000LL : cycles, std::memory_order_relaxed);
+    return previous;
+}
+
+int dsv4_bulk_wait_selftest(void* q, const void* kv, void* k_cache, const int64_t* slot_mapping, const int64_t* position_ids,
+                            const float* cos_sin_cache, float eps, int64_t num_tokens, int64_t num_heads,
+                            int64_t num_tokens_insert, int64_t cache_block_size, int64_t kv_block_stride_bytes,
+                            int64_t short_tile, void* cuda_stream) {
+    const int rc = validate(q, kv, k_cache, slot_mapping, position_ids, cos_sin_cache, num_tokens, num_heads,
+                            num_tokens_insert, cache_block_size, kv_block_stride_bytes);
+    if (rc != DSV4_OK || num_tokens == 0) return rc;
+    if (short_tile < 0 || short_tile >= 0xffffffffLL) return DSV4_ERR_BAD_SIZE;
+    PrologueParams p = make_params(q, kv, k_cache, slot_mapping, position_ids, cos_sin_cache, eps, num_tokens, num_heads,
+                                   num_tokens_insert, cache_block_size, kv_block_stride_bytes);
+    p.short_tile = static_cast<uint32_t>(short_tile);
+    return static_cast<int>(launch_prologue_bulk(p, static_cast<cudaStream_t>(cuda_stream)));
+}
+
+int dsv4_set_table_staging(int mode) {
+    const int previous = current_table_staging();
+    g_table_staging.store(mode < -1 || mode > 1 ? -1 : mode, std::memory_order_relaxed);
     return previous;
 }
 

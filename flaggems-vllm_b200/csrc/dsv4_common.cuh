@@ -56,6 +56,14 @@ struct PrologueParams {
     // programmatic dependent launch: read position_ids / slot_mapping / cos_sin before the preceding kernel of the
     // stream has finished, wait for it only before touching q and kv (rows variant; 0 = ordinary launch)
     int pdl;
+    // rows variant: 1 = the cos|sin rows of a tile go through shared memory (one fetch per CTA), 0 = every warp
+    // fetches the table row of its own rows into registers (no barrier; chosen for launches of a few waves)
+    int table_staging;
+    // bulk variant: SM cycles after which a wait on a shared-memory barrier gives up (the kernel then sets the
+    // device error word and returns), and a self-test hook: the tile whose loader announces bytes it never sends
+    // (0xffffffff = none)
+    long long wait_cycles;
+    uint32_t short_tile;
 };
 
 // floor(n / d) for n < 2^31 via the multiplier the host derived with make_fast_divisor().
@@ -332,28 +340,52 @@ __device__ __forceinline__ uint32_t pow2_ceil_code(float s) {
 // How x / scale is formed for a scale that is not a power of two.
 enum : int { kDivideIeee = 0, kDivideFast = 1, kMultiplyReciprocal = 2 };
 
-// kDivideFast: y = RN(1/scale) once, then per value q0 = x*y, r = fma(-scale, q0, x), q = fma(r, y, q0) - three
-// instructions instead of an IEEE division.  q can differ from RN(x/scale) in the last fp32 bit, but never in the
-// e4m3 byte: a CPU test enumerates every bf16 group maximum (hence every reachable scale, for the reference's
-// eps = 1e-10) against every bf16 value below it - 5.3e8 pairs, zero differing bytes.  For any other eps the
-// kernels divide.  kMultiplyReciprocal: x * RN(1/scale), which is what the statement of `act_quant` computes.
+// kDivideFast: once per group y = RN(1/scale) and its residual y_lo = RN(fma(-scale, y, 1) * y), so that y + y_lo is
+// 1/scale to about 2^-48; then per value q = fma(x, y, RN(x * y_lo)) - two instructions instead of an IEEE division.
+// q can differ from RN(x/scale) in the last fp32 bit, but never in the e4m3 byte: a CPU test enumerates every bf16
+// group maximum (hence every reachable scale, for the reference's eps = 1e-10) against every bf16 value below it -
+// 5.3e8 pairs, zero differing bytes.  Scales outside [2^-100, 2^100] (where y_lo would be subnormal) are divided.
+// For any other eps the kernels divide.  kMultiplyReciprocal: x * RN(1/scale), what the statement of `act_quant` computes.
+constexpr float kFastDivideMinScale = 0x1p-100f, kFastDivideMaxScale = 0x1p100f;
+
 template <int MODE>
-__device__ __forceinline__ float div_by_scale(float x, float scale, float recip) {
-    if (MODE == kDivideIeee) return __fdiv_rn(x, scale);
-    const float q0 = __fmul_rn(x, recip);
-    if (MODE == kMultiplyReciprocal) return q0;
-    return fmaf(fmaf(-scale, q0, x), recip, q0);
+struct ScaleDivider {
+    float scale, recip, recip_lo;
+    bool fast;
+    __device__ __forceinline__ explicit ScaleDivider(float s) : scale(s), recip(0.0f), recip_lo(0.0f), fast(false) {
+        if (MODE != kDivideIeee) recip = __frcp_rn(s);
+        if (MODE == kDivideFast) {
+            recip_lo = __fmul_rn(__fmaf_rn(-s, recip, 1.0f), recip);
+            fast = s >= kFastDivideMinScale && s <= kFastDivideMaxScale;
+        }
+    }
+    // quotient of one value; callers with many values test `fast` once and use the two forms below directly
+    __device__ __forceinline__ float operator()(float x) const {
+        if (MODE == kMultiplyReciprocal) return __fmul_rn(x, recip);
+        if (MODE == kDivideFast && fast) return quick(x);
+        return __fdiv_rn(x, scale);
+    }
+    __device__ __forceinline__ float quick(float x) const { return __fmaf_rn(x, recip, __fmul_rn(x, recip_lo)); }
+};
+
+template <int MODE>
+__device__ __forceinline__ uint2 quant8_by(const uint4& v, const ScaleDivider<MODE>& d) {
+    float x[8];
+    unpack8(v, x);
+    float q[8];  // the e4m3 conversion saturates at +-448
+    if (MODE == kDivideFast && d.fast) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) q[i] = d.quick(x[i]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) q[i] = MODE == kMultiplyReciprocal ? __fmul_rn(x[i], d.recip) : __fdiv_rn(x[i], d.scale);
+    }
+    return make_uint2(pack_e4m3x4(q[0], q[1], q[2], q[3]), pack_e4m3x4(q[4], q[5], q[6], q[7]));
 }
 
 template <int MODE>
 __device__ __forceinline__ uint2 quant8_by(const uint4& v, float scale) {
-    float x[8];
-    unpack8(v, x);
-    const float recip = MODE != kDivideIeee ? __frcp_rn(scale) : 0.0f;
-    float q[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) q[i] = div_by_scale<MODE>(x[i], scale, recip);  // the e4m3 conversion saturates at +-448
-    return make_uint2(pack_e4m3x4(q[0], q[1], q[2], q[3]), pack_e4m3x4(q[4], q[5], q[6], q[7]));
+    return quant8_by<MODE>(v, ScaleDivider<MODE>(scale));
 }
 
 // 8 bf16 values times the exact reciprocal of a power-of-two scale (same result as dividing by it).  The products are
@@ -484,7 +516,6 @@ cudaError_t launch_indexer_q_rope_quant(const int64_t* positions, const void* q,
                                         int64_t scale_stride1, const void* weights, int64_t weights_stride, int weights_dtype,
                                         float* weights_out, int64_t weights_out_stride, float softmax_scale, float head_scale,
                                         int64_t num_tokens, int num_heads, int head_dim, int fp4, cudaStream_t stream);
-cudaError_t launch_hbm_probe(int mode, uint8_t* buf, int64_t rows, uint32_t* sink, cudaStream_t stream);
 void count_launch();
 cudaError_t read_device_error(int* value);
 

@@ -73,9 +73,10 @@ __global__ void __launch_bounds__(WARPS * 32) group_quant_fp8_kernel(const Group
         }
         if (g >= p.num_groups) continue;
         uint8_t* dst = p.out + g * p.group_size;
+        const ScaleDivider<DIVISION> by_scale(scale);
 #pragma unroll
         for (int c = 0; c < CHUNKS; ++c)
-            st_global8(dst + 8 * (sub + c * LANES), UE8M0 ? quant8_pow2(v[u][c], code) : quant8_by<DIVISION>(v[u][c], scale));
+            st_global8(dst + 8 * (sub + c * LANES), UE8M0 ? quant8_pow2(v[u][c], code) : quant8_by<DIVISION>(v[u][c], by_scale));
         if (sub == 0) p.scales[row[u] * p.scale_stride_row + col[u] * p.scale_stride_group] = scale;
     }
 }

@@ -2,6 +2,10 @@
 // every warp moves whole 1-KiB rows with 16-byte accesses, two rows per warp, 4 warps per CTA.
 // They answer "how fast can this GPU stream N KiB rows in place / read-only / write-only",
 // which is the bound the fused kernel is measured against next to the driver's copy figure.
+//
+// A measurement aid: built into its own library (libdsv4_hbm_probe.so, declared in include/dsv4_hbm_probe.h),
+// not into the operator library.
+#include "../../include/dsv4_hbm_probe.h"
 #include "dsv4_common.cuh"
 
 namespace dsv4 {
@@ -47,8 +51,6 @@ __global__ void __launch_bounds__(kProbeWarps * 32) hbm_probe_kernel(uint8_t* bu
     if (MODE == 1 && fold == 0x9e3779b9u && sink) *sink = fold;
 }
 
-}  // namespace
-
 cudaError_t launch_hbm_probe(int mode, uint8_t* buf, int64_t rows, uint32_t* sink, cudaStream_t stream) {
     if (rows == 0) return cudaSuccess;
     const unsigned grid = static_cast<unsigned>((rows + kProbeWarps * kProbeRows - 1) / (kProbeWarps * kProbeRows));
@@ -57,8 +59,17 @@ cudaError_t launch_hbm_probe(int mode, uint8_t* buf, int64_t rows, uint32_t* sin
     else if (mode == 1) hbm_probe_kernel<1><<<grid, kProbeWarps * 32, 0, stream>>>(buf, n, sink);
     else if (mode == 3) hbm_probe_kernel<3><<<grid, kProbeWarps * 32, 0, stream>>>(buf, n, sink);
     else hbm_probe_kernel<2><<<grid, kProbeWarps * 32, 0, stream>>>(buf, n, sink);
-    count_launch();
     return cudaGetLastError();
 }
 
+}  // namespace
 }  // namespace dsv4
+
+extern "C" int dsv4_hbm_probe(int mode, void* buffer, int64_t rows, void* cuda_stream) {
+    if (mode < 0 || mode > 3) return -2;
+    if (rows < 0 || rows >= (1LL << 31)) return -2;
+    if (rows == 0) return 0;
+    if (!buffer) return -1;
+    if (reinterpret_cast<uintptr_t>(buffer) & 15u) return -3;
+    return static_cast<int>(dsv4::launch_hbm_probe(mode, static_cast<uint8_t*>(buffer), rows, nullptr, static_cast<cudaStream_t>(cuda_stream)));
+}

@@ -34,7 +34,7 @@ struct InvRopeParams {
 // quantisation groups of 128 are: A lanes 0-15, A lanes 16-31, B lanes 0-15, and B lanes 16-23 together with T.
 constexpr int kHeadsPerTask = 16;
 
-// FASTDIV (fp32-scale mode only): see div_by_scale.
+// FASTDIV (fp32-scale mode only): see ScaleDivider.
 template <int WARPS, bool PACKED, bool FASTDIV, int U, int MIN_CTAS>
 __global__ void __launch_bounds__(WARPS * 32, MIN_CTAS) inv_rope_fp8_quant_kernel(const InvRopeParams p, const uint32_t tasks_per_token,
                                                                       const uint32_t tpt_mul, const uint32_t tpt_shift) {
@@ -117,11 +117,11 @@ __global__ void __launch_bounds__(WARPS * 32, MIN_CTAS) inv_rope_fp8_quant_kerne
                 const uint32_t word = mine | (__shfl_xor_sync(0xffffffffu, mine, 16) << 8);
                 if (lane == 0) *reinterpret_cast<uint32_t*>(scale_row + head_in_group * p.padded_tokens * 4) = word;
             } else {
-                st_global8(out + 8 * lane, quant8_by<FASTDIV ? kDivideFast : kDivideIeee>(a[u], sa));
-                if (lane < kFirstRopeLane) st_global8(out + 256 + 8 * lane, quant8_by<FASTDIV ? kDivideFast : kDivideIeee>(b[u], sb));
-                const float r3 = FASTDIV ? __frcp_rn(s3) : 0.0f;
-                *reinterpret_cast<uint16_t*>(out + kNopeDim + 2 * lane) = static_cast<uint16_t>(
-                    pack_e4m3x4(div_by_scale<FASTDIV ? kDivideFast : kDivideIeee>(te, s3, r3), div_by_scale<FASTDIV ? kDivideFast : kDivideIeee>(to, s3, r3), 0.f, 0.f));
+                constexpr int kDivision = FASTDIV ? kDivideFast : kDivideIeee;
+                st_global8(out + 8 * lane, quant8_by<kDivision>(a[u], sa));
+                if (lane < kFirstRopeLane) st_global8(out + 256 + 8 * lane, quant8_by<kDivision>(b[u], sb));
+                const ScaleDivider<kDivision> by3(s3);
+                *reinterpret_cast<uint16_t*>(out + kNopeDim + 2 * lane) = static_cast<uint16_t>(pack_e4m3x4(by3(te), by3(to), 0.f, 0.f));
                 if ((lane & 15) == 0) {
                     const int k = head_in_group * 4 + (lane >> 4);
                     *reinterpret_cast<float*>(scale_row + k * p.padded_tokens * 4) = sa;

@@ -15,11 +15,14 @@
 //   warps 2.. "workers": one warp per row: RMSNorm (shuffle reduction) + RoPE in shared memory
 //                        for q tiles; RoPE + UE8M0/e4m3 quantisation + scatter to the paged
 //                        cache with ordinary stores for KV tiles.
-// Every mbarrier wait is bounded; a wait that runs out sets bit 0 of the device-side error
-// word (read with dsv4_device_error) and makes the CTA's roles leave their loops.
+// Every mbarrier wait is bounded (PrologueParams::wait_cycles SM cycles, set per launch by the host); a wait that runs
+// out sets bit 0 of the device-side error word (read with dsv4_device_error) and makes the CTA's roles leave their
+// loops: the loader then waits, again bounded, for the copies it has already issued before the CTA ends.
 //
 // Replaces the per-(token, head) Triton programs of the reference
 // (src/flaggems_vllm/ops/fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert.py:45-286).
+#include <mutex>
+
 #include "dsv4_common.cuh"
 
 namespace dsv4 {
@@ -29,8 +32,7 @@ __device__ int g_device_error = 0;
 namespace {
 
 constexpr int kKindQ = 0, kKindKV = 1, kKindDone = 2;
-constexpr uint32_t kWaitLimit = 1u << 24;            // polls before a wait gives up ...
-constexpr long long kWaitCycles = 2000000000LL;  // ... or SM cycles (about a second), whichever comes first
+constexpr uint32_t kWaitLimit = 1u << 24;  // polls before a wait gives up, or PrologueParams::wait_cycles SM cycles, whichever comes first
 
 struct __align__(16) TileHeader {
     uint32_t row0;         // first row of the tile in its tensor (rows and tokens fit 32 bits: host-checked)
@@ -68,13 +70,13 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 // Bounded wait.  Returns false (and raises the abort flag) when the limit is reached or another
 // role of the CTA has already given up.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, long long limit_cycles) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long start = clock64();
     for (uint32_t i = 0; i < kWaitLimit; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if (*abort_flag) return false;
-        if (clock64() - start > kWaitCycles) break;
+        if (clock64() - start > limit_cycles) break;
     }
     *abort_flag = 1;
     atomicOr(&g_device_error, 1);
@@ -186,7 +188,7 @@ prologue_bulk_kernel(const PrologueParams p, const uint32_t kv_tiles, const uint
             const TileHeader after = describe(ahead(tile, 2));  // positions are fetched two tiles ahead
             const int64_t pos_after = fetch_pos(after);
             const int s = it % STAGES;
-            ok = mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1, abort_flag);
+            ok = mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1, abort_flag, p.wait_cycles);
             if (!ok) break;
             if (lane == 0) headers[s] = cur;
             if (cur.kind == kKindDone) {
@@ -196,7 +198,10 @@ prologue_bulk_kernel(const PrologueParams p, const uint32_t kv_tiles, const uint
             uint8_t* stage = smem + s * L::kStageBytes;
             if (lane == 0) {
                 const uint32_t row_bytes = static_cast<uint32_t>(cur.nrows) * kRowBytes;
-                mbar_arrive_expect_tx(&full[s], row_bytes + static_cast<uint32_t>(cur.ntok) * kCosSinRowBytes);
+                // self-test hook: for one chosen tile, announce 16 bytes that are never sent, so that the waits on this
+                // stage run out (p.short_tile is 0xffffffff in every ordinary launch)
+                const uint32_t never_sent = tile == p.short_tile ? 16u : 0u;
+                mbar_arrive_expect_tx(&full[s], row_bytes + static_cast<uint32_t>(cur.ntok) * kCosSinRowBytes + never_sent);
                 const uint8_t* src = (cur.kind == kKindQ ? p.q : p.kv) + static_cast<uint64_t>(cur.row0) * kRowBytes;
                 bulk_load(stage, src, row_bytes, &full[s]);
             }
@@ -215,7 +220,7 @@ prologue_bulk_kernel(const PrologueParams p, const uint32_t kv_tiles, const uint
             for (uint32_t it = first; it < issued; ++it)
             {
                 const long long start = clock64();
-                while (!mbar_try_wait(&full[it % STAGES], (it / STAGES) & 1) && clock64() - start < kWaitCycles) {
+                while (!mbar_try_wait(&full[it % STAGES], (it / STAGES) & 1) && clock64() - start < p.wait_cycles) {
                 }
             }
         }
@@ -225,10 +230,10 @@ prologue_bulk_kernel(const PrologueParams p, const uint32_t kv_tiles, const uint
             for (uint32_t it = 0;; ++it) {
                 const int s = it % STAGES;
                 const uint32_t parity = (it / STAGES) & 1;
-                if (!mbar_wait(&full[s], parity, abort_flag)) break;
+                if (!mbar_wait(&full[s], parity, abort_flag, p.wait_cycles)) break;
                 const TileHeader h = headers[s];
                 if (h.kind == kKindDone) break;
-                if (!mbar_wait(&done[s], parity, abort_flag)) break;
+                if (!mbar_wait(&done[s], parity, abort_flag, p.wait_cycles)) break;
                 if (h.kind == kKindQ)
                     bulk_store(p.q + static_cast<uint64_t>(h.row0) * kRowBytes, smem + s * L::kStageBytes, static_cast<uint32_t>(h.nrows) * kRowBytes);
                 bulk_commit();
@@ -244,7 +249,7 @@ prologue_bulk_kernel(const PrologueParams p, const uint32_t kv_tiles, const uint
         const int w = warp - 2;
         for (uint32_t it = 0;; ++it) {
             const int s = it % STAGES;
-            if (!mbar_wait(&full[s], (it / STAGES) & 1, abort_flag)) break;
+            if (!mbar_wait(&full[s], (it / STAGES) & 1, abort_flag, p.wait_cycles)) break;
             const TileHeader h = headers[s];
             if (h.kind == kKindDone) break;
             uint8_t* stage = smem + s * L::kStageBytes;
@@ -295,9 +300,11 @@ prologue_bulk_kernel(const PrologueParams p, const uint32_t kv_tiles, const uint
     }
 }
 
+// Per-device set-up, done once per device however many host threads make their first call at the same time.
 struct DeviceInfo {
+    std::once_flag once;
     int sm_count = 0;
-    bool configured = false;
+    cudaError_t status = cudaSuccess;
 };
 DeviceInfo g_devices[64];
 
@@ -311,13 +318,13 @@ cudaError_t launch(const PrologueParams& p, cudaStream_t stream) {
     if (err != cudaSuccess) return err;
     if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
     DeviceInfo& info = g_devices[dev];
-    if (!info.configured) {
-        err = cudaDeviceGetAttribute(&info.sm_count, cudaDevAttrMultiProcessorCount, dev);
-        if (err != cudaSuccess) return err;
-        err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotalBytes);
-        if (err != cudaSuccess) return err;
-        info.configured = true;
-    }
+    std::call_once(info.once, [&]() {
+        info.status = cudaDeviceGetAttribute(&info.sm_count, cudaDevAttrMultiProcessorCount, dev);
+        if (info.status == cudaSuccess)
+            info.status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotalBytes);
+    });
+    if (info.status != cudaSuccess) return info.status;
+    if (info.sm_count <= 0) return cudaErrorInvalidDevice;
     const int64_t kv_tiles = (p.num_tokens_insert + TILE - 1) / TILE;
     const int64_t q_tiles = (p.num_tokens * p.num_heads + TILE - 1) / TILE;
     const int64_t total = kv_tiles + q_tiles;

@@ -24,8 +24,13 @@ namespace {
 __device__ __forceinline__ void wait_for_preceding_kernel() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void let_next_kernel_start() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
-template <int RPW, int WARPS, int MIN_CTAS, bool CHECKED, bool PADDED, bool PDL = false>
+// STAGED: the cos|sin rows of the tile's tokens go through shared memory (one fetch per CTA, one barrier).  Without
+// it every warp fetches position and table row of its own rows straight into registers (lane i holds cosine i and
+// sine i): 256 more bytes from L2 per row, but no barrier and no shared-memory round trip in the dependent chain
+// position -> table row, which is what a launch of a few waves waits for.
+template <int RPW, int WARPS, int MIN_CTAS, bool CHECKED, bool PADDED, bool PDL = false, bool STAGED = true>
 __global__ void __launch_bounds__(WARPS * 32, MIN_CTAS) prologue_rows_kernel(const PrologueParams p, const int64_t kv_ctas) {
+    static_assert(STAGED || !CHECKED, "the range-checked build marks bad tokens in shared memory");
     constexpr int TILE = RPW * WARPS;
     constexpr int MAX_TOKENS = TILE + 1;  // a tile of TILE rows touches at most TILE tokens (+1 slack)
     __shared__ __align__(16) float cs_smem[MAX_TOKENS][kRopeDim];
@@ -123,18 +128,31 @@ __global__ void __launch_bounds__(WARPS * 32, MIN_CTAS) prologue_rows_kernel(con
             *reinterpret_cast<float4*>(&cs_smem[j][4 * part]) = ld_readonly_f4(p.cos_sin + pos * kRopeDim + 4 * part);
         }
     };
+    // without staging: cosine and sine of this lane's pair for each row of the warp, straight from the table
+    float cos_r[RPW], sin_r[RPW];
+    const auto fetch_cos_sin = [&]() {
+#pragma unroll
+        for (int i = 0; i < RPW; ++i) {
+            cos_r[i] = sin_r[i] = 0.f;
+            if (row0 + i < total_rows) {
+                const int64_t pos = p.position_ids[fast_div(row0 + i, p.heads_mul, p.heads_shift)];
+                const float* cs = p.cos_sin + pos * kRopeDim + lane;
+                cos_r[i] = __ldg(cs), sin_r[i] = __ldg(cs + 32);
+            }
+        }
+    };
     if (PDL) {
         // the table rows first (they do not depend on the preceding kernel), q only once that kernel has finished
-        stage_cos_sin();
+        if (STAGED) stage_cos_sin(); else fetch_cos_sin();
         wait_for_preceding_kernel();
         issue_row_loads();
         let_next_kernel_start();
     } else {
         // every row load goes out first; the table rows are fetched while they fly
         issue_row_loads();
-        stage_cos_sin();
+        if (STAGED) stage_cos_sin(); else fetch_cos_sin();
     }
-    __syncthreads();
+    if (STAGED) __syncthreads();
 
     // 3. one row at a time: unpack once, reduce, scale, rotate the lane's pair, store
 #pragma unroll
@@ -152,7 +170,7 @@ __global__ void __launch_bounds__(WARPS * 32, MIN_CTAS) prologue_rows_kernel(con
         st_stream16(row + 16 * lane, pack8(xa));
         if (lane < kFirstRopeLane) st_stream16(row + 512 + 16 * lane, pack8(xb));
         st_stream4(row + 2 * kNopeDim + 4 * lane,
-                   scale_rotate_pair(tail[i], r, cs_smem[tok][lane], cs_smem[tok][32 + lane]));
+                   scale_rotate_pair(tail[i], r, STAGED ? cs_smem[tok][lane] : cos_r[i], STAGED ? cs_smem[tok][32 + lane] : sin_r[i]));
     }
 }
 
@@ -168,16 +186,20 @@ cudaError_t launch(const PrologueParams& p, bool checked, cudaStream_t stream) {
     if (checked) {
         prologue_rows_kernel<RPW, WARPS, MIN_CTAS, true, false><<<static_cast<unsigned>(grid), WARPS * 32, 0, stream>>>(p, kv_ctas);
     } else if (p.pdl) {
+        const auto kernel = p.table_staging ? prologue_rows_kernel<RPW, WARPS, MIN_CTAS, false, false, true, true>
+                                            : prologue_rows_kernel<RPW, WARPS, MIN_CTAS, false, false, true, false>;
         cudaLaunchConfig_t config = {};
         config.gridDim = dim3(static_cast<unsigned>(grid)), config.blockDim = dim3(WARPS * 32), config.stream = stream;
         cudaLaunchAttribute attribute[1];
         attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attribute[0].val.programmaticStreamSerializationAllowed = 1;
         config.attrs = attribute, config.numAttrs = 1;
-        const cudaError_t err = cudaLaunchKernelEx(&config, prologue_rows_kernel<RPW, WARPS, MIN_CTAS, false, false, true>, p, kv_ctas);
+        const cudaError_t err = cudaLaunchKernelEx(&config, kernel, p, kv_ctas);
         if (err != cudaSuccess) return err;
-    } else {
+    } else if (p.table_staging) {
         prologue_rows_kernel<RPW, WARPS, MIN_CTAS, false, false><<<static_cast<unsigned>(grid), WARPS * 32, 0, stream>>>(p, kv_ctas);
+    } else {
+        prologue_rows_kernel<RPW, WARPS, MIN_CTAS, false, false, false, false><<<static_cast<unsigned>(grid), WARPS * 32, 0, stream>>>(p, kv_ctas);
     }
     count_launch();
     return cudaGetLastError();

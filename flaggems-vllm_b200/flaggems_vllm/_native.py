@@ -29,11 +29,13 @@ EXPORTS = (
     "dsv4_top_k_per_row_decode",
     "dsv4_top_k_per_row_prefill",
     "dsv4_fused_indexer_q_rope_quant",
-    "dsv4_hbm_probe",
     "dsv4_device_error",
     "dsv4_set_variant",
     "dsv4_get_variant",
+    "dsv4_set_bulk_wait_cycles",
+    "dsv4_bulk_wait_selftest",
     "dsv4_set_pdl",
+    "dsv4_set_table_staging",
     "dsv4_launch_count",
     "dsv4_error_string",
     "dsv4_version",
@@ -101,12 +103,16 @@ def lib() -> ctypes.CDLL:
     L.dsv4_fused_indexer_q_rope_quant.argtypes = [vp, vp, i64, i64, vp, i64, i32, i64, vp, i64, i64, vp, i64, i64, vp, i64, i32,
                                                   vp, i64, f32, f32, i64, i64, i64, i32, vp]
     L.dsv4_fused_indexer_q_rope_quant.restype = i32
-    L.dsv4_hbm_probe.argtypes = [i32, vp, i64, vp]
-    L.dsv4_hbm_probe.restype = i32
     L.dsv4_device_error.argtypes = [vp]
     L.dsv4_device_error.restype = i32
     L.dsv4_set_pdl.argtypes = [i32]
     L.dsv4_set_pdl.restype = i32
+    L.dsv4_set_bulk_wait_cycles.argtypes = [i64]
+    L.dsv4_set_bulk_wait_cycles.restype = i64
+    L.dsv4_bulk_wait_selftest.argtypes = [vp, vp, vp, vp, vp, vp, f32, i64, i64, i64, i64, i64, i64, vp]
+    L.dsv4_bulk_wait_selftest.restype = i32
+    L.dsv4_set_table_staging.argtypes = [i32]
+    L.dsv4_set_table_staging.restype = i32
     L.dsv4_set_variant.argtypes = [i32]
     L.dsv4_set_variant.restype = i32
     L.dsv4_get_variant.restype = i32
@@ -144,6 +150,12 @@ def set_variant(variant: int) -> int:
 def set_pdl(enabled: bool) -> bool:
     """Programmatic dependent launch of the prologue (see dsv4_set_pdl); returns the previous setting."""
     return bool(lib().dsv4_set_pdl(1 if enabled else 0))
+
+
+def set_table_staging(mode: int) -> int:
+    """-1: by launch size, 0: per-warp table fetch, 1: shared-memory staging (see dsv4_set_table_staging);
+    returns the previous mode."""
+    return int(lib().dsv4_set_table_staging(int(mode)))
 
 
 def version() -> str:

@@ -1,7 +1,10 @@
-"""Builds libdsv4_prologue.so in place with nvcc for sm_100a: `python -m flaggems_vllm.build`.
+"""Builds the CUDA libraries in place with nvcc for sm_100a: `python -m flaggems_vllm.build`.
 
-Cross-compiles without a GPU.  The CUDA runtime is linked statically so the library
-loads (and exports its symbols) on a machine that has no driver.
+  libdsv4_prologue.so            the operators (the product)
+  testing/libdsv4_hbm_probe.so   the bandwidth probe the benchmark compares the kernels with (a measurement aid)
+
+Cross-compiles without a GPU.  The CUDA runtime is linked statically so the libraries
+load (and export their symbols) on a machine that has no driver.
 """
 from __future__ import annotations
 
@@ -14,9 +17,11 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 CSRC = PKG.parent / "csrc"
 OUT = PKG / "libdsv4_prologue.so"
-SOURCES = ("abi.cu", "prologue_rows.cu", "prologue_bulk.cu", "gather_dequant.cu", "hbm_probe.cu", "q_kv_rmsnorm.cu", "inv_rope_fp8_quant.cu", "indexer_k_quant.cu",
+PROBE_OUT = PKG / "testing" / "libdsv4_hbm_probe.so"
+PROBE_SOURCES = ("hbm_probe.cu",)
+SOURCES = ("abi.cu", "prologue_rows.cu", "prologue_bulk.cu", "gather_dequant.cu", "q_kv_rmsnorm.cu", "inv_rope_fp8_quant.cu", "indexer_k_quant.cu",
            "indexer_q_rope_quant.cu", "cp_gather_indexer.cu", "topk_indices.cu", "topk_per_row.cu", "topk_per_row_short.cu", "group_quant_fp8.cu")
-HEADERS = ("dsv4_common.cuh", "../../include/dsv4_prologue.h")
+HEADERS = ("dsv4_common.cuh", "../../include/dsv4_prologue.h", "../../include/dsv4_hbm_probe.h")
 
 
 def nvcc_path() -> str:
@@ -26,32 +31,34 @@ def nvcc_path() -> str:
     return exe
 
 
-def command(extra_flags=()) -> list[str]:
+def command(extra_flags=(), out: Path = OUT, sources=SOURCES) -> list[str]:
     return [
         nvcc_path(), "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
         "-Xcompiler", "-fPIC", "-shared", "-cudart", "static", *extra_flags,
-        "-o", str(OUT), *[str(CSRC / s) for s in SOURCES],
+        "-o", str(out), *[str(CSRC / s) for s in sources],
     ]
 
 
-def up_to_date() -> bool:
-    if not OUT.exists():
+def up_to_date(out: Path = OUT, sources=SOURCES) -> bool:
+    if not out.exists():
         return False
-    newest = max((CSRC / f).resolve().stat().st_mtime for f in SOURCES + HEADERS)
-    return OUT.stat().st_mtime >= newest
+    newest = max((CSRC / f).resolve().stat().st_mtime for f in tuple(sources) + HEADERS)
+    return out.stat().st_mtime >= newest
 
 
 def build(force: bool = False, verbose: bool = False, extra_flags=()) -> Path:
-    if not force and up_to_date():
-        return OUT
-    cmd = command(extra_flags)
+    """Build whichever of the two libraries is older than its sources; returns the operator library's path."""
     env = dict(os.environ)
     env.pop("CC", None), env.pop("CXX", None)  # let nvcc pick the system host compiler
-    res = subprocess.run(cmd, capture_output=True, text=True, env=env)
-    if verbose or res.returncode != 0:
-        sys.stderr.write(" ".join(cmd) + "\n" + res.stdout + res.stderr)
-    if res.returncode != 0:
-        raise RuntimeError("nvcc failed building libdsv4_prologue.so")
+    for out, sources in ((OUT, SOURCES), (PROBE_OUT, PROBE_SOURCES)):
+        if not force and up_to_date(out, sources):
+            continue
+        cmd = command(extra_flags, out, sources)
+        res = subprocess.run(cmd, capture_output=True, text=True, env=env)
+        if verbose or res.returncode != 0:
+            sys.stderr.write(" ".join(cmd) + "\n" + res.stdout + res.stderr)
+        if res.returncode != 0:
+            raise RuntimeError(f"nvcc failed building {out.name}")
     return OUT
 
 

@@ -19,7 +19,8 @@ TOKEN_BYTES = 584  # 448 e4m3 + 64 bf16 + 8 scale bytes per cached token
 
 def _check_arguments(q, kv, k_cache, slot_mapping, position_ids, cos_sin_cache, cache_block_size):
     """The reference's checks (:320-333) in its order and with its exception type, then what the reference leaves
-    to chance and a raw-pointer kernel cannot.  Returns (num_tokens, num_heads, num_tokens_insert, device)."""
+    to chance and a raw-pointer kernel cannot.  Returns (num_tokens, num_heads, num_tokens_insert, device index).
+    Written for a short call: decode-sized launches run about as long as this function."""
     assert q.is_contiguous() and kv.is_contiguous()
     num_tokens, num_heads, head_dims = q.shape
     assert head_dims == HEAD_DIM
@@ -37,11 +38,22 @@ def _check_arguments(q, kv, k_cache, slot_mapping, position_ids, cos_sin_cache, 
     assert k_cache.dim() == 2 and k_cache.stride(1) == 1, "k_cache must be [num_blocks, block_bytes] with unit byte stride"
     assert cache_block_size > 0 and k_cache.shape[1] >= cache_block_size * TOKEN_BYTES, "cache block too small"
     assert slot_mapping.is_contiguous() and position_ids.is_contiguous() and cos_sin_cache.is_contiguous()
-    dev = q.device
-    assert dev.type == "cuda", "this operator has no CPU path: tensors must live on a CUDA device"
-    for t in (kv, k_cache, slot_mapping, position_ids, cos_sin_cache):
-        assert t.device == dev, "all tensors must be on the same device"
-    return num_tokens, num_heads, num_tokens_insert, dev
+    index = q.get_device()  # -1 for a CPU tensor
+    assert index >= 0 and q.is_cuda, "this operator has no CPU path: tensors must live on a CUDA device"
+    assert (kv.get_device() == index and k_cache.get_device() == index and slot_mapping.get_device() == index
+            and position_ids.get_device() == index and cos_sin_cache.get_device() == index), "all tensors must be on the same device"
+    return num_tokens, num_heads, num_tokens_insert, index
+
+
+# raw handle of the current stream without building a torch.cuda.Stream object
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None) or (lambda index: torch.cuda.current_stream(index).cuda_stream)
+_launch = None  # the bound C entry point, looked up once
+
+
+def _bind():
+    global _launch
+    _launch = _native.lib().dsv4_qnorm_rope_kv_insert
+    return _launch
 
 
 def fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert(
@@ -72,27 +84,24 @@ def fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert(
         eps: RMSNorm epsilon
         cache_block_size: tokens per cache block
     """
-    num_tokens, num_heads, num_tokens_insert, dev = _check_arguments(
+    num_tokens, num_heads, num_tokens_insert, index = _check_arguments(
         q, kv, k_cache, slot_mapping, position_ids, cos_sin_cache, cache_block_size)
     if num_tokens == 0:
         return
-
-    def launch():
-        code = _native.lib().dsv4_qnorm_rope_kv_insert(
-            q.data_ptr(), kv.data_ptr(), k_cache.data_ptr(), slot_mapping.data_ptr(), position_ids.data_ptr(),
-            cos_sin_cache.data_ptr(), float(eps), num_tokens, num_heads, num_tokens_insert,
-            int(cache_block_size), k_cache.stride(0), torch.cuda.current_stream(dev).cuda_stream,
-        )
-        if code != 0:
-            _native.check(code)
-
+    launch = _launch or _bind()
     # the library launches on the current device: switch only when q lives elsewhere (the guard costs
     # several microseconds, which matters for decode-sized calls outside CUDA graphs)
-    if dev.index is None or dev.index == torch.cuda.current_device():
-        launch()
+    if index == torch.cuda.current_device():
+        code = launch(q.data_ptr(), kv.data_ptr(), k_cache.data_ptr(), slot_mapping.data_ptr(), position_ids.data_ptr(),
+                      cos_sin_cache.data_ptr(), float(eps), num_tokens, num_heads, num_tokens_insert, int(cache_block_size),
+                      k_cache.stride(0), _raw_stream(index))
     else:
-        with torch.cuda.device(dev):
-            launch()
+        with torch.cuda.device(index):
+            code = launch(q.data_ptr(), kv.data_ptr(), k_cache.data_ptr(), slot_mapping.data_ptr(), position_ids.data_ptr(),
+                          cos_sin_cache.data_ptr(), float(eps), num_tokens, num_heads, num_tokens_insert, int(cache_block_size),
+                          k_cache.stride(0), _raw_stream(index))
+    if code != 0:
+        _native.check(code)
 
 
 def fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert_padded(
@@ -109,8 +118,9 @@ def fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert_padded(
     """The nine-argument, out-of-place form vLLM >= 0.22 uses: q is left untouched and a new tensor
     [num_tokens, padded_heads, 512] is returned whose first num_heads heads hold the normalised, rotated q and
     whose remaining heads are zero; the KV side is the same as in the in-place operator."""
-    num_tokens, num_heads, num_tokens_insert, dev = _check_arguments(
+    num_tokens, num_heads, num_tokens_insert, _ = _check_arguments(
         q, kv, k_cache, slot_mapping, position_ids, cos_sin_cache, cache_block_size)
+    dev = q.device
     assert padded_heads >= num_heads
     q_out = torch.empty(num_tokens, padded_heads, HEAD_DIM, dtype=q.dtype, device=dev)
     if num_tokens == 0:

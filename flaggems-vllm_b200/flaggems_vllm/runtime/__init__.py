@@ -9,6 +9,10 @@ import torch
 class _Device:
     name = "cuda"
     vendor_name = "nvidia"
+    # capability flags the reference's shared test helpers read (tests/accuracy_utils.py:26-28 there)
+    support_fp64 = True
+    support_bf16 = True
+    support_int64 = True
 
     @property
     def device_count(self) -> int:

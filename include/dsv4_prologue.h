@@ -296,17 +296,6 @@ int dsv4_fused_indexer_q_rope_quant(const int64_t* positions, const void* index_
                                     void* cuda_stream);
 
 /*
- * Bandwidth probe with the prologue's q access pattern and no arithmetic, over `rows` rows of
- * 1 KiB starting at `buffer` (16-byte aligned): mode 0 reads every row and writes it back in
- * place, mode 1 only reads, mode 2 only writes (the buffer's contents are overwritten), mode 3 reads
- * every row and writes 512 bytes per row behind the rows (the buffer then holds rows * 1536 bytes;
- * 2 read : 1 write, the mix of the narrowing sibling operators).  Used by
- * bench.py to measure, on the GPU at hand, the ceiling the fused kernel is compared with.
- * No counterpart in the reference.
- */
-int dsv4_hbm_probe(int mode, void* buffer, int64_t rows, void* cuda_stream);
-
-/*
  * Reads into *value_host, and clears, the error word the kernels of the current device keep:
  * bit 0 = a bounded wait inside the DSV4_VARIANT_BULK kernel ran out (its result is then
  * incomplete).  Synchronises the device.  0 after every healthy run.  No counterpart in the reference.
@@ -320,12 +309,37 @@ int dsv4_device_error(int32_t* value_host);
 int dsv4_set_variant(int variant);
 int dsv4_get_variant(void);
 
+/* DSV4_VARIANT_BULK only.  Every wait of that kernel on a shared-memory barrier is bounded: after `cycles` SM cycles
+ * (default 2e8, about 0.1 s; values above 2e9 are clamped, values <= 0 only read the setting) the waiting role gives up,
+ * bit 0 of the device error word is set, the CTA's other roles leave their loops, the loader waits - bounded again - for
+ * the copies it has issued, and the kernel returns with q and the cache partly processed.  The entry points still
+ * return 0 in that case (the launch itself succeeded): a caller that selects the bulk variant must read
+ * dsv4_device_error at its next synchronisation point.  Returns the previous limit. */
+int64_t dsv4_set_bulk_wait_cycles(int64_t cycles);
+
+/* Self-test of that give-up path, for test suites; not an operator.  Same arguments and effects as
+ * dsv4_qnorm_rope_kv_insert on the bulk variant, except that the loader of tile `short_tile` (tiles are 16 rows:
+ * first ceil(num_tokens_insert / 16) tiles of kv rows, then the tiles of q rows) announces 16 bytes it never sends,
+ * so the waits on that tile's stage run out after the limit set with dsv4_set_bulk_wait_cycles.  Nothing traps and
+ * nothing waits without a limit: the kernel returns by itself, dsv4_device_error then reads 1, and the rows of the
+ * affected CTA from that tile on are left unprocessed. */
+int dsv4_bulk_wait_selftest(void* q, const void* kv, void* k_cache, const int64_t* slot_mapping, const int64_t* position_ids,
+                            const float* cos_sin_cache, float eps, int64_t num_tokens, int64_t num_heads,
+                            int64_t num_tokens_insert, int64_t cache_block_size, int64_t kv_block_stride_bytes,
+                            int64_t short_tile, void* cuda_stream);
+
 /* Programmatic dependent launch for dsv4_qnorm_rope_kv_insert (rows variant; also read once from the environment
  * variable DSV4_PDL; off by default).  When on, the kernel is launched so that it may start before the preceding kernel
  * of the stream has finished: it fetches position_ids, slot_mapping and the cos/sin rows at once and waits for that
  * kernel only before it touches q, kv and the cache.  The caller promises that position_ids, slot_mapping and
  * cos_sin_cache are not written by the kernel that precedes the call in the stream.  Returns the previous setting. */
 int dsv4_set_pdl(int enabled);
+
+/* Where the rows variant of dsv4_qnorm_rope_kv_insert takes the cos/sin rows from (also read once from the environment
+ * variable DSV4_TABLE_STAGING): -1 (default) = by launch size, 0 = every warp fetches the table row of its own q rows
+ * into registers (no barrier; the choice for decode-sized launches), 1 = once per CTA through shared memory (less L2
+ * traffic; the choice for large launches).  Results do not depend on it.  Returns the previous mode. */
+int dsv4_set_table_staging(int mode);
 
 /* Number of kernels this library has launched in this process (all entry points). */
 int64_t dsv4_launch_count(void);

@@ -9,28 +9,40 @@ from pathlib import Path
 import pytest
 
 from flaggems_vllm import _native
+from flaggems_vllm.testing import hbm_probe
 
 ROOT = Path(__file__).resolve().parent.parent
 HEADERS = sorted((ROOT / "include").glob("*.h"))
 
 
-def declared_functions() -> list[str]:
+# which library implements which header
+LIBRARY_OF = {"dsv4_prologue.h": _native.LIB_PATH, "dsv4_hbm_probe.h": hbm_probe.LIB_PATH}
+
+
+def declared_functions() -> list[tuple[str, str]]:
+    """(header name, function) for every function a header under include/ declares."""
     names = []
     for h in HEADERS:
         text = re.sub(r"/\*.*?\*/", "", h.read_text(), flags=re.S)
-        names += re.findall(r"\b(dsv4_[a-z0-9_]+)\s*\(", text)
-    return sorted(set(names))
+        names += [(h.name, f) for f in sorted(set(re.findall(r"\b(dsv4_[a-z0-9_]+)\s*\(", text)))]
+    return names
 
 
 def test_header_declares_the_expected_entry_points():
     assert HEADERS, "include/*.h missing"
-    assert set(_native.EXPORTS) <= set(declared_functions())
+    assert {h.name for h in HEADERS} == set(LIBRARY_OF)
+    assert set(_native.EXPORTS) == {f for h, f in declared_functions() if h == "dsv4_prologue.h"}
 
 
-@pytest.mark.parametrize("symbol", declared_functions())
-def test_library_exports_every_declared_symbol(symbol):
-    lib = ctypes.CDLL(str(_native.LIB_PATH))
+@pytest.mark.parametrize("header,symbol", declared_functions())
+def test_library_exports_every_declared_symbol(header, symbol):
+    lib = ctypes.CDLL(str(LIBRARY_OF[header]))
     assert getattr(lib, symbol) is not None
+
+
+def test_operator_library_exports_no_measurement_aid():
+    lib = ctypes.CDLL(str(_native.LIB_PATH))
+    assert not hasattr(lib, "dsv4_hbm_probe")
 
 
 def test_version_and_error_strings():

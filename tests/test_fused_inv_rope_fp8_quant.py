@@ -41,7 +41,7 @@ def test_pow2_scale_bit_derivation_equals_log_statement_for_every_bf16_amax():
 
 
 def test_division_shortcut_never_changes_a_byte():
-    """fp32-scale mode divides with a reciprocal and one correction (three instructions) instead of an IEEE
+    """fp32-scale mode divides with a two-term reciprocal (two instructions per value) instead of an IEEE
     division.  Every reachable (scale, value) pair for bf16 inputs and the reference's eps: no e4m3 byte differs."""
     pairs, byte_mismatches, _ = c_oracle.check_division_shortcut(1e-10)
     assert pairs > 5e8 and byte_mismatches == 0

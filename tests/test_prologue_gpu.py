@@ -352,12 +352,14 @@ def test_hbm_probe_modes_leave_or_fill_the_buffer():
     rows = 1000
     buf = torch.randint(0, 256, ((rows + 8) * 1024,), dtype=torch.uint8, device=DEV)
     before = buf.clone()
-    lib, stream = _native.lib(), torch.cuda.current_stream().cuda_stream
+    from flaggems_vllm.testing import hbm_probe
+
+    stream = torch.cuda.current_stream().cuda_stream
     for mode in (0, 1):
-        _native.check(lib.dsv4_hbm_probe(mode, buf.data_ptr(), rows, stream))
+        hbm_probe.probe(mode, buf.data_ptr(), rows, stream)
         torch.cuda.synchronize()
         assert torch.equal(buf, before)
-    _native.check(lib.dsv4_hbm_probe(2, buf.data_ptr(), rows, stream))
+    hbm_probe.probe(2, buf.data_ptr(), rows, stream)
     torch.cuda.synchronize()
     assert torch.equal(buf[rows * 1024 :], before[rows * 1024 :])
     assert not torch.equal(buf[: rows * 1024], before[: rows * 1024])

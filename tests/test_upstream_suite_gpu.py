@@ -34,8 +34,8 @@ def run_upstream(test_file: str, tmp_path: Path, select: str | None = None, dese
            "-c", str(make_ref.OUT / "pytest.ini"), "--rootdir", str(make_ref.OUT)]
     if select:
         cmd += ["-k", select]
-    for d in deselect:
-        cmd += ["--deselect", f"{target}::{d}"]
+    if deselect:
+        cmd += ["-k", " and ".join(f"not {d}" for d in deselect)]
     env = dict(os.environ)
     env["PYTHONPATH"] = str(PKG_DIR)  # this package, and nothing else of this repository
     env["PYTHONDONTWRITEBYTECODE"] = "1"
@@ -61,6 +61,7 @@ def test_hot_path_upstream_tests_all_sizes(tmp_path):
     skipped by upstream itself on NVIDIA (no override bound), test_matches_vllm_reference skips itself where the
     installed vLLM's operator has another signature (:661-676)."""
     rc, counts, tail = run_upstream(f"test_{make_ref.OP}.py", tmp_path)
+    print(f"upstream test_{make_ref.OP}.py: {counts}")
     assert rc == 0, tail
     assert counts.get("failed", 0) == 0 and counts.get("error", 0) == 0 and counts.get("errors", 0) == 0, tail
     # 8 q-path + 8 kv-path + 8 DP-padding + 36 combined cases
@@ -73,6 +74,9 @@ SIBLINGS = [
     ("test_fused_indexer_q_rope_quant.py", ()),
     ("test_indexer_k_quant_and_cache.py", ()),
     ("test_cp_gather_indexer_k_quant_cache.py", ()),
+    # test_unfused_path (:563 upstream) builds its expectation from flaggems_vllm.apply_rotary_pos_emb, a generic
+    # rotary operator that is not on this path and that this package does not provide
+    ("test_fused_inv_rope_fp8_quant.py", ("test_unfused_path",)),
 ]
 
 
@@ -81,5 +85,6 @@ def test_sibling_upstream_tests(tmp_path, test_file, deselect):
     """The upstream test files of the neighbouring operators (reader of the cache, the weighted norms before the
     path, the sparse-indexer prologue), unmodified, against this package."""
     rc, counts, tail = run_upstream(test_file, tmp_path, deselect=deselect)
+    print(f"upstream {test_file}: {counts}")
     assert rc == 0, tail
     assert counts.get("failed", 0) == 0 and counts.get("passed", 0) > 0, tail
