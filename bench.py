@@ -628,38 +628,36 @@ def side_measurement(name, steps, warmup, op, native):
     out = {"tokens": w.num_tokens, "us_per_launch": secs / steps * 1e6, "tokens_per_s": w.num_tokens * steps / secs,
            "hbm_gbs": nbytes * steps / secs / 1e9, "rotating_sets": sets}
     if sets > 1:
-        # launches this short are bounded by the Python call, not by the GPU: the same rotation captured once in a
-        # CUDA graph (how serving runs decode steps) and replayed gives the device-side time per launch
+        # The same rotation captured once in a CUDA graph (how serving runs decode steps) and replayed gives the
+        # device-side time per launch.  Both ways of calling are timed in each launch mode of the library
+        # (dsv4_set_pdl): 2 = the default, dependent launch with ordinary stream semantics; 0 = plain launches;
+        # 1 = dependent launch that also reads positions and table rows early (positions and table are not written
+        # inside the rotation).
         side = torch.cuda.Stream()
-        side.wait_stream(stream)
-        with torch.cuda.stream(side):
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=side):
-                for _ in range(sets):
-                    fn()
-        stream.wait_stream(side)
         replays = max(2, steps // sets)
-        gsecs = time_steps(graph.replay, replays, 2, stream, torch.cuda.synchronize)
-        out["us_per_launch_cuda_graph"] = gsecs / (replays * sets) * 1e6
-        out["hbm_gbs_cuda_graph"] = nbytes * replays * sets / gsecs / 1e9
-        # the same graph with programmatic dependent launch: each launch fetches its positions and table rows while
-        # the launch before it still runs (positions and table are not written inside the graph)
-        previous = native.set_pdl(True)
-        try:
+
+        def graph_us():
+            side.wait_stream(stream)
             with torch.cuda.stream(side):
-                side.wait_stream(stream)
-                graph_pdl = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(graph_pdl, stream=side):
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=side):
                     for _ in range(sets):
                         fn()
             stream.wait_stream(side)
-            psecs = time_steps(graph_pdl.replay, replays, 2, stream, torch.cuda.synchronize)
-            out["us_per_launch_cuda_graph_pdl"] = psecs / (replays * sets) * 1e6
-            # and through the Python entry point, launch by launch
-            esecs = time_steps(fn, steps, warmup, stream, torch.cuda.synchronize)
-            out["us_per_launch_pdl"] = esecs / steps * 1e6
+            return time_steps(graph.replay, replays, 2, stream, torch.cuda.synchronize) / (replays * sets) * 1e6
+
+        out["us_per_launch_cuda_graph"] = graph_us()
+        out["hbm_gbs_cuda_graph"] = nbytes / out["us_per_launch_cuda_graph"] / 1e3
+        default_mode = native.set_pdl(0)
+        try:
+            out["us_per_launch_plain_launch"] = time_steps(fn, steps, warmup, stream, torch.cuda.synchronize) / steps * 1e6
+            out["us_per_launch_cuda_graph_plain_launch"] = graph_us()
+            native.set_pdl(1)
+            out["us_per_launch_early_reads"] = time_steps(fn, steps, warmup, stream, torch.cuda.synchronize) / steps * 1e6
+            out["us_per_launch_cuda_graph_early_reads"] = graph_us()
         finally:
-            native.set_pdl(previous)
+            native.set_pdl(default_mode)
+        out["launch_mode"] = default_mode
         # The ceiling for a launch of THIS size: the arithmetic-free in-place copy with the same row access pattern
         # over the same number of q rows, rotating over as many buffers, replayed from a CUDA graph the same way.
         # A launch this short is bounded by launch, ramp-up and drain as much as by bandwidth; the probe pays the same.

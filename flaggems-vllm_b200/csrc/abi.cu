@@ -29,7 +29,8 @@ int current_pdl() {
     int v = g_pdl.load(std::memory_order_relaxed);
     if (v < 0) {
         const char* e = std::getenv("DSV4_PDL");
-        v = (e && std::atoi(e) != 0) ? 1 : 0;
+        v = e ? std::atoi(e) : 2;
+        if (v < 0 || v > 2) v = 2;
         g_pdl.store(v, std::memory_order_relaxed);
     }
     return v;
@@ -417,9 +418,9 @@ int dsv4_set_variant(int variant) {
 
 int dsv4_get_variant(void) { return current_variant(); }
 
-int dsv4_set_pdl(int enabled) {
+int dsv4_set_pdl(int mode) {
     const int previous = current_pdl();
-    g_pdl.store(enabled ? 1 : 0, std::memory_order_relaxed);
+    g_pdl.store(mode < 0 || mode > 2 ? 2 : mode, std::memory_order_relaxed);
     return previous;
 }
 

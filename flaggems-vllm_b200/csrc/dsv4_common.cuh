@@ -340,52 +340,62 @@ __device__ __forceinline__ uint32_t pow2_ceil_code(float s) {
 // How x / scale is formed for a scale that is not a power of two.
 enum : int { kDivideIeee = 0, kDivideFast = 1, kMultiplyReciprocal = 2 };
 
-// kDivideFast: once per group y = RN(1/scale) and its residual y_lo = RN(fma(-scale, y, 1) * y), so that y + y_lo is
-// 1/scale to about 2^-48; then per value q = fma(x, y, RN(x * y_lo)) - two instructions instead of an IEEE division.
+// kDivideFast: x / scale without an IEEE division.  Once per group: y = the hardware's approximate reciprocal refined
+// by one Newton step (relative error about 2^-44 before its rounding, hence within one ulp of RN(1/scale)) and
+// y_lo = RN(fma(-scale, y, 1) * y), which brings y + y_lo to about 2^-46 of 1/scale.  Per value, either
+//   two-term       q = fma(x, y, RN(x * y_lo))                                    two instructions, scale <= 2^100 only
+//                  (beyond that y_lo would be subnormal), or
+//   corrected      q0 = RN(x * y), r = fma(-scale, q0, x), q = fma(r, y, q0)      three instructions, any scale.
 // q can differ from RN(x/scale) in the last fp32 bit, but never in the e4m3 byte: a CPU test enumerates every bf16
-// group maximum (hence every reachable scale, for the reference's eps = 1e-10) against every bf16 value below it -
-// 5.3e8 pairs, zero differing bytes.  Scales outside [2^-100, 2^100] (where y_lo would be subnormal) are divided.
-// For any other eps the kernels divide.  kMultiplyReciprocal: x * RN(1/scale), what the statement of `act_quant` computes.
-constexpr float kFastDivideMinScale = 0x1p-100f, kFastDivideMaxScale = 0x1p100f;
+// group maximum (hence every reachable scale, for the reference's eps = 1e-10) against every bf16 value below it, for
+// each of the three values y can take (the correctly rounded reciprocal and its two neighbours) and both forms -
+// 1.6e9 cases each, zero differing bytes.  Callers pick the form once per warp (see all_scales_allow_two_term), so the
+// choice is a uniform branch around straight-line code.  For any other eps the kernels divide.
+// kMultiplyReciprocal: x * RN(1/scale), what the statement of `act_quant` computes.
+constexpr float kTwoTermMaxScale = 0x1p100f;
 
 template <int MODE>
 struct ScaleDivider {
     float scale, recip, recip_lo;
-    bool fast;
-    __device__ __forceinline__ explicit ScaleDivider(float s) : scale(s), recip(0.0f), recip_lo(0.0f), fast(false) {
-        if (MODE != kDivideIeee) recip = __frcp_rn(s);
+    __device__ __forceinline__ explicit ScaleDivider(float s) : scale(s), recip(0.0f), recip_lo(0.0f) {
+        if (MODE == kMultiplyReciprocal) recip = __frcp_rn(s);
         if (MODE == kDivideFast) {
+            float y0;
+            asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y0) : "f"(s));
+            recip = __fmaf_rn(__fmaf_rn(-s, y0, 1.0f), y0, y0);
             recip_lo = __fmul_rn(__fmaf_rn(-s, recip, 1.0f), recip);
-            fast = s >= kFastDivideMinScale && s <= kFastDivideMaxScale;
         }
     }
-    // quotient of one value; callers with many values test `fast` once and use the two forms below directly
-    __device__ __forceinline__ float operator()(float x) const {
+    __device__ __forceinline__ bool allows_two_term() const { return scale <= kTwoTermMaxScale; }
+    // TWO_TERM is honoured in kDivideFast mode only
+    template <bool TWO_TERM>
+    __device__ __forceinline__ float quotient(float x) const {
         if (MODE == kMultiplyReciprocal) return __fmul_rn(x, recip);
-        if (MODE == kDivideFast && fast) return quick(x);
-        return __fdiv_rn(x, scale);
+        if (MODE == kDivideIeee) return __fdiv_rn(x, scale);
+        if (TWO_TERM) return __fmaf_rn(x, recip, __fmul_rn(x, recip_lo));
+        const float q0 = __fmul_rn(x, recip);
+        return __fmaf_rn(__fmaf_rn(-scale, q0, x), recip, q0);
     }
-    __device__ __forceinline__ float quick(float x) const { return __fmaf_rn(x, recip, __fmul_rn(x, recip_lo)); }
 };
 
+// True in every lane iff every lane's scales are in the range of the two-term form (warp-uniform by construction).
 template <int MODE>
+__device__ __forceinline__ bool all_scales_allow_two_term(const ScaleDivider<MODE>& a) {
+    return MODE == kDivideFast && __all_sync(0xffffffffu, a.allows_two_term());
+}
+template <int MODE>
+__device__ __forceinline__ bool all_scales_allow_two_term(const ScaleDivider<MODE>& a, const ScaleDivider<MODE>& b, const ScaleDivider<MODE>& c) {
+    return MODE == kDivideFast && __all_sync(0xffffffffu, a.allows_two_term() && b.allows_two_term() && c.allows_two_term());
+}
+
+template <int MODE, bool TWO_TERM>
 __device__ __forceinline__ uint2 quant8_by(const uint4& v, const ScaleDivider<MODE>& d) {
     float x[8];
     unpack8(v, x);
     float q[8];  // the e4m3 conversion saturates at +-448
-    if (MODE == kDivideFast && d.fast) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) q[i] = d.quick(x[i]);
-    } else {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) q[i] = MODE == kMultiplyReciprocal ? __fmul_rn(x[i], d.recip) : __fdiv_rn(x[i], d.scale);
-    }
+    for (int i = 0; i < 8; ++i) q[i] = d.template quotient<TWO_TERM>(x[i]);
     return make_uint2(pack_e4m3x4(q[0], q[1], q[2], q[3]), pack_e4m3x4(q[4], q[5], q[6], q[7]));
-}
-
-template <int MODE>
-__device__ __forceinline__ uint2 quant8_by(const uint4& v, float scale) {
-    return quant8_by<MODE>(v, ScaleDivider<MODE>(scale));
 }
 
 // 8 bf16 values times the exact reciprocal of a power-of-two scale (same result as dividing by it).  The products are

@@ -71,12 +71,24 @@ __global__ void __launch_bounds__(WARPS * 32) group_quant_fp8_kernel(const Group
             code = pow2_ceil_code(scale);
             scale = __uint_as_float(code << 23);
         }
+        const bool two_term = !UE8M0 && DIVISION == kDivideFast && __all_sync(0xffffffffu, scale <= kTwoTermMaxScale);
         if (g >= p.num_groups) continue;
         uint8_t* dst = p.out + g * p.group_size;
-        const ScaleDivider<DIVISION> by_scale(scale);
+        if (UE8M0) {
 #pragma unroll
-        for (int c = 0; c < CHUNKS; ++c)
-            st_global8(dst + 8 * (sub + c * LANES), UE8M0 ? quant8_pow2(v[u][c], code) : quant8_by<DIVISION>(v[u][c], by_scale));
+            for (int c = 0; c < CHUNKS; ++c) st_global8(dst + 8 * (sub + c * LANES), quant8_pow2(v[u][c], code));
+        } else {
+            // one warp-uniform choice of the division form per pass (see ScaleDivider); lanes past the last group
+            // have left the loop body above only after the vote, so every lane takes part in it
+            const ScaleDivider<DIVISION> by_scale(scale);
+            if (two_term) {
+#pragma unroll
+                for (int c = 0; c < CHUNKS; ++c) st_global8(dst + 8 * (sub + c * LANES), quant8_by<DIVISION, true>(v[u][c], by_scale));
+            } else {
+#pragma unroll
+                for (int c = 0; c < CHUNKS; ++c) st_global8(dst + 8 * (sub + c * LANES), quant8_by<DIVISION, false>(v[u][c], by_scale));
+            }
+        }
         if (sub == 0) p.scales[row[u] * p.scale_stride_row + col[u] * p.scale_stride_group] = scale;
     }
 }

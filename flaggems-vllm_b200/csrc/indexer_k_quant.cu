@@ -151,25 +151,48 @@ __global__ void __launch_bounds__(WARPS * 32) indexer_k_quant_rows_kernel(const 
 
 // The DeepSeek-V4 indexer shape (head_dim = quant_block = 128): 8 lanes per token, lane s keeps values [8s, 8s+8)
 // and [64+8s, 64+8s+8), one scale per token; 4 tokens per warp instruction, U passes in flight.
-template <int WARPS, int U, bool FP16>
-__global__ void __launch_bounds__(WARPS * 32) indexer_k_quant_128_kernel(const IndexerParams p) {
+#ifndef DSV4_INDEXER_K_CTAS
+#define DSV4_INDEXER_K_CTAS 1
+#endif
+// UE8M0 (power-of-two scales): bf16 keys stay packed - group maximum and scaling on the bf16x2 words, as in quant8_pow2.
+template <int WARPS, int U, bool FP16, bool UE8M0>
+__global__ void __launch_bounds__(WARPS * 32, DSV4_INDEXER_K_CTAS) indexer_k_quant_128_kernel(const IndexerParams p) {
     const int lane = threadIdx.x & 31, sub = lane & 7, which = lane >> 3;
     const int64_t base = (static_cast<int64_t>(blockIdx.x) * WARPS + (threadIdx.x >> 5)) * (U * 4) + which;
     uint4 lo[U], hi[U];
     int64_t slot[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
+        // the key row is fetched whether or not its slot turns out to be a skipped one (-1): the row load then does
+        // not wait for the slot, and padding tokens are few
         const int64_t t = base + u * 4;
-        slot[u] = t < p.num_tokens ? p.slot_mapping[t] : -1;
+        slot[u] = -1;
         lo[u] = hi[u] = make_uint4(0u, 0u, 0u, 0u);
-        if (slot[u] >= 0) {
+        if (t < p.num_tokens) {
             const uint8_t* row = p.k + (t * p.k_stride + 8 * sub) * 2;
+            slot[u] = p.slot_mapping[t];
             lo[u] = ld_stream16(row);
             hi[u] = ld_stream16(row + 128);
         }
     }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
+        if (UE8M0 && !FP16) {
+            uint32_t pk = max_abs_bf16x2(max_abs_bf16x2(max_abs_bf16x2(lo[u].x, lo[u].y), max_abs_bf16x2(lo[u].z, lo[u].w)),
+                                         max_abs_bf16x2(max_abs_bf16x2(hi[u].x, hi[u].y), max_abs_bf16x2(hi[u].z, hi[u].w))) & 0x7fff7fffu;
+#pragma unroll
+            for (int m = 1; m < 8; m <<= 1) pk = max_bf16x2(pk, __shfl_xor_sync(0xffffffffu, pk, m));
+            if (slot[u] < 0) continue;
+            const uint32_t code = ue8m0_code(fmaxf(bf16_lo(pk), bf16_hi(pk)));
+            int64_t block, in_block;
+            split_slot(slot[u], p.block_size, p.bs_shift, &block, &in_block);
+            uint8_t* blk = p.cache + block * p.block_stride;
+            uint8_t* dst = blk + in_block * 128 + 8 * sub;
+            st_global8(dst, quant8_pow2(lo[u], code));
+            st_global8(dst + 64, quant8_pow2(hi[u], code));
+            if (sub == 0) reinterpret_cast<float*>(blk + p.block_size * 128)[in_block] = __uint_as_float(code << 23);
+            continue;
+        }
         float x[8], y[8];
         unpack8_any<FP16>(lo[u], x);
         unpack8_any<FP16>(hi[u], y);
@@ -184,7 +207,7 @@ __global__ void __launch_bounds__(WARPS * 32) indexer_k_quant_128_kernel(const I
         uint8_t* blk = p.cache + block * p.block_stride;
         uint8_t* dst = blk + in_block * 128 + 8 * sub;
         float s;
-        if (p.ue8m0) {
+        if (UE8M0) {
             const uint32_t code = ue8m0_code(amax);
             s = __uint_as_float(code << 23);
             const float inv = __uint_as_float((254u - code) << 23);
@@ -227,10 +250,15 @@ cudaError_t launch_indexer_k_quant(const void* k, int64_t k_stride, int is_fp16,
     const int64_t grid = (num_tokens + WARPS - 1) / WARPS;
     if (grid > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
     if (p.vec_ok && head_dim == 128 && quant_block == 128) {
-        constexpr int W = 4, U = 2;
+#ifndef DSV4_INDEXER_K_U
+#define DSV4_INDEXER_K_U 2  // passes of 4 tokens a warp keeps in flight
+#endif
+        constexpr int W = 4, U = DSV4_INDEXER_K_U;
         const unsigned g128 = static_cast<unsigned>((num_tokens + W * U * 4 - 1) / (W * U * 4));
-        if (is_fp16) indexer_k_quant_128_kernel<W, U, true><<<g128, W * 32, 0, stream>>>(p);
-        else indexer_k_quant_128_kernel<W, U, false><<<g128, W * 32, 0, stream>>>(p);
+        if (is_fp16) ue8m0 ? indexer_k_quant_128_kernel<W, U, true, true><<<g128, W * 32, 0, stream>>>(p)
+                           : indexer_k_quant_128_kernel<W, U, true, false><<<g128, W * 32, 0, stream>>>(p);
+        else ue8m0 ? indexer_k_quant_128_kernel<W, U, false, true><<<g128, W * 32, 0, stream>>>(p)
+                   : indexer_k_quant_128_kernel<W, U, false, false><<<g128, W * 32, 0, stream>>>(p);
         count_launch();
         return cudaGetLastError();
     }

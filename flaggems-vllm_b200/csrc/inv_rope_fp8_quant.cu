@@ -33,6 +33,9 @@ struct InvRopeParams {
 // every lane rotates exactly one pair with a cosine and sine it loaded once for the whole task.  The four
 // quantisation groups of 128 are: A lanes 0-15, A lanes 16-31, B lanes 0-15, and B lanes 16-23 together with T.
 constexpr int kHeadsPerTask = 16;
+#ifndef DSV4_INVROPE_FP32_CTAS
+#define DSV4_INVROPE_FP32_CTAS 9  // CTAs per SM of the fp32-scale instantiation (fixes its register budget)
+#endif
 
 // FASTDIV (fp32-scale mode only): see ScaleDivider.
 template <int WARPS, bool PACKED, bool FASTDIV, int U, int MIN_CTAS>
@@ -117,11 +120,14 @@ __global__ void __launch_bounds__(WARPS * 32, MIN_CTAS) inv_rope_fp8_quant_kerne
                 const uint32_t word = mine | (__shfl_xor_sync(0xffffffffu, mine, 16) << 8);
                 if (lane == 0) *reinterpret_cast<uint32_t*>(scale_row + head_in_group * p.padded_tokens * 4) = word;
             } else {
+                // the three-instruction form of the fast division for every scale: measured here, a warp-uniform choice
+                // between it and the two-instruction form was no faster (296 us against 294 us on 1 Mi rows)
                 constexpr int kDivision = FASTDIV ? kDivideFast : kDivideIeee;
-                st_global8(out + 8 * lane, quant8_by<kDivision>(a[u], sa));
-                if (lane < kFirstRopeLane) st_global8(out + 256 + 8 * lane, quant8_by<kDivision>(b[u], sb));
-                const ScaleDivider<kDivision> by3(s3);
-                *reinterpret_cast<uint16_t*>(out + kNopeDim + 2 * lane) = static_cast<uint16_t>(pack_e4m3x4(by3(te), by3(to), 0.f, 0.f));
+                const ScaleDivider<kDivision> by_a(sa), by_b(sb), by_3(s3);
+                st_global8(out + 8 * lane, quant8_by<kDivision, false>(a[u], by_a));
+                if (lane < kFirstRopeLane) st_global8(out + 256 + 8 * lane, quant8_by<kDivision, false>(b[u], by_b));
+                *reinterpret_cast<uint16_t*>(out + kNopeDim + 2 * lane) = static_cast<uint16_t>(
+                    pack_e4m3x4(by_3.template quotient<false>(te), by_3.template quotient<false>(to), 0.f, 0.f));
                 if ((lane & 15) == 0) {
                     const int k = head_in_group * 4 + (lane >> 4);
                     *reinterpret_cast<float*>(scale_row + k * p.padded_tokens * 4) = sa;
@@ -158,9 +164,9 @@ cudaError_t launch_inv_rope_fp8_quant(const void* o, int64_t o_stride_token, int
     const unsigned g = static_cast<unsigned>(grid);
     const uint32_t tpt = static_cast<uint32_t>(tasks_per_token);
     // Heads in flight per warp (2) and CTAs per SM, measured on 1 Mi rows: UE8M0 mode 10 CTAs (48 registers) 268 us
-    // against 280 us at 8; fp32-scale mode 9 CTAs (56 registers) 315 us against 322 us at 8 and 339 us at 10.
+    // against 280 us at 8; fp32-scale mode 9 CTAs (56 registers) 294 us, the same at 10, 306 us at 8.
     if (packed) inv_rope_fp8_quant_kernel<WARPS, true, false, 2, 10><<<g, WARPS * 32, 0, stream>>>(p, tpt, tpt_mul, tpt_shift);
-    else if (eps == 1e-10f) inv_rope_fp8_quant_kernel<WARPS, false, true, 2, 9><<<g, WARPS * 32, 0, stream>>>(p, tpt, tpt_mul, tpt_shift);
+    else if (eps == 1e-10f) inv_rope_fp8_quant_kernel<WARPS, false, true, 2, DSV4_INVROPE_FP32_CTAS><<<g, WARPS * 32, 0, stream>>>(p, tpt, tpt_mul, tpt_shift);
     else inv_rope_fp8_quant_kernel<WARPS, false, false, 2, 8><<<g, WARPS * 32, 0, stream>>>(p, tpt, tpt_mul, tpt_shift);
     count_launch();
     return cudaGetLastError();

@@ -28,7 +28,7 @@ __device__ __forceinline__ void let_next_kernel_start() { asm volatile("griddepc
 // it every warp fetches position and table row of its own rows straight into registers (lane i holds cosine i and
 // sine i): 256 more bytes from L2 per row, but no barrier and no shared-memory round trip in the dependent chain
 // position -> table row, which is what a launch of a few waves waits for.
-template <int RPW, int WARPS, int MIN_CTAS, bool CHECKED, bool PADDED, bool PDL = false, bool STAGED = true>
+template <int RPW, int WARPS, int MIN_CTAS, bool CHECKED, bool PADDED, int PDL = 0, bool STAGED = true>
 __global__ void __launch_bounds__(WARPS * 32, MIN_CTAS) prologue_rows_kernel(const PrologueParams p, const int64_t kv_ctas) {
     static_assert(STAGED || !CHECKED, "the range-checked build marks bad tokens in shared memory");
     constexpr int TILE = RPW * WARPS;
@@ -39,6 +39,11 @@ __global__ void __launch_bounds__(WARPS * 32, MIN_CTAS) prologue_rows_kernel(con
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
 
+    // PDL 2: programmatic dependent launch with ordinary stream semantics - nothing is read before the preceding kernel
+    // of the stream has finished; what overlaps with that kernel's tail is only this kernel's own launch.
+    // PDL 1: positions, slots and table rows are read first and only q, kv and the cache wait (the caller promises
+    // that the preceding kernel does not write the former).
+    if (PDL == 2) wait_for_preceding_kernel();
     if (static_cast<int64_t>(blockIdx.x) < kv_ctas) {
         // ---- latent KV: RoPE tail + UE8M0/e4m3 quantisation + scatter through slot_mapping
         const int64_t t = static_cast<int64_t>(blockIdx.x) * WARPS + warp;
@@ -59,7 +64,7 @@ __global__ void __launch_bounds__(WARPS * 32, MIN_CTAS) prologue_rows_kernel(con
             c = ld_readonly_f4(cs);
             s = ld_readonly_f4(cs + 32);
         }
-        if (PDL) wait_for_preceding_kernel();  // kv (and the cache) may still be written by it
+        if (PDL == 1) wait_for_preceding_kernel();  // kv (and the cache) may still be written by it
         const uint8_t* row = p.kv + t * kRowBytes;
         const uint4 a = ld_stream16(row + 16 * lane);
         const uint4 b = ld_stream16(row + 512 + 16 * lane);
@@ -141,7 +146,7 @@ __global__ void __launch_bounds__(WARPS * 32, MIN_CTAS) prologue_rows_kernel(con
             }
         }
     };
-    if (PDL) {
+    if (PDL == 1) {
         // the table rows first (they do not depend on the preceding kernel), q only once that kernel has finished
         if (STAGED) stage_cos_sin(); else fetch_cos_sin();
         wait_for_preceding_kernel();
@@ -151,6 +156,7 @@ __global__ void __launch_bounds__(WARPS * 32, MIN_CTAS) prologue_rows_kernel(con
         // every row load goes out first; the table rows are fetched while they fly
         issue_row_loads();
         if (STAGED) stage_cos_sin(); else fetch_cos_sin();
+        if (PDL) let_next_kernel_start();
     }
     if (STAGED) __syncthreads();
 
@@ -186,8 +192,10 @@ cudaError_t launch(const PrologueParams& p, bool checked, cudaStream_t stream) {
     if (checked) {
         prologue_rows_kernel<RPW, WARPS, MIN_CTAS, true, false><<<static_cast<unsigned>(grid), WARPS * 32, 0, stream>>>(p, kv_ctas);
     } else if (p.pdl) {
-        const auto kernel = p.table_staging ? prologue_rows_kernel<RPW, WARPS, MIN_CTAS, false, false, true, true>
-                                            : prologue_rows_kernel<RPW, WARPS, MIN_CTAS, false, false, true, false>;
+        const auto kernel = p.pdl == 2 ? (p.table_staging ? prologue_rows_kernel<RPW, WARPS, MIN_CTAS, false, false, 2, true>
+                                                          : prologue_rows_kernel<RPW, WARPS, MIN_CTAS, false, false, 2, false>)
+                                       : (p.table_staging ? prologue_rows_kernel<RPW, WARPS, MIN_CTAS, false, false, 1, true>
+                                                          : prologue_rows_kernel<RPW, WARPS, MIN_CTAS, false, false, 1, false>);
         cudaLaunchConfig_t config = {};
         config.gridDim = dim3(static_cast<unsigned>(grid)), config.blockDim = dim3(WARPS * 32), config.stream = stream;
         cudaLaunchAttribute attribute[1];
@@ -199,7 +207,7 @@ cudaError_t launch(const PrologueParams& p, bool checked, cudaStream_t stream) {
     } else if (p.table_staging) {
         prologue_rows_kernel<RPW, WARPS, MIN_CTAS, false, false><<<static_cast<unsigned>(grid), WARPS * 32, 0, stream>>>(p, kv_ctas);
     } else {
-        prologue_rows_kernel<RPW, WARPS, MIN_CTAS, false, false, false, false><<<static_cast<unsigned>(grid), WARPS * 32, 0, stream>>>(p, kv_ctas);
+        prologue_rows_kernel<RPW, WARPS, MIN_CTAS, false, false, 0, false><<<static_cast<unsigned>(grid), WARPS * 32, 0, stream>>>(p, kv_ctas);
     }
     count_launch();
     return cudaGetLastError();

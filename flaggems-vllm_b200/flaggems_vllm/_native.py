@@ -147,9 +147,10 @@ def set_variant(variant: int) -> int:
     return prev
 
 
-def set_pdl(enabled: bool) -> bool:
-    """Programmatic dependent launch of the prologue (see dsv4_set_pdl); returns the previous setting."""
-    return bool(lib().dsv4_set_pdl(1 if enabled else 0))
+def set_pdl(mode) -> int:
+    """Programmatic dependent launch of the prologue (see dsv4_set_pdl): 0 / False off, 1 / True with early index
+    reads, 2 with ordinary stream semantics; returns the previous mode."""
+    return int(lib().dsv4_set_pdl(int(mode)))
 
 
 def set_table_staging(mode: int) -> int:

@@ -60,7 +60,7 @@ def lib() -> ctypes.CDLL:
         L.dsv4_oracle_group_quant_fp8.restype = i32
         L.dsv4_oracle_indexer_q_rope_quant.argtypes = [vp, vp, vp, i64, vp, f32, f32, i64, i64, i64, i32, vp, vp, vp]
         L.dsv4_oracle_indexer_q_rope_quant.restype = i32
-        L.dsv4_oracle_check_division_shortcut.argtypes = [f32, vp, vp]
+        L.dsv4_oracle_check_division_shortcut.argtypes = [f32, i32, i32, vp, vp]
         L.dsv4_oracle_check_division_shortcut.restype = i64
         L.dsv4_oracle_version.restype = ctypes.c_char_p
         _lib = L
@@ -264,10 +264,12 @@ def indexer_q_rope_quant(positions, index_q, cos_sin_cache, weights, softmax_sca
     return out, scales, w_out
 
 
-def check_division_shortcut(eps: float = 1e-10):
-    """(pairs examined, e4m3 byte mismatches, fp32 value mismatches) of the reciprocal-and-correct division."""
+def check_division_shortcut(eps: float = 1e-10, form: int = 3, y_ulps: int = 0):
+    """(pairs examined, e4m3 byte mismatches, fp32 value mismatches) of the CUDA quantisers' division shortcut:
+    form 2 = two-term reciprocal (scales up to 2^100), form 3 = product with one correction (any scale); `y_ulps`
+    moves the reciprocal off RN(1/scale) by that many ulps (the device's reciprocal is within one)."""
     b, v = ctypes.c_int64(0), ctypes.c_int64(0)
-    n = lib().dsv4_oracle_check_division_shortcut(float(eps), ctypes.byref(b), ctypes.byref(v))
+    n = lib().dsv4_oracle_check_division_shortcut(float(eps), int(form), int(y_ulps), ctypes.byref(b), ctypes.byref(v))
     return int(n), int(b.value), int(v.value)
 
 

@@ -673,18 +673,21 @@ int dsv4_oracle_indexer_q_rope_quant(const int64_t* positions, const uint16_t* q
 }
 
 /*
- * Exhaustive check of the division shortcut the CUDA quantisers use when their scales are not powers of two:
- * once per group y = RN(1/s) and y_lo = RN(fma(-s, y, 1) * y), then per value q = fma(x, y, RN(x * y_lo)); scales
- * outside [2^-100, 2^100] are divided instead (y_lo would be subnormal there).
- * For every non-negative finite bf16 amax, s = RN(max(amax, eps) * RN(1/448)), and every bf16 x with
- * 0 <= x <= amax, counts the pairs whose e4m3 byte differs from that of the IEEE quotient RN(x/s)
- * (`byte_mismatches`) and, for information, those whose fp32 value differs (`value_mismatches`; they are
- * quotients so far below the group maximum that their byte is zero either way).
- * Negative x behave symmetrically.  Returns the number of pairs examined.
+ * Exhaustive check of the division shortcuts the CUDA quantisers use when their scales are not powers of two.
+ * Once per group they form y within one ulp of RN(1/s) (approximate reciprocal + one Newton step) and
+ * y_lo = RN(fma(-s, y, 1) * y); per value then either
+ *   form 2 ("two-term"):   q = fma(x, y, RN(x * y_lo)), used for s <= 2^100 only (y_lo would be subnormal beyond), or
+ *   form 3 ("corrected"):  q0 = RN(x * y), r = fma(-s, q0, x), q = fma(r, y, q0), used for any s.
+ * For every non-negative finite bf16 amax, s = RN(max(amax, eps) * RN(1/448)), every bf16 x with 0 <= x <= amax, and
+ * y = RN(1/s) moved by `y_ulps` (-1, 0 or +1: the three values the device's y can take), counts the pairs whose
+ * e4m3 byte differs from that of the IEEE quotient RN(x/s) (`byte_mismatches`) and, for information, those whose fp32
+ * value differs (`value_mismatches`; for form 2 these are quotients so far below the group maximum that their byte is
+ * zero either way).  Pairs outside a form's range are not counted.  Negative x behave symmetrically.
+ * Returns the number of pairs examined.
  */
 __attribute__((target("fma"))) static inline float fma_hw(float a, float b, float c) { return __builtin_fmaf(a, b, c); }
 
-int64_t dsv4_oracle_check_division_shortcut(float eps, int64_t* byte_mismatches, int64_t* value_mismatches) {
+int64_t dsv4_oracle_check_division_shortcut(float eps, int form, int y_ulps, int64_t* byte_mismatches, int64_t* value_mismatches) {
     int64_t pairs = 0, bytes = 0, values = 0;
     const float inv448 = (float)(1.0 / 448.0);
     const int have_fma = __builtin_cpu_supports("fma");
@@ -692,15 +695,25 @@ int64_t dsv4_oracle_check_division_shortcut(float eps, int64_t* byte_mismatches,
     for (int32_t ia = 0; ia < 0x7f80; ++ia) {
         float amax = bf16_bits_to_f32((uint16_t)ia);
         float s = (amax < eps ? eps : amax) * inv448;
+        if (form == 2 && !(s <= 0x1p100f)) continue;
         float y = 1.0f / s;
+        uint32_t y_bits;
+        memcpy(&y_bits, &y, 4);
+        y_bits += (uint32_t)y_ulps;
+        memcpy(&y, &y_bits, 4);
         float residual = have_fma ? fma_hw(-s, y, 1.0f) : fmaf(-s, y, 1.0f);
         float y_lo = residual * y;
-        const int fast = s >= 0x1p-100f && s <= 0x1p100f;
         for (int32_t ix = 0; ix <= ia; ++ix) {
             float x = bf16_bits_to_f32((uint16_t)ix);
-            float want = x / s;
-            float c = x * y_lo;
-            float q = !fast ? want : (have_fma ? fma_hw(x, y, c) : fmaf(x, y, c));
+            float want = x / s, q;
+            if (form == 2) {
+                float c = x * y_lo;
+                q = have_fma ? fma_hw(x, y, c) : fmaf(x, y, c);
+            } else {
+                float q0 = x * y;
+                float r = have_fma ? fma_hw(-s, q0, x) : fmaf(-s, q0, x);
+                q = have_fma ? fma_hw(r, y, q0) : fmaf(r, y, q0);
+            }
             pairs++;
             if (q != want) values++;
             float qc = q > 448.0f ? 448.0f : q, wc = want > 448.0f ? 448.0f : want;

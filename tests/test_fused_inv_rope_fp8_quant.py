@@ -40,15 +40,20 @@ def test_pow2_scale_bit_derivation_equals_log_statement_for_every_bf16_amax():
     assert torch.equal(got, want)
 
 
-def test_division_shortcut_never_changes_a_byte():
-    """fp32-scale mode divides with a two-term reciprocal (two instructions per value) instead of an IEEE
-    division.  Every reachable (scale, value) pair for bf16 inputs and the reference's eps: no e4m3 byte differs."""
-    pairs, byte_mismatches, _ = c_oracle.check_division_shortcut(1e-10)
-    assert pairs > 5e8 and byte_mismatches == 0
+@pytest.mark.parametrize("form", [2, 3])
+@pytest.mark.parametrize("y_ulps", [-1, 0, 1])
+def test_division_shortcut_never_changes_a_byte(form, y_ulps):
+    """fp32-scale mode forms x / scale from a refined reciprocal - two instructions per value (form 2, scales up to
+    2^100) or three (form 3, any scale) - instead of an IEEE division.  Every reachable (scale, value) pair for bf16
+    inputs and the reference's eps, for each value the device's reciprocal can take (within one ulp of the correctly
+    rounded one): no e4m3 byte differs."""
+    enough = 4.5e8 if form == 2 else 5.3e8  # form 2 leaves out the group maxima above 2^108
+    pairs, byte_mismatches, _ = c_oracle.check_division_shortcut(1e-10, form, y_ulps)
+    assert pairs > enough and byte_mismatches == 0
     # per_token_group_quant_fp8 uses the same shortcut with eps rounded to bf16 (its statement clamps a bf16 tensor)
     eps_bf16 = float(torch.tensor(1e-10).to(torch.bfloat16))
-    pairs, byte_mismatches, _ = c_oracle.check_division_shortcut(eps_bf16)
-    assert pairs > 5e8 and byte_mismatches == 0
+    pairs, byte_mismatches, _ = c_oracle.check_division_shortcut(eps_bf16, form, y_ulps)
+    assert pairs > enough and byte_mismatches == 0
 
 
 @pytest.mark.parametrize("packed", [False, True])

@@ -509,23 +509,33 @@ def test_kernel_reproduces_the_upstream_flash_mla_cache_builder():
             _native.set_variant(previous)
 
 
-def test_programmatic_dependent_launch_gives_the_same_result():
-    """With dsv4_set_pdl(1) the kernel may start before the kernel in front of it has finished and waits for it only
-    before touching q / kv / cache: a producer of q and kv directly in front of it, eager and replayed from a CUDA graph,
-    must give the bytes of the ordinary launch."""
-    q0, kv0, kc0, slots, pos, cs = random_case(300, 16, 64, 12, seed=77)
+@pytest.mark.parametrize("mode", [1, 2])
+def test_programmatic_dependent_launch_gives_the_same_result(mode):
+    """In launch modes 1 and 2 (dsv4_set_pdl) the kernel may start before the kernel in front of it has finished.  Mode 2,
+    the default, reads nothing before that kernel is done: every input, positions and slots included, may come from the
+    kernel right in front.  Mode 1 waits only before touching q / kv / cache.  A producer directly in front of the
+    prologue, eager and replayed from a CUDA graph, must give the bytes of a plain launch (mode 0)."""
+    q0, kv0, kc0, slots0, pos0, cs = random_case(300, 16, 64, 12, seed=77)
     want_q, want_kv, want_kc = q0.clone(), kv0.clone(), kc0.clone()
-    op(want_q, want_kv, want_kc, slots, pos, cs, 1e-6, 64)
-    q_ref, kc_ref = oracle_of(q0, kv0, kc0, slots, pos, cs, 1e-6, 64)
-    assert torch.equal(want_kc.cpu(), kc_ref)
-    previous = _native.set_pdl(True)
+    previous = _native.set_pdl(0)
     try:
+        op(want_q, want_kv, want_kc, slots0, pos0, cs, 1e-6, 64)
+        q_ref, kc_ref = oracle_of(q0, kv0, kc0, slots0, pos0, cs, 1e-6, 64)
+        assert torch.equal(want_kc.cpu(), kc_ref)
+        assert _native.set_pdl(mode) == 0
         q, kv, kc = torch.empty_like(q0), torch.empty_like(kv0), kc0.clone()
+        slots, pos = (torch.zeros_like(slots0), torch.zeros_like(pos0)) if mode == 2 else (slots0, pos0)
 
         def produce_then_consume():
-            q.copy_(q0)  # the producers of q and kv are the kernels right in front of the prologue
+            q.copy_(q0)  # the producers of the inputs are the kernels right in front of the prologue
             kv.copy_(kv0)
+            if mode == 2:
+                slots.copy_(slots0)
+                pos.copy_(pos0)
             op(q, kv, kc, slots, pos, cs, 1e-6, 64)
+            if mode == 2:  # and the kernel behind it may overwrite them at once
+                slots.zero_()
+                pos.zero_()
 
         produce_then_consume()
         torch.cuda.synchronize()
