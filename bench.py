@@ -31,13 +31,23 @@ sys.path[:0] = [str(ROOT / "flaggems-vllm_b200"), str(ROOT)]
 import torch  # noqa: E402
 
 METRIC = "fused qnorm/RoPE/FP8-insert tokens/s"
-HBM_FALLBACK_GBS = 6650.0  # earlier measurement on this pool, used only if MEASURED_PEAKS.json is absent
+HBM_FALLBACK_GBS = 6650.0  # an earlier B200 copy measurement, used only if MEASURED_PEAKS.json is absent
 NOMINAL_HBM_GBS = 8000.0
 CPU_SAMPLE_TOKENS = 2048
-# DRAM traffic per token (dram__bytes_read.sum + dram__bytes_write.sum) of one ncu capture of the
-# kernel on the 8192-token prefill workload (profiles/prologue_rows_kernel_prefill.md), scaled by
-# tokens for the reported launch: traffic grows in proportion to tokens (no reuse across tokens).
-NCU_DRAM_BYTES_PER_TOKEN = 257123  # (1.084464 + 1.021883) GB over 8192 tokens x 128 heads, see profiles/
+# DRAM traffic per token (dram__bytes_read.sum + dram__bytes_write.sum) of one ncu capture of the kernel, scaled by
+# the tokens of the reported launch: traffic grows in proportion to tokens (no byte is shared between tokens).  The
+# capture is of a smaller workload than the timed one because a profiler replays each launch about 40 times.
+# To refresh after a kernel change: the --set full command in TRAFFIC_SOURCE["command"], then read both counters.
+NCU_DRAM_BYTES_PER_TOKEN = 257191  # (1.084411 + 1.022503) GB over 8192 tokens x 128 heads
+TRAFFIC_SOURCE = {
+    "kind": "one ncu capture, scaled by tokens; not measured in this run",
+    "kernel": "prologue_rows_kernel<2 rows/warp, 4 warps, 10 CTAs/SM, unchecked, in place, launch mode 2, shared-memory table staging>",
+    "workload": "prefill: 8192 tokens x 128 heads (1 GiB of q, 2.2 GB on the device)",
+    "captured": "2026-11-25, 1 x B200, CUDA 12.9, ncu --set full --clock-control none, second of two captured launches",
+    "command": "ncu --set full --clock-control none -k regex:prologue_rows_kernel -s 3 -c 2 python bench.py --workload prefill "
+               "--steps 2 --warmup 3 --no-e2e --no-cpu-baseline --no-extra",
+    "dram_bytes_read": 1084411000, "dram_bytes_write": 1022503000, "tokens": 8192,
+}
 
 
 def parse_args():
@@ -55,6 +65,9 @@ def parse_args():
                     help="time the shapes of the reference's own benchmark for this operator; prints JSON and exits")
     ap.add_argument("--siblings-only", action="store_true",
                     help="time only the sibling operators (used to profile them); prints their JSON and exits")
+    ap.add_argument("--sibling", default=None,
+                    help="with --siblings-only: only the operators whose name contains this string, e.g. "
+                         "'fused_inv_rope_fp8_quant[fp32' (one operator and its tensors: the form to run under a profiler)")
     return ap.parse_args()
 
 
@@ -292,31 +305,61 @@ def hbm_ceiling(native, nbytes: int, stream):
     return out
 
 
-def sibling_ops(steps, warmup):
+def sibling_ops(steps, warmup, only=None):
     """The operators either side of the prologue (the step before, the cache reader, the attention epilogue, the sparse-indexer
     prologue), 8192 tokens x 128 heads,
-    device-resident inputs larger than L2, CUDA-event time; GB/s = algorithmic bytes / time."""
+    device-resident inputs larger than L2, CUDA-event time; GB/s = algorithmic bytes / time.
+    `only`: time just the operators whose name contains this string, and allocate nothing for the others (the form to
+    put under a profiler: one operator, at most a few GB on the device)."""
     import flaggems_vllm
+    from flaggems_vllm.testing.workloads import cos_sin_table
 
     dev, n, h = "cuda", 8192, 128
     stream = torch.cuda.current_stream()
     g = torch.Generator(device=dev).manual_seed(0)
     out = {}
+    cs = cos_sin_table(65536, device=dev)
+
+    def want(*names):
+        return only is None or any(only in name or name in only for name in names)
+
+    if want("fused_inv_rope_fp8_quant"):
+        _sibling_epilogue(flaggems_vllm, out, steps, warmup, stream, g, cs, n, h, only)
+    if want("fused_q_kv_rmsnorm"):
+        _sibling_rmsnorm(flaggems_vllm, out, steps, warmup, stream, g)
+    if want("dequantize_and_gather_k_cache"):
+        _sibling_gather(flaggems_vllm, out, steps, warmup, stream, g)
+    if want("fused_indexer_q_rope_quant"):
+        _sibling_indexer_q(flaggems_vllm, out, steps, warmup, stream, g, cs, only)
+    if want("indexer_k_quant_and_cache", "cp_gather_indexer_k_quant_cache"):
+        _sibling_indexer_k(flaggems_vllm, out, steps, warmup, stream, g, only)
+    if want("compute_global_topk_indices_and_lens", "combine_topk_swa_indices"):
+        _sibling_index_ops(flaggems_vllm, out, steps, warmup, stream, g, only)
+    if want("per_token_group_quant_fp8"):
+        _sibling_group_quant(flaggems_vllm, out, steps, warmup, stream, g, only)
+    if want("top_k_per_row_decode"):
+        _sibling_topk(flaggems_vllm, out, steps, warmup, stream, g)
+    return out
+
+
+def _sibling_epilogue(flaggems_vllm, out, steps, warmup, stream, g, cs, n, h, only):
     # epilogue: read 1 KiB, write 512 B + 4 fp32 scales per (token, head) row
+    dev = "cuda"
     o = torch.randn(n, h, 512, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
     pos = torch.randint(0, 65536, (n,), generator=g, device=dev, dtype=torch.int64)
-    from flaggems_vllm.testing.workloads import cos_sin_table
-
-    cs = cos_sin_table(65536, device=dev)
     for packed, key, scale_bytes in ((True, "fused_inv_rope_fp8_quant[ue8m0 scales]", 4), (False, "fused_inv_rope_fp8_quant[fp32 scales]", 16)):
+        if only is not None and only not in key:
+            continue
         secs = time_steps(lambda: flaggems_vllm.fused_inv_rope_fp8_quant(o, pos, cs, 8, 16, tma_aligned_scales=packed), steps,
                           warmup, stream, torch.cuda.synchronize)
         nbytes = n * h * (1024 + 512 + scale_bytes) + n * 264
         out[key] = {"rows": n * h, "us_per_launch": secs / steps * 1e6, "hbm_gbs": nbytes * steps / secs / 1e9,
                     "note": "includes torch.empty of the two outputs per call"}
-    del o
+
+
+def _sibling_rmsnorm(flaggems_vllm, out, steps, warmup, stream, g):
     # step before: weighted RMSNorm of [N,1536] and [N,512]; 64 Ki tokens so the working set exceeds L2
-    nt = 65536
+    dev, nt = "cuda", 65536
     qr = torch.randn(nt, 1536, generator=g, device=dev).to(torch.bfloat16)
     kv = torch.randn(nt, 512, generator=g, device=dev).to(torch.bfloat16)
     qw, kw = torch.ones(1536, device=dev, dtype=torch.bfloat16), torch.ones(512, device=dev, dtype=torch.bfloat16)
@@ -324,9 +367,11 @@ def sibling_ops(steps, warmup):
     out["fused_q_kv_rmsnorm"] = {"tokens": nt, "us_per_launch": secs / steps * 1e6,
                                  "hbm_gbs": nt * 2048 * 2 * 2 * steps / secs / 1e9,
                                  "note": "includes torch.empty_like of the two outputs per call"}
-    del qr, kv
+
+
+def _sibling_gather(flaggems_vllm, out, steps, warmup, stream, g):
     # reader: 16 requests x 16384 tokens gathered through a block table; 584 B read, 1 KiB written per token
-    reqs, seq, bs = 16, 16384, 64
+    dev, reqs, seq, bs = "cuda", 16, 16384, 64
     blocks = reqs * seq // bs
     cache = torch.randint(0, 256, (blocks, bs * 584), generator=g, device=dev, dtype=torch.uint8)
     table = torch.randperm(blocks, generator=g, device=dev).to(torch.int32).view(reqs, seq // bs).contiguous()
@@ -336,19 +381,25 @@ def sibling_ops(steps, warmup):
                       torch.cuda.synchronize)
     out["dequantize_and_gather_k_cache"] = {"tokens": reqs * seq, "us_per_launch": secs / steps * 1e6,
                                             "hbm_gbs": reqs * seq * (584 + 1024) * steps / secs / 1e9}
-    del cache, dst
+
+
+def _sibling_indexer_q(flaggems_vllm, out, steps, warmup, stream, g, cs, only):
     # sparse-indexer siblings: 64 Ki tokens, 64 index heads x 128 (q), one 128-wide key per token (k)
-    nt, ih = 65536, 64
+    dev, nt, ih = "cuda", 65536, 64
     iq = torch.randn(nt, ih, 128, generator=g, device=dev).to(torch.bfloat16)
     ipos = torch.randint(0, 65536, (nt,), generator=g, device=dev, dtype=torch.int64)
     iw = torch.randn(nt, ih, generator=g, device=dev).to(torch.bfloat16)
     for fp4, key, out_b in ((False, "fused_indexer_q_rope_quant[fp8]", 128), (True, "fused_indexer_q_rope_quant[mxfp4]", 68)):
+        if only is not None and only not in key:
+            continue
         secs = time_steps(lambda: flaggems_vllm.fused_indexer_q_rope_quant(ipos, iq, cs, iw, 0.088, 0.125, use_fp4=fp4), steps, warmup,
                           stream, torch.cuda.synchronize)
         out[key] = {"rows": nt * ih, "us_per_launch": secs / steps * 1e6, "hbm_gbs": nt * ih * (256 + out_b + 6) * steps / secs / 1e9,
                     "note": "includes torch.empty of the outputs per call"}
-    del iq
-    nk = 1 << 20
+
+
+def _sibling_indexer_k(flaggems_vllm, out, steps, warmup, stream, g, only):
+    dev, nk = "cuda", 1 << 20
     ik = torch.randn(nk, 128, generator=g, device=dev).to(torch.bfloat16)
     icache = torch.zeros(nk // 64, 64, 132, device=dev, dtype=torch.uint8)
     # slots as a prefill produces them (tokens fill randomly chosen blocks in order) and fully random slots
@@ -356,10 +407,14 @@ def sibling_ops(steps, warmup):
     order = torch.arange(nk, device=dev, dtype=torch.int64)
     for key, islots in (("indexer_k_quant_and_cache[block-contiguous slots]", (table[order // 64] * 64 + order % 64).contiguous()),
                         ("indexer_k_quant_and_cache[random slots]", torch.randperm(nk, generator=g, device=dev).to(torch.int64))):
+        if only is not None and only not in key:
+            continue
         secs = time_steps(lambda: flaggems_vllm.indexer_k_quant_and_cache(ik, icache, islots, 128, "ue8m0"), steps, warmup, stream,
                           torch.cuda.synchronize)
         out[key] = {"tokens": nk, "us_per_launch": secs / steps * 1e6, "hbm_gbs": nk * (256 + 132 + 8) * steps / secs / 1e9}
     del ik
+    if only is not None and only not in "cp_gather_indexer_k_quant_cache" and "cp_gather_indexer_k_quant_cache" not in only:
+        return
     # reader of that cache: 16 requests x 64 Ki tokens gathered into token order (132 B read + 132 B written per token)
     reqs = 16
     cu = (torch.arange(reqs + 1, device=dev, dtype=torch.int32) * (nk // reqs)).contiguous()
@@ -369,19 +424,15 @@ def sibling_ops(steps, warmup):
     secs = time_steps(lambda: flaggems_vllm.cp_gather_indexer_k_quant_cache(icache, gk, gs, btable, cu), steps, warmup, stream,
                       torch.cuda.synchronize)
     out["cp_gather_indexer_k_quant_cache"] = {"tokens": nk, "us_per_launch": secs / steps * 1e6, "hbm_gbs": nk * 264 * steps / secs / 1e9}
-    del icache, gk, gs
+
+
+def _sibling_index_ops(flaggems_vllm, out, steps, warmup, stream, g, only):
     # index bookkeeping of the sparse attention: 32768 tokens, 16 requests
-    nt, reqs, tk = 32768, 16, 2048
-    local = torch.randint(0, 65536, (nt, tk), generator=g, device=dev, dtype=torch.int32)
-    local[torch.rand(nt, tk, generator=g, device=dev) < 0.1] = -1
-    t2r = torch.randint(0, reqs, (nt,), generator=g, device=dev, dtype=torch.int32)
-    btable = torch.randperm(reqs * 1024, generator=g, device=dev).to(torch.int32).view(reqs, 1024).contiguous()
-    secs = time_steps(lambda: flaggems_vllm.compute_global_topk_indices_and_lens(local, t2r, btable, 64), steps, warmup, stream,
-                      torch.cuda.synchronize)
-    out["compute_global_topk_indices_and_lens"] = {"tokens": nt, "topk": tk, "us_per_launch": secs / steps * 1e6,
-                                                   "hbm_gbs": nt * (8 * tk + 8) * steps / secs / 1e9,
-                                                   "note": "includes torch.empty of the outputs per call"}
-    del local
+    dev, nt, reqs, tk = "cuda", 32768, 16, 2048
+    if only is None or only in "compute_global_topk_indices_and_lens" or "compute_global_topk_indices_and_lens" in only:
+        _sibling_global_topk(flaggems_vllm, out, steps, warmup, stream, g, dev, nt, reqs, tk)
+    if only is not None and only not in "combine_topk_swa_indices" and "combine_topk_swa_indices" not in only:
+        return
     tk, window = 512, 128
     tki = torch.randint(0, 8192, (nt, tk), generator=g, device=dev, dtype=torch.int32)
     qsl = (torch.arange(reqs + 1, device=dev, dtype=torch.int32) * (nt // reqs)).contiguous()
@@ -392,15 +443,35 @@ def sibling_ops(steps, warmup):
     out["combine_topk_swa_indices"] = {"tokens": nt, "topk": tk, "window": window, "us_per_launch": secs / steps * 1e6,
                                        "hbm_gbs": nt * (4 * tk + 4 * (tk + window) + 4) * steps / secs / 1e9,
                                        "note": "includes torch.empty of the outputs per call; positions 6144-8191, so every row has 512 + 128 entries"}
-    del tki
+
+
+def _sibling_global_topk(flaggems_vllm, out, steps, warmup, stream, g, dev, nt, reqs, tk):
+    local = torch.randint(0, 65536, (nt, tk), generator=g, device=dev, dtype=torch.int32)
+    local[torch.rand(nt, tk, generator=g, device=dev) < 0.1] = -1
+    t2r = torch.randint(0, reqs, (nt,), generator=g, device=dev, dtype=torch.int32)
+    btable = torch.randperm(reqs * 1024, generator=g, device=dev).to(torch.int32).view(reqs, 1024).contiguous()
+    secs = time_steps(lambda: flaggems_vllm.compute_global_topk_indices_and_lens(local, t2r, btable, 64), steps, warmup, stream,
+                      torch.cuda.synchronize)
+    out["compute_global_topk_indices_and_lens"] = {"tokens": nt, "topk": tk, "us_per_launch": secs / steps * 1e6,
+                                                   "hbm_gbs": nt * (8 * tk + 8) * steps / secs / 1e9,
+                                                   "note": "includes torch.empty of the outputs per call"}
+
+
+def _sibling_group_quant(flaggems_vllm, out, steps, warmup, stream, g, only):
     # activation quantiser in front of the FP8 projections: 32768 tokens x 7168, groups of 128
+    dev = "cuda"
     xa = torch.randn(32768, 7168, generator=g, device=dev).to(torch.bfloat16)
     for ue8m0, key in ((True, "per_token_group_quant_fp8[ue8m0 scales]"), (False, "per_token_group_quant_fp8[fp32 scales]")):
+        if only is not None and only not in key:
+            continue
         secs = time_steps(lambda: flaggems_vllm.per_token_group_quant_fp8(xa, 128, scale_ue8m0=ue8m0), steps, warmup, stream, torch.cuda.synchronize)
         out[key] = {"tokens": 32768, "columns": 7168, "us_per_launch": secs / steps * 1e6,
                     "hbm_gbs": xa.numel() * (2 + 1 + 4 / 128) * steps / secs / 1e9, "note": "includes torch.empty of the two outputs per call"}
-    del xa
+
+
+def _sibling_topk(flaggems_vllm, out, steps, warmup, stream, g):
     # top-k selection over the indexer logits: one decode row, a decode batch, a prefill chunk (rotating inputs larger than L2)
+    dev = "cuda"
     try:
         import vllm._custom_ops  # noqa: F401  (loads torch.ops._C)
 
@@ -431,7 +502,6 @@ def sibling_ops(steps, warmup):
             entry["vllm_kernel_us_per_launch"] = time_steps(theirs, steps, warmup, stream, torch.cuda.synchronize) / steps * 1e6
         out[f"top_k_per_row_decode[{rows}x{vocab}, k={tk}]"] = entry
         del logits
-    return out
 
 
 def measure_e2e(flaggems_vllm, w, args, dev, stream, sync_all, tokens_all_ranks):
@@ -574,7 +644,8 @@ def upstream_shapes(op, reps: int = 20):
         return statistics.median(times)
 
     rows = []
-    for n in (1, 4, 17, 64, 1024, 2048, 8192, 32768, 65536, 98304, 131072):
+    # 256 tokens is not among the reference's shapes: it is the decode batch of this repository's benchmark configurations
+    for n in (1, 4, 17, 64, 256, 1024, 2048, 8192, 32768, 65536, 98304, 131072):
         for h in (64, 128):
             q = torch.empty(n, h, 512, dtype=torch.bfloat16, device=dev)
             for a in range(0, n, 8192):
@@ -676,6 +747,31 @@ def side_measurement(name, steps, warmup, op, native):
         csecs = time_steps(graph_probe.replay, replays, 2, stream, torch.cuda.synchronize)
         out["copy_probe_us_per_launch_cuda_graph"] = csecs / (replays * sets) * 1e6
         out["frac_of_copy_probe_same_size"] = out["copy_probe_us_per_launch_cuda_graph"] / out["us_per_launch_cuda_graph"]
+        out["frac_of_copy_probe_same_size_plain_launch"] = (out["copy_probe_us_per_launch_cuda_graph"] /
+                                                            out["us_per_launch_cuda_graph_plain_launch"])
+        # the library kernel of the same operator (vLLM's, out of place, nine arguments) over the same rotation
+        try:
+            import vllm._custom_ops  # noqa: F401
+
+            lib_kernel = torch.ops._C.fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert
+
+            def lib_fn():
+                i = state["i"] % sets
+                state["i"] += 1
+                lib_kernel(q_sets[i], kv_sets[i], w.k_cache, slot_sets[i], w.position_ids, w.cos_sin_cache, w.num_heads, w.eps, 64)
+
+            out["vllm_kernel_us_per_launch"] = time_steps(lib_fn, steps, warmup, stream, torch.cuda.synchronize) / steps * 1e6
+            side.wait_stream(stream)
+            with torch.cuda.stream(side):
+                graph_lib = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph_lib, stream=side):
+                    for _ in range(sets):
+                        lib_fn()
+            stream.wait_stream(side)
+            out["vllm_kernel_us_per_launch_cuda_graph"] = (time_steps(graph_lib.replay, replays, 2, stream, torch.cuda.synchronize)
+                                                           / (replays * sets) * 1e6)
+        except Exception as e:
+            out["vllm_kernel_error"] = str(e).splitlines()[0][:120]
     return out
 
 
@@ -706,8 +802,10 @@ def main():
     op = flaggems_vllm.fused_deepseek_v4_qnorm_rope_kv_rope_quant_insert
 
     if args.siblings_only:
-        print(json.dumps({"sibling_ops": sibling_ops(args.steps, args.warmup),
-                          "hbm_ceiling": hbm_ceiling(_native, 1 << 30, torch.cuda.current_stream(dev))}), flush=True)
+        out = {"sibling_ops": sibling_ops(args.steps, args.warmup, args.sibling)}
+        if args.sibling is None:
+            out["hbm_ceiling"] = hbm_ceiling(_native, 1 << 30, torch.cuda.current_stream(dev))
+        print(json.dumps(out), flush=True)
         return
     if args.upstream_shapes:
         print(json.dumps({"upstream_benchmark_shapes": upstream_shapes(op)}), flush=True)
@@ -762,7 +860,7 @@ def main():
         even_agg = sharding.aggregate(even_secs, w_even.num_tokens, w_even.algorithmic_bytes(), even_steps, status=_native.device_error(), device=dev)
         even = {"tokens_total": int(even_agg["tokens"]), "tokens_per_rank": w_even.num_tokens, "steps": even_steps,
                 "ms_per_step": even_agg["seconds"] / even_steps * 1e3, "value": float(even_agg["tokens"]) * even_steps / even_agg["seconds"],
-                "note": "same kernel and total token count, every rank 32768 tokens; the headline uses the uneven split BASELINE asks for"}
+                "note": "same kernel and total token count, every rank 32768 tokens; the headline uses the uneven seeded Dirichlet(5) split"}
         if not args.no_e2e:
             even_e2e = measure_e2e(flaggems_vllm, w_even, args, dev, stream, sync_all, float(even_agg["tokens"]))
             even["e2e"] = {k: even_e2e.get(k) for k in ("value", "unit", "ms_per_step", "h2d_bytes_per_step", "d2h_bytes_per_step",
@@ -793,7 +891,8 @@ def main():
         "tokens_per_s_sum_of_rank_rates": agg["sum_of_rank_rates"] * args.steps,
         "hbm_frac_of_nominal_8tbs": achieved / NOMINAL_HBM_GBS,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": traffic, "peak_source": f"{peak_kind} copy bandwidth",
+                     "traffic": traffic, "traffic_source": TRAFFIC_SOURCE if traffic is not None else None,
+                     "peak_source": f"{peak_kind} copy bandwidth",
                      "algorithmic_bytes_per_launch": int(largest_bytes),
                      "kernel_ms": secs_max / args.steps * 1e3, "kernel_ms_per_launch_rank0": launch_stats},
         "clocks": clocks, "gpu_launches": launches_total, "e2e": e2e, "even_shards": even,

@@ -32,6 +32,7 @@ struct IndexerQParams {
     int64_t num_tokens;
     int32_t num_heads;
     uint32_t heads_mul, heads_shift;
+    int32_t scales_word_aligned;  // fp4: every head's group of scale bytes starts on a 4-byte boundary
 };
 
 __device__ __forceinline__ float load_weight(const uint8_t* base, int64_t idx, int dtype) {
@@ -58,6 +59,29 @@ __device__ __forceinline__ uint32_t pack_e2m1x2(float lo, float hi) {
     uint32_t r;
     asm("{.reg .b8 t; cvt.rn.satfinite.e2m1x2.f32 t, %1, %2; cvt.u32.u8 %0, t;}" : "=r"(r) : "f"(hi), "f"(lo));
     return r;
+}
+
+// Four packed bf16 pairs -> one word of eight e2m1 codes (element 0 in bits 0-3), round to nearest even, saturating at +-6.
+__device__ __forceinline__ uint32_t pack_e2m1x8(const uint32_t (&w)[4]) {
+    uint32_t r;
+    asm("{.reg .b8 t0, t1, t2, t3;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 t0, %2, %1;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 t1, %4, %3;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 t2, %6, %5;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 t3, %8, %7;\n\t"
+        "mov.b32 %0, {t0, t1, t2, t3};}"
+        : "=r"(r)
+        : "f"(bf16_lo(w[0])), "f"(bf16_hi(w[0])), "f"(bf16_lo(w[1])), "f"(bf16_hi(w[1])), "f"(bf16_lo(w[2])), "f"(bf16_hi(w[2])),
+          "f"(bf16_lo(w[3])), "f"(bf16_hi(w[3])));
+    return r;
+}
+
+// Four packed bf16 pairs times 2^(127 - code): exact (a power-of-two factor only moves the exponent; products below the
+// bf16 range become zero with their sign, as their e2m1 codes would anyway).
+__device__ __forceinline__ void scale_pow2_bf16x2(const uint32_t (&v)[4], uint32_t code, uint32_t (&w)[4]) {
+    const uint32_t inv2 = ((254u - code) << 7) * 0x00010001u;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(w[j]) : "r"(v[j]), "r"(inv2));
 }
 
 template <int E>
@@ -272,64 +296,83 @@ __global__ void __launch_bounds__(WARPS * 32) indexer_q_rope_quant_token_kernel(
     }
     const uint8_t* q_tok = p.q + t * p.q_stride0 * 2 + 16 * sub;
     uint8_t* out_tok = p.out + t * p.out_stride0;
-    constexpr int U = 2;  // groups of four heads loaded before the first is used
-    for (int h0 = 0; h0 < p.num_heads; h0 += 4 * U) {
-        uint4 nope[U], rope[U];
+#ifndef DSV4_INDEXER_Q_U
+#define DSV4_INDEXER_Q_U 2
+#endif
+    constexpr int U = DSV4_INDEXER_Q_U;  // groups of four heads per pass
+    // Two passes are in flight: the loads of the next pass go out before the current one is worked on, so a warp
+    // always has rows on their way while it computes.
+    uint4 nope[U], rope[U], nope_next[U], rope_next[U];
+    const auto load_pass = [&](int h0, uint4 (&n)[U], uint4 (&r)[U]) {
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             const int h = h0 + 4 * u + which;
-            nope[u] = rope[u] = make_uint4(0u, 0u, 0u, 0u);
+            n[u] = r[u] = make_uint4(0u, 0u, 0u, 0u);
             if (h < p.num_heads) {
                 const uint8_t* row = q_tok + h * p.q_stride1 * 2;
-                nope[u] = ld_stream16(row);
-                rope[u] = ld_stream16(row + 128);
+                n[u] = ld_stream16(row);
+                r[u] = ld_stream16(row + 128);
             }
         }
+    };
+    load_pass(0, nope, rope);
+    for (int h0 = 0; h0 < p.num_heads; h0 += 4 * U) {
+        load_pass(h0 + 4 * U, nope_next, rope_next);  // past the last head: zeros, nothing is loaded
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             const int h = h0 + 4 * u + which;
             const bool live = h < p.num_heads;
-            float x[8], y[8];
-            unpack8(nope[u], x);
+            float y[8];
             unpack8(rope[u], y);
+            uint32_t rot[4];  // the rotated pairs, rounded to bf16 as the reference does before quantising
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const float e = y[2 * j], o = y[2 * j + 1];
-                // separately rounded products, then the bf16 round trip the reference makes before quantising
-                const uint32_t r = pack_bf16x2(__fsub_rn(__fmul_rn(e, c[j]), __fmul_rn(o, sn[j])),
-                                               __fadd_rn(__fmul_rn(o, c[j]), __fmul_rn(e, sn[j])));
-                y[2 * j] = bf16_lo(r), y[2 * j + 1] = bf16_hi(r);
+                // separately rounded products
+                rot[j] = pack_bf16x2(__fsub_rn(__fmul_rn(e, c[j]), __fmul_rn(o, sn[j])),
+                                     __fadd_rn(__fmul_rn(o, c[j]), __fmul_rn(e, sn[j])));
             }
-            float amax_n = 0.0f, amax_r = 0.0f;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) amax_n = fmaxf(amax_n, fabsf(x[i])), amax_r = fmaxf(amax_r, fabsf(y[i]));
             uint8_t* out = out_tok + h * p.out_stride1;
             float weight_factor = 1.0f;
             if (FP4) {
+                // everything on the packed words: |.| maxima of the un-rotated half (low 16 bits of `both`) and of the
+                // rotated half (high 16 bits) reduced together over the 4 lanes of a block of 32
+                const uint32_t plain[4] = {nope[u].x, nope[u].y, nope[u].z, nope[u].w};
+                const uint32_t pn = max_abs_bf16x2(max_abs_bf16x2(plain[0], plain[1]), max_abs_bf16x2(plain[2], plain[3]));
+                const uint32_t pr = max_abs_bf16x2(max_abs_bf16x2(rot[0], rot[1]), max_abs_bf16x2(rot[2], rot[3]));
+                uint32_t both = max_abs_bf16x2(__byte_perm(pn, pr, 0x5410), __byte_perm(pn, pr, 0x7632)) & 0x7fff7fffu;
 #pragma unroll
-                for (int m = 1; m < 4; m <<= 1) {
-                    amax_n = fmaxf(amax_n, __shfl_xor_sync(0xffffffffu, amax_n, m));
-                    amax_r = fmaxf(amax_r, __shfl_xor_sync(0xffffffffu, amax_r, m));
-                }
-                const uint32_t code[2] = {mxfp4_code(amax_n), mxfp4_code(amax_r)};
-                const float inv_n = __uint_as_float((254u - code[0]) << 23), inv_r = __uint_as_float((254u - code[1]) << 23);
-                uint32_t bn = 0, br = 0;
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    bn |= pack_e2m1x2(__fmul_rn(x[2 * j], inv_n), __fmul_rn(x[2 * j + 1], inv_n)) << (8 * j);
-                    br |= pack_e2m1x2(__fmul_rn(y[2 * j], inv_r), __fmul_rn(y[2 * j + 1], inv_r)) << (8 * j);
-                }
+                for (int m = 1; m < 4; m <<= 1) both = max_bf16x2(both, __shfl_xor_sync(0xffffffffu, both, m));
+                const uint32_t code_n = mxfp4_code(bf16_lo(both)), code_r = mxfp4_code(bf16_hi(both));
+                uint32_t wn[4], wr[4];
+                scale_pow2_bf16x2(plain, code_n, wn);
+                scale_pow2_bf16x2(rot, code_r, wr);
+                const uint32_t bn = pack_e2m1x8(wn), br = pack_e2m1x8(wr);
+                // the head's four scale bytes in one word: blocks (un-rotated 0-31, 32-63, rotated 0-31, 32-63)
+                const uint32_t mine = code_n | (code_r << 16);
+                const uint32_t other = __shfl_xor_sync(0xffffffffu, mine, 4);
                 if (live) {
                     *reinterpret_cast<uint32_t*>(out + 4 * sub) = bn;
                     *reinterpret_cast<uint32_t*>(out + 32 + 4 * sub) = br;
-                    if ((sub & 3) == 0) {
-                        uint8_t* sc = p.scales + t * p.scale_stride0 + h * p.scale_stride1 + (sub >> 2);
-                        sc[0] = static_cast<uint8_t>(code[0]);
-                        sc[2] = static_cast<uint8_t>(code[1]);
+                    if (sub == 0) {
+                        uint8_t* sc = p.scales + t * p.scale_stride0 + h * p.scale_stride1;
+                        const uint32_t word = (mine & 0xffu) | ((other & 0xffu) << 8) | (mine & 0xff0000u) | ((other & 0xff0000u) << 8);
+                        if (p.scales_word_aligned) {
+                            *reinterpret_cast<uint32_t*>(sc) = word;
+                        } else {
+                            sc[0] = static_cast<uint8_t>(word), sc[1] = static_cast<uint8_t>(word >> 8);
+                            sc[2] = static_cast<uint8_t>(word >> 16), sc[3] = static_cast<uint8_t>(word >> 24);
+                        }
                     }
                 }
             } else {
-                float amax = fmaxf(amax_n, amax_r);
+                float x[8];
+                unpack8(nope[u], x);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) y[2 * j] = bf16_lo(rot[j]), y[2 * j + 1] = bf16_hi(rot[j]);
+                float amax = 0.0f;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fmaxf(fabsf(x[i]), fabsf(y[i])));
 #pragma unroll
                 for (int m = 1; m < 8; m <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
                 const uint32_t code = ue8m0_code(amax);
@@ -348,6 +391,8 @@ __global__ void __launch_bounds__(WARPS * 32) indexer_q_rope_quant_token_kernel(
                 p.weights_out[t * p.weights_out_stride + h] = __fmul_rn(__fmul_rn(w, p.softmax_scale), p.head_scale);
             }
         }
+#pragma unroll
+        for (int u = 0; u < U; ++u) nope[u] = nope_next[u], rope[u] = rope_next[u];
     }
 }
 
@@ -380,6 +425,7 @@ cudaError_t launch_indexer_q_rope_quant(const int64_t* positions, const void* q,
     p.softmax_scale = softmax_scale, p.head_scale = head_scale, p.num_tokens = num_tokens, p.num_heads = num_heads;
     make_fast_divisor(static_cast<uint32_t>(num_heads), &p.heads_mul, &p.heads_shift);
     const auto addr = [](const void* q_) { return reinterpret_cast<uintptr_t>(q_); };
+    p.scales_word_aligned = addr(scales) % 4 == 0 && scale_stride0 % 4 == 0 && scale_stride1 % 4 == 0;
     const int nope = head_dim - rot_dim;
     const bool rows_shape = nope % 8 == 0 && rot_dim % 8 == 0 && addr(q) % 16 == 0 && q_stride0 % 8 == 0 && q_stride1 % 8 == 0 &&
                             addr(out) % 8 == 0 && out_stride0 % 8 == 0 && out_stride1 % 8 == 0;

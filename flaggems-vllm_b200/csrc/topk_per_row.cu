@@ -27,6 +27,8 @@
 #include <cooperative_groups.h>
 #include <cuda_fp16.h>
 
+#include <mutex>
+
 #include "dsv4_common.cuh"
 
 namespace dsv4 {
@@ -449,25 +451,30 @@ cudaError_t launch_topk_per_row(const float* logits, int64_t stride0, int64_t st
     constexpr size_t kDynamicBytes = sizeof(uint2) * kCandidateCap;
     // rows that fit into the buffer as a whole keep 4-byte keys only: more CTAs per SM for the many-short-rows case
     const size_t dynamic_bytes = vocab <= kCandidateCap ? sizeof(uint32_t) * static_cast<size_t>(vocab > 256 ? vocab : 256) : kDynamicBytes;
-    static bool configured[64] = {};  // per device; setting the attribute twice is harmless
+    // per-device set-up, once per device however many host threads make their first call at the same time
+    struct DeviceSetup {
+        std::once_flag once;
+        cudaError_t status = cudaSuccess;
+        int sms = 0;
+    };
+    static DeviceSetup setups[64];
     int dev = 0;
     cudaError_t err = cudaGetDevice(&dev);
     if (err != cudaSuccess) return err;
     if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
-    if (!configured[dev]) {
-        err = cudaFuncSetAttribute(topk_per_row_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kDynamicBytes));
-        if (err != cudaSuccess) return err;
-        err = cudaFuncSetAttribute(topk_per_row_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kDynamicBytes));
-        if (err != cudaSuccess) return err;
-        configured[dev] = true;
-    }
+    DeviceSetup& setup = setups[dev];
+    std::call_once(setup.once, [&]() {
+        setup.status = cudaFuncSetAttribute(topk_per_row_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kDynamicBytes));
+        if (setup.status == cudaSuccess)
+            setup.status = cudaFuncSetAttribute(topk_per_row_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kDynamicBytes));
+        if (setup.status == cudaSuccess) setup.status = cudaDeviceGetAttribute(&setup.sms, cudaDevAttrMultiProcessorCount, dev);
+    });
+    if (setup.status != cudaSuccess) return setup.status;
     // CTAs per row: long rows are shared by a cluster (shorter streaming time per row, no straggling rows at the
     // end of the grid); the candidates meet in the first CTA's shared memory.
     // Only while the grid would not fill the GPU otherwise (about 3 CTAs per SM are resident): with many rows the
     // repeated sample and the barriers cost more than the shorter rows win.
-    int sms = 0;
-    err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    if (err != cudaSuccess) return err;
+    const int sms = setup.sms;
     unsigned ctas = vocab >= 131072 ? 8u : vocab >= 65536 ? 4u : vocab >= 32768 ? 2u : 1u;
     while (ctas > 1 && num_rows * ctas > 3LL * sms) ctas >>= 1;
     if (num_rows * ctas > 0x7fffffffLL) return cudaErrorInvalidConfiguration;

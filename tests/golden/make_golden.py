@@ -115,7 +115,7 @@ def main() -> None:
         )
         print(name, "ok")
 
-    # BASELINE config 1 (CPU torch reference path, seed 0): digest-checked regenerated inputs
+    # benchmark configuration "CPU torch reference path, seed 0": digest-checked regenerated inputs
     w = workloads.make("cpu_ref", device="cpu", seed=0)
     cs_up = T.make_cos_sin_cache(4096, 64, torch.float32, "cpu")
     assert torch.equal(cs_up, w.cos_sin_cache), "workload cos/sin table differs from the upstream helper"

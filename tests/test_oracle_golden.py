@@ -42,7 +42,7 @@ def _sha(t):
 
 
 def test_cpu_ref_config_against_upstream_digests():
-    """BASELINE config "CPU torch reference path, seed 0": 256 tokens x 8 heads."""
+    """The benchmark configuration "CPU torch reference path, seed 0": 256 tokens x 8 heads."""
     z = np.load(GOLDEN / "cpu_ref.npz")
     w = workloads.make("cpu_ref", device="cpu", seed=0)
     got = [_sha(t) for t in (w.q, w.kv, w.k_cache, w.slot_mapping, w.position_ids)]

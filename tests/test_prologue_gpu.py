@@ -92,7 +92,7 @@ def test_golden_vectors(variant, case):
 
 
 def test_cpu_ref_config_matches_upstream_golden(variant):
-    """BASELINE config "CPU torch reference path, seed 0" (256 tokens x 8 heads)."""
+    """The benchmark configuration "CPU torch reference path, seed 0" (256 tokens x 8 heads)."""
     z = np.load(GOLDEN / "cpu_ref.npz")
     w = workloads.make("cpu_ref", device="cpu", seed=0)
     q, kv, kc, slots, pos, cs = [t.to(DEV) for t in (w.q, w.kv, w.k_cache, w.slot_mapping, w.position_ids, w.cos_sin_cache)]
