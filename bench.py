@@ -338,7 +338,7 @@ def sibling_ops(steps, warmup, only=None):
     if want("per_token_group_quant_fp8"):
         _sibling_group_quant(flaggems_vllm, out, steps, warmup, stream, g, only)
     if want("top_k_per_row_decode"):
-        _sibling_topk(flaggems_vllm, out, steps, warmup, stream, g)
+        _sibling_topk(flaggems_vllm, out, steps, warmup, stream, g, only)
     return out
 
 
@@ -469,7 +469,7 @@ def _sibling_group_quant(flaggems_vllm, out, steps, warmup, stream, g, only):
                     "hbm_gbs": xa.numel() * (2 + 1 + 4 / 128) * steps / secs / 1e9, "note": "includes torch.empty of the two outputs per call"}
 
 
-def _sibling_topk(flaggems_vllm, out, steps, warmup, stream, g):
+def _sibling_topk(flaggems_vllm, out, steps, warmup, stream, g, only):
     # top-k selection over the indexer logits: one decode row, a decode batch, a prefill chunk (rotating inputs larger than L2)
     dev = "cuda"
     try:
@@ -479,6 +479,9 @@ def _sibling_topk(flaggems_vllm, out, steps, warmup, stream, g):
     except Exception:
         library = None
     for rows, vocab, tk in ((1, 262144, 512), (496, 262144, 512), (4096, 32768, 2048)):
+        key = f"top_k_per_row_decode[{rows}x{vocab}, k={tk}]"
+        if only is not None and only not in key:
+            continue
         sets = max(1, min(8, (1 << 30) // (rows * vocab * 4)))
         logits = [torch.randn(rows, vocab, generator=g, device=dev) for _ in range(sets)]
         seq = torch.full((rows,), vocab, device=dev, dtype=torch.int32)
@@ -498,9 +501,9 @@ def _sibling_topk(flaggems_vllm, out, steps, warmup, stream, g):
         secs = time_steps(ours, steps, warmup, stream, torch.cuda.synchronize)
         entry = {"rows": rows, "vocab": vocab, "top_k": tk, "us_per_launch": secs / steps * 1e6,
                  "hbm_gbs": rows * (vocab + tk) * 4 * steps / secs / 1e9}
-        if library is not None:
+        if library is not None and only is None:
             entry["vllm_kernel_us_per_launch"] = time_steps(theirs, steps, warmup, stream, torch.cuda.synchronize) / steps * 1e6
-        out[f"top_k_per_row_decode[{rows}x{vocab}, k={tk}]"] = entry
+        out[key] = entry
         del logits
 
 
