@@ -215,6 +215,28 @@ int dsv4_fused_q_kv_rmsnorm(const void* qr, void* qr_out, const void* q_weight, 
                                                 static_cast<cudaStream_t>(cuda_stream)));
 }
 
+int dsv4_fused_q_kv_rmsnorm_dtypes(const void* qr, void* qr_out, const void* q_weight, int64_t q_in_stride, int64_t q_out_stride,
+                                   int64_t q_size, int32_t q_dtype, int32_t q_weight_dtype, const void* kv, void* kv_out,
+                                   const void* kv_weight, int64_t kv_in_stride, int64_t kv_out_stride, int64_t kv_size,
+                                   int32_t kv_dtype, int32_t kv_weight_dtype, int64_t num_tokens, float eps, void* cuda_stream) {
+    if (num_tokens < 0 || q_size <= 0 || kv_size <= 0 || q_size >= (1LL << 31) || kv_size >= (1LL << 31))
+        return DSV4_ERR_BAD_SIZE;
+    for (const int32_t d : {q_dtype, q_weight_dtype, kv_dtype, kv_weight_dtype})
+        if (d < 0 || d > 2) return DSV4_ERR_BAD_SIZE;
+    if (num_tokens == 0) return DSV4_OK;
+    if (!qr || !qr_out || !q_weight || !kv || !kv_out || !kv_weight) return DSV4_ERR_NULL_POINTER;
+    const auto misaligned = [](const void* p, int32_t dtype) { return (reinterpret_cast<uintptr_t>(p) & (dtype == 2 ? 3u : 1u)) != 0; };
+    if (misaligned(qr, q_dtype) || misaligned(qr_out, q_dtype) || misaligned(q_weight, q_weight_dtype) || misaligned(kv, kv_dtype) ||
+        misaligned(kv_out, kv_dtype) || misaligned(kv_weight, kv_weight_dtype))
+        return DSV4_ERR_MISALIGNED;
+    if (q_dtype == 0 && q_weight_dtype == 0 && kv_dtype == 0 && kv_weight_dtype == 0)
+        return dsv4_fused_q_kv_rmsnorm(qr, qr_out, q_weight, q_in_stride, q_out_stride, q_size, kv, kv_out, kv_weight, kv_in_stride,
+                                       kv_out_stride, kv_size, num_tokens, eps, cuda_stream);
+    return static_cast<int>(launch_q_kv_rmsnorm_any(qr, qr_out, q_weight, q_in_stride, q_out_stride, q_size, q_dtype, q_weight_dtype, kv,
+                                                    kv_out, kv_weight, kv_in_stride, kv_out_stride, kv_size, kv_dtype, kv_weight_dtype,
+                                                    num_tokens, eps, static_cast<cudaStream_t>(cuda_stream)));
+}
+
 int dsv4_fused_inv_rope_fp8_quant(const void* o, int64_t o_stride_token, int64_t o_stride_head, const int64_t* positions,
                                   const float* cos_sin_cache, int64_t cos_sin_stride, void* fp8_out, void* scale_out,
                                   int64_t scale_stride_group, int64_t num_tokens, int64_t padded_tokens, int64_t n_groups,

@@ -526,6 +526,10 @@ cudaError_t launch_indexer_q_rope_quant(const int64_t* positions, const void* q,
                                         int64_t scale_stride1, const void* weights, int64_t weights_stride, int weights_dtype,
                                         float* weights_out, int64_t weights_out_stride, float softmax_scale, float head_scale,
                                         int64_t num_tokens, int num_heads, int head_dim, int fp4, cudaStream_t stream);
+cudaError_t launch_q_kv_rmsnorm_any(const void* q, void* q_out, const void* q_weight, int64_t q_in_stride, int64_t q_out_stride,
+                                    int64_t q_size, int q_dtype, int q_weight_dtype, const void* kv, void* kv_out,
+                                    const void* kv_weight, int64_t kv_in_stride, int64_t kv_out_stride, int64_t kv_size,
+                                    int kv_dtype, int kv_weight_dtype, int64_t num_tokens, float eps, cudaStream_t stream);
 void count_launch();
 cudaError_t read_device_error(int* value);
 

@@ -5,6 +5,8 @@
 // One warp per row; a row of up to 2048 elements stays in registers between the reduction and
 // the scaling (one read, one write per element); longer or unaligned rows take a two-pass
 // scalar path.  Row 2t is the q row of token t, row 2t+1 its kv row.
+#include <cuda_fp16.h>
+
 #include "dsv4_common.cuh"
 
 namespace dsv4 {
@@ -91,6 +93,51 @@ __global__ void __launch_bounds__(WARPS * 32, CH <= 2 ? 16 : (CH <= 6 ? 8 : 6)) 
     }
 }
 
+// Any of bf16 (0), fp16 (1), fp32 (2) for the rows and, independently, for the weights: the reference kernel is
+// generic over the element types (it loads everything as fp32 and stores in the output's type).  One warp per row,
+// two passes over the row, element by element.  The DeepSeek-V4 layer passes bf16 everywhere and takes the kernel above.
+struct AnyRows {
+    const uint8_t* in;
+    uint8_t* out;
+    const uint8_t* weight;
+    int64_t in_stride, out_stride;  // elements
+    int32_t size, dtype, weight_dtype;
+};
+
+__device__ __forceinline__ float load_any(const uint8_t* base, int64_t i, int dtype) {
+    if (dtype == 2) return reinterpret_cast<const float*>(base)[i];
+    const uint16_t h = reinterpret_cast<const uint16_t*>(base)[i];
+    return dtype == 0 ? bf16_lo(h) : __half2float(__ushort_as_half(h));
+}
+
+__device__ __forceinline__ void store_any(uint8_t* base, int64_t i, int dtype, float v) {
+    if (dtype == 2) reinterpret_cast<float*>(base)[i] = v;
+    else if (dtype == 0) reinterpret_cast<uint16_t*>(base)[i] = static_cast<uint16_t>(pack_bf16x2(v, 0.0f) & 0xffffu);
+    else reinterpret_cast<uint16_t*>(base)[i] = __half_as_ushort(__float2half_rn(v));
+}
+
+template <int WARPS>
+__global__ void __launch_bounds__(WARPS * 32) q_kv_rmsnorm_any_kernel(const AnyRows q, const AnyRows kv, int64_t num_tokens, float eps) {
+    const int lane = threadIdx.x & 31;
+    const int64_t r = static_cast<int64_t>(blockIdx.x) * WARPS + (threadIdx.x >> 5);
+    if (r >= 2 * num_tokens) return;
+    const AnyRows& t = (r & 1) == 0 ? q : kv;
+    const int64_t token = r >> 1;
+    const int esize = t.dtype == 2 ? 4 : 2;
+    const uint8_t* in = t.in + token * t.in_stride * esize;
+    uint8_t* out = t.out + token * t.out_stride * esize;
+    float acc = 0.0f;
+    for (int i = lane; i < t.size; i += 32) {
+        const float f = load_any(in, i, t.dtype);
+        acc = fmaf(f, f, acc);
+    }
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, m);
+    const float rr = inv_rms_of(acc, t.size, eps);
+    for (int i = lane; i < t.size; i += 32)
+        store_any(out, i, t.dtype, __fmul_rn(__fmul_rn(load_any(in, i, t.dtype), rr), load_any(t.weight, i, t.weight_dtype)));
+}
+
 bool vec_ok(const void* in, const void* out, const void* w, int64_t in_stride, int64_t out_stride, int64_t size) {
     const auto a = [](const void* p) { return reinterpret_cast<uintptr_t>(p) & 15u; };
     return a(in) == 0 && a(out) == 0 && a(w) == 0 && in_stride % 8 == 0 && out_stride % 8 == 0 && size % 8 == 0 &&
@@ -118,6 +165,23 @@ cudaError_t launch_q_kv_rmsnorm(const void* q, void* q_out, const void* q_weight
     else if (longest <= 1024) q_kv_rmsnorm_kernel<WARPS, 4><<<g, WARPS * 32, 0, stream>>>(a, b, num_tokens, eps);
     else if (longest <= 1536) q_kv_rmsnorm_kernel<WARPS, 6><<<g, WARPS * 32, 0, stream>>>(a, b, num_tokens, eps);
     else q_kv_rmsnorm_kernel<WARPS, 8><<<g, WARPS * 32, 0, stream>>>(a, b, num_tokens, eps);
+    count_launch();
+    return cudaGetLastError();
+}
+
+cudaError_t launch_q_kv_rmsnorm_any(const void* q, void* q_out, const void* q_weight, int64_t q_in_stride, int64_t q_out_stride,
+                                    int64_t q_size, int q_dtype, int q_weight_dtype, const void* kv, void* kv_out,
+                                    const void* kv_weight, int64_t kv_in_stride, int64_t kv_out_stride, int64_t kv_size,
+                                    int kv_dtype, int kv_weight_dtype, int64_t num_tokens, float eps, cudaStream_t stream) {
+    constexpr int WARPS = 4;
+    if (num_tokens == 0) return cudaSuccess;
+    const AnyRows a{static_cast<const uint8_t*>(q), static_cast<uint8_t*>(q_out), static_cast<const uint8_t*>(q_weight),
+                    q_in_stride, q_out_stride, static_cast<int32_t>(q_size), q_dtype, q_weight_dtype};
+    const AnyRows b{static_cast<const uint8_t*>(kv), static_cast<uint8_t*>(kv_out), static_cast<const uint8_t*>(kv_weight),
+                    kv_in_stride, kv_out_stride, static_cast<int32_t>(kv_size), kv_dtype, kv_weight_dtype};
+    const int64_t grid = (2 * num_tokens + WARPS - 1) / WARPS;
+    if (grid > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
+    q_kv_rmsnorm_any_kernel<WARPS><<<static_cast<unsigned>(grid), WARPS * 32, 0, stream>>>(a, b, num_tokens, eps);
     count_launch();
     return cudaGetLastError();
 }

@@ -19,6 +19,7 @@ EXPORTS = (
     "dsv4_gather_dequant_k_cache",
     "dsv4_dequantize_and_gather_k_cache",
     "dsv4_fused_q_kv_rmsnorm",
+    "dsv4_fused_q_kv_rmsnorm_dtypes",
     "dsv4_fused_inv_rope_fp8_quant",
     "dsv4_indexer_k_quant_and_cache",
     "dsv4_cp_gather_indexer_k_quant_cache",
@@ -82,6 +83,8 @@ def lib() -> ctypes.CDLL:
     L.dsv4_dequantize_and_gather_k_cache.restype = i32
     L.dsv4_fused_q_kv_rmsnorm.argtypes = [vp, vp, vp, i64, i64, i64, vp, vp, vp, i64, i64, i64, i64, f32, vp]
     L.dsv4_fused_q_kv_rmsnorm.restype = i32
+    L.dsv4_fused_q_kv_rmsnorm_dtypes.argtypes = [vp, vp, vp, i64, i64, i64, i32, i32, vp, vp, vp, i64, i64, i64, i32, i32, i64, f32, vp]
+    L.dsv4_fused_q_kv_rmsnorm_dtypes.restype = i32
     L.dsv4_fused_inv_rope_fp8_quant.argtypes = [vp, i64, i64, vp, vp, i64, vp, vp, i64, i64, i64, i64, i64, f32, i32, vp]
     L.dsv4_fused_inv_rope_fp8_quant.restype = i32
     L.dsv4_indexer_k_quant_and_cache.argtypes = [vp, i64, i32, vp, i64, vp, i64, i64, i64, i64, i32, vp]

@@ -146,6 +146,17 @@ int dsv4_fused_q_kv_rmsnorm(const void* qr, void* qr_out, const void* q_weight, 
                             void* cuda_stream);
 
 /*
+ * The same operator for the element types the reference kernel accepts besides bf16 (it loads rows and weights as fp32
+ * whatever their type and stores in the row's type, :50-62 there): *_dtype 0 = bf16, 1 = fp16, 2 = fp32, given
+ * separately for the q rows (input and output share it), the kv rows and the two weight vectors.  All bf16 is forwarded
+ * to dsv4_fused_q_kv_rmsnorm; anything else runs one warp per row, two passes, element by element.
+ */
+int dsv4_fused_q_kv_rmsnorm_dtypes(const void* qr, void* qr_out, const void* q_weight, int64_t q_in_stride, int64_t q_out_stride,
+                                   int64_t q_size, int32_t q_dtype, int32_t q_weight_dtype, const void* kv, void* kv_out,
+                                   const void* kv_weight, int64_t kv_in_stride, int64_t kv_out_stride, int64_t kv_size,
+                                   int32_t kv_dtype, int32_t kv_weight_dtype, int64_t num_tokens, float eps, void* cuda_stream);
+
+/*
  * The attention epilogue that mirrors the prologue.  Replaces the reference operator
  *   fused_inv_rope_fp8_quant(o, positions, cos_sin_cache, n_groups, heads_per_group, nope_dim=448,
  *                            rope_dim=64, quant_group_size=128, eps, dtype, tma_aligned_scales)

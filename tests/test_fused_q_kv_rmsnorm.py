@@ -91,6 +91,41 @@ def test_rmsnorm_feeds_the_prologue():
     assert torch.equal(w.k_cache.cpu(), kc_ref)
 
 
+def _statement(x, weight, eps):
+    """The torch statement of the operator in the upstream test (tests/test_deepseek_v4_attention_fused_q_kv_rmsnorm.py:40-44)."""
+    y = x.float() * torch.rsqrt(torch.mean(x.float() * x.float(), dim=-1, keepdim=True) + eps)
+    return (y * weight.float()).to(x.dtype)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("q_dtype,kv_dtype,w_dtype", [
+    (torch.float16, torch.float16, torch.float16), (torch.float32, torch.float32, torch.float32),
+    (torch.bfloat16, torch.bfloat16, torch.float32), (torch.float16, torch.bfloat16, torch.float32),
+    (torch.float32, torch.float16, torch.bfloat16)])
+@pytest.mark.parametrize("tokens,qdim,kvdim", [(1, 7, 3), (33, 1536, 512), (5, 2500, 130)])
+def test_element_types_the_reference_kernel_accepts(q_dtype, kv_dtype, w_dtype, tokens, qdim, kvdim):
+    """Rows and weights in float16 / float32 / bfloat16, each tensor its own (the reference kernel loads everything as
+    fp32 and stores in the row's type).  Compared with the upstream test's torch statement on the same device; the
+    mean's summation order is free, so the bar is one unit in the last place of the row's type (float32: 4 ulps, the
+    reciprocal square root adds its own)."""
+    g = torch.Generator(device="cuda:0").manual_seed(tokens * 1000 + qdim)
+    qr = torch.randn(tokens, qdim, generator=g, device="cuda:0").to(q_dtype)
+    kv = (torch.randn(tokens, kvdim, generator=g, device="cuda:0") * 3).to(kv_dtype)
+    qw = torch.randn(qdim, generator=g, device="cuda:0").to(w_dtype)
+    kw = torch.randn(kvdim, generator=g, device="cuda:0").to(w_dtype)
+    q_out, kv_out = flaggems_vllm.fused_q_kv_rmsnorm(qr, kv, qw, kw, 1e-6)
+    assert q_out.dtype == q_dtype and kv_out.dtype == kv_dtype and q_out.shape == qr.shape and kv_out.shape == kv.shape
+    for got, want in ((q_out, _statement(qr, qw, 1e-6)), (kv_out, _statement(kv, kw, 1e-6))):
+        if got.dtype == torch.float32:
+            torch.testing.assert_close(got, want, rtol=5e-7, atol=0)
+        else:
+            ints = torch.int16
+            a, b = got.view(ints).to(torch.int32), want.view(ints).to(torch.int32)
+            a, b = torch.where(a < 0, -(a & 0x7FFF), a), torch.where(b < 0, -(b & 0x7FFF), b)
+            d = (a - b).abs()
+            assert int(d.max()) <= 1 and float((d != 0).float().mean()) < 2e-3
+
+
 def test_host_checks_without_gpu():
     qr, kv = torch.zeros(4, 256, dtype=torch.bfloat16), torch.zeros(4, 128, dtype=torch.bfloat16)
     qw, kw = torch.ones(256, dtype=torch.bfloat16), torch.ones(128, dtype=torch.bfloat16)

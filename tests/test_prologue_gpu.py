@@ -554,3 +554,20 @@ def test_programmatic_dependent_launch_gives_the_same_result(mode):
     finally:
         _native.set_pdl(previous)
     assert _native.set_pdl(previous) == previous
+
+
+@pytest.mark.parametrize("staging", [0, 1])
+@pytest.mark.parametrize("pdl", [0, 1, 2])
+@pytest.mark.parametrize("n,h", [(37, 9), (600, 128)])
+def test_every_launch_mode_and_table_staging_gives_the_oracle_result(staging, pdl, n, h):
+    """The rows kernel has two ways to fetch the cos/sin rows (per warp into registers, or once per CTA through shared
+    memory; chosen by launch size unless forced) and three launch modes; the result does not depend on either.  Both
+    sizes are run in both staging modes: a launch of a few CTAs and one above the size at which the library switches."""
+    q, kv, kc, slots, pos, cs = random_case(n, h, 64, n // 64 + 3, seed=1000 + n, minus_one=max(1, n // 10))
+    previous_staging, previous_pdl = _native.set_table_staging(staging), _native.set_pdl(pdl)
+    try:
+        run_and_check(q, kv, kc, slots, pos, cs, 1e-6, 64)
+    finally:
+        _native.set_table_staging(previous_staging)
+        _native.set_pdl(previous_pdl)
+    assert _native.set_table_staging(previous_staging) == previous_staging
