@@ -257,6 +257,37 @@ int dsv4_fused_inv_rope_fp8_quant(const void* o, int64_t o_stride_token, int64_t
                                                       static_cast<cudaStream_t>(cuda_stream)));
 }
 
+int dsv4_fused_inv_rope_fp8_quant_geometry(const void* o, int64_t o_stride_token, int64_t o_stride_head, const int64_t* positions,
+                                           const float* cos_sin_cache, int64_t cos_sin_stride, void* fp8_out, void* scale_out,
+                                           int64_t scale_stride_group, int64_t num_tokens, int64_t padded_tokens, int64_t n_groups,
+                                           int64_t heads_per_group, int64_t nope_dim, int64_t rope_dim, int64_t quant_group_size,
+                                           float eps, int32_t packed_ue8m0_scales, void* cuda_stream) {
+    if (num_tokens < 0 || padded_tokens < num_tokens || padded_tokens % 4 != 0 || n_groups <= 0 || heads_per_group <= 0 ||
+        n_groups * heads_per_group >= (1LL << 31))
+        return DSV4_ERR_BAD_SIZE;
+    // the reference wrapper's geometry rules (src/flaggems_vllm/ops/fused_inv_rope_fp8_quant.py:193-200), plus an even group
+    const int64_t head_dim = nope_dim + rope_dim;
+    if (nope_dim < 0 || rope_dim < 0 || quant_group_size <= 0 || head_dim <= 0 || head_dim >= (1 << 20) || head_dim % quant_group_size != 0 ||
+        nope_dim % quant_group_size != quant_group_size - rope_dim || rope_dim % 2 != 0 || quant_group_size % 2 != 0)
+        return DSV4_ERR_BAD_SIZE;
+    if (packed_ue8m0_scales && head_dim / quant_group_size != 4) return DSV4_ERR_BAD_SIZE;
+    const bool fast_layout = aligned16(o) && aligned16(cos_sin_cache) && o_stride_token % 8 == 0 && o_stride_head % 8 == 0 &&
+                             cos_sin_stride % 4 == 0 && (reinterpret_cast<uintptr_t>(fp8_out) & 7u) == 0;
+    if (nope_dim == 448 && rope_dim == 64 && quant_group_size == 128 && (fast_layout || num_tokens == 0))
+        return dsv4_fused_inv_rope_fp8_quant(o, o_stride_token, o_stride_head, positions, cos_sin_cache, cos_sin_stride, fp8_out,
+                                             scale_out, scale_stride_group, num_tokens, padded_tokens, n_groups, heads_per_group, eps,
+                                             packed_ue8m0_scales, cuda_stream);
+    if (num_tokens == 0) return DSV4_OK;
+    if (!o || !positions || !cos_sin_cache || !fp8_out || !scale_out) return DSV4_ERR_NULL_POINTER;
+    const auto low_bits = [](const void* p, uintptr_t mask) { return (reinterpret_cast<uintptr_t>(p) & mask) != 0; };
+    if (low_bits(o, 1u) || low_bits(cos_sin_cache, 3u) || low_bits(fp8_out, 1u) || low_bits(scale_out, 3u)) return DSV4_ERR_MISALIGNED;
+    return static_cast<int>(launch_inv_rope_fp8_quant_any(
+        o, o_stride_token, o_stride_head, positions, cos_sin_cache, cos_sin_stride, fp8_out, scale_out, scale_stride_group, num_tokens,
+        padded_tokens, static_cast<int>(n_groups * heads_per_group), static_cast<int>(heads_per_group), static_cast<int>(nope_dim),
+        static_cast<int>(rope_dim), static_cast<int>(quant_group_size), eps, packed_ue8m0_scales ? 1 : 0,
+        static_cast<cudaStream_t>(cuda_stream)));
+}
+
 int dsv4_indexer_k_quant_and_cache(const void* k, int64_t k_row_stride, int32_t k_is_fp16, void* kv_cache,
                                    int64_t cache_block_stride_bytes, const int64_t* slot_mapping, int64_t num_tokens,
                                    int64_t cache_block_size, int64_t head_dim, int64_t quant_block_size,

@@ -530,6 +530,11 @@ cudaError_t launch_q_kv_rmsnorm_any(const void* q, void* q_out, const void* q_we
                                     int64_t q_size, int q_dtype, int q_weight_dtype, const void* kv, void* kv_out,
                                     const void* kv_weight, int64_t kv_in_stride, int64_t kv_out_stride, int64_t kv_size,
                                     int kv_dtype, int kv_weight_dtype, int64_t num_tokens, float eps, cudaStream_t stream);
+cudaError_t launch_inv_rope_fp8_quant_any(const void* o, int64_t o_stride_token, int64_t o_stride_head, const int64_t* positions,
+                                          const float* cos_sin, int64_t cos_sin_stride, void* fp8, void* scale,
+                                          int64_t scale_stride_group, int64_t num_tokens, int64_t padded_tokens, int num_heads,
+                                          int heads_per_group, int nope_dim, int rope_dim, int group_size, float eps, int packed,
+                                          cudaStream_t stream);
 void count_launch();
 cudaError_t read_device_error(int* value);
 

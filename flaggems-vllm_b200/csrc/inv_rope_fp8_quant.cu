@@ -138,7 +138,104 @@ __global__ void __launch_bounds__(WARPS * 32, MIN_CTAS) inv_rope_fp8_quant_kerne
     }
 }
 
+// Any geometry the reference wrapper accepts (head_dim = nope + rope a multiple of the group size, the rotary tail
+// ending the last group, even group size): one warp per (token, head), one group after the other, two passes over a
+// group (maximum, then quantise; the rotation is recomputed, which is deterministic).  Same arithmetic as above: rotated
+// values rounded to bf16 before quantising, fp32 scales divide (IEEE), power-of-two scales multiply by the exact
+// reciprocal.  Packed scales need four groups per head: one int32 per head is the only layout in which the reference's
+// kernel and its allocation agree (src/flaggems_vllm/ops/fused_inv_rope_fp8_quant.py:133-143, 206-217).
+struct InvRopeGeometry {
+    int32_t nope_dim, rope_dim, group, chunks;
+};
+
+template <int WARPS, bool PACKED>
+__global__ void __launch_bounds__(WARPS * 32) inv_rope_fp8_quant_any_kernel(const InvRopeParams p, const InvRopeGeometry geo) {
+    const int lane = threadIdx.x & 31;
+    const int64_t row = static_cast<int64_t>(blockIdx.x) * WARPS + (threadIdx.x >> 5);
+    if (row >= p.padded_tokens * p.num_heads) return;
+    const int64_t token = row / p.num_heads;
+    const int head = static_cast<int>(row - token * p.num_heads);
+    const int group = head / p.heads_per_group, head_in_group = head - group * p.heads_per_group;
+    uint8_t* scale_row = p.scale + (group * p.scale_stride_group + token) * 4;
+    if (token >= p.num_tokens) {  // token padding of the scale storage: zero scales
+        if (PACKED) {
+            if (lane == 0) *reinterpret_cast<uint32_t*>(scale_row + static_cast<int64_t>(head_in_group) * p.padded_tokens * 4) = 0u;
+        } else if (lane < geo.chunks) {
+            *reinterpret_cast<float*>(scale_row + (static_cast<int64_t>(head_in_group) * geo.chunks + lane) * p.padded_tokens * 4) = 0.0f;
+        }
+        return;
+    }
+    const int head_dim = geo.nope_dim + geo.rope_dim, half_rope = geo.rope_dim / 2;
+    const float* cs = p.cos_sin + p.positions[token] * p.cos_sin_stride;
+    const uint16_t* in = reinterpret_cast<const uint16_t*>(p.o) + token * p.o_stride_token + static_cast<int64_t>(head) * p.o_stride_head;
+    uint8_t* out = p.fp8 + (static_cast<int64_t>(group) * p.num_tokens + token) * (static_cast<int64_t>(p.heads_per_group) * head_dim) +
+                   static_cast<int64_t>(head_in_group) * head_dim;
+    // the pair (2j, 2j+1) of the head after the inverse rotation (if it lies in the rotary tail) and the bf16 rounding
+    const auto pair_at = [&](int e0, float* a, float* b) {
+        const float e = bf16_lo(in[e0]), o = bf16_lo(in[e0 + 1]);
+        if (e0 >= geo.nope_dim) {
+            const int j = (e0 - geo.nope_dim) >> 1;
+            const float c = cs[j], sn = cs[half_rope + j];
+            const uint32_t rot = pack_bf16x2(__fadd_rn(__fmul_rn(e, c), __fmul_rn(o, sn)), __fsub_rn(__fmul_rn(o, c), __fmul_rn(e, sn)));
+            *a = bf16_lo(rot), *b = bf16_hi(rot);
+        } else {
+            *a = e, *b = o;
+        }
+    };
+    uint32_t word = 0;
+    for (int k = 0; k < geo.chunks; ++k) {
+        float amax = 0.0f;
+        for (int pr = lane; pr < geo.group / 2; pr += 32) {
+            float a, b;
+            pair_at(k * geo.group + 2 * pr, &a, &b);
+            amax = fmaxf(amax, fmaxf(fabsf(a), fabsf(b)));
+        }
+#pragma unroll
+        for (int m = 16; m > 0; m >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
+        float scale = __fmul_rn(fmaxf(amax, p.eps), 1.0f / 448.0f);
+        float inv = 0.0f;
+        if (PACKED) {
+            const uint32_t code = pow2_ceil_code(scale);
+            word |= code << (8 * k);
+            inv = __uint_as_float((254u - code) << 23);
+        }
+        for (int pr = lane; pr < geo.group / 2; pr += 32) {
+            const int e0 = k * geo.group + 2 * pr;
+            float a, b;
+            pair_at(e0, &a, &b);
+            const float qa = PACKED ? __fmul_rn(a, inv) : __fdiv_rn(a, scale), qb = PACKED ? __fmul_rn(b, inv) : __fdiv_rn(b, scale);
+            *reinterpret_cast<uint16_t*>(out + e0) = static_cast<uint16_t>(pack_e4m3x4(qa, qb, 0.f, 0.f));
+        }
+        if (!PACKED && lane == 0)
+            *reinterpret_cast<float*>(scale_row + (static_cast<int64_t>(head_in_group) * geo.chunks + k) * p.padded_tokens * 4) = scale;
+    }
+    if (PACKED && lane == 0) *reinterpret_cast<uint32_t*>(scale_row + static_cast<int64_t>(head_in_group) * p.padded_tokens * 4) = word;
+}
+
 }  // namespace
+
+cudaError_t launch_inv_rope_fp8_quant_any(const void* o, int64_t o_stride_token, int64_t o_stride_head, const int64_t* positions,
+                                          const float* cos_sin, int64_t cos_sin_stride, void* fp8, void* scale,
+                                          int64_t scale_stride_group, int64_t num_tokens, int64_t padded_tokens, int num_heads,
+                                          int heads_per_group, int nope_dim, int rope_dim, int group_size, float eps, int packed,
+                                          cudaStream_t stream) {
+    constexpr int WARPS = 4;
+    const int64_t rows = padded_tokens * num_heads;
+    if (rows == 0) return cudaSuccess;
+    const int64_t grid = (rows + WARPS - 1) / WARPS;
+    if (grid > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
+    InvRopeParams p{};
+    p.o = static_cast<const uint8_t*>(o), p.o_stride_token = o_stride_token, p.o_stride_head = o_stride_head;
+    p.positions = positions, p.cos_sin = cos_sin, p.cos_sin_stride = cos_sin_stride;
+    p.fp8 = static_cast<uint8_t*>(fp8), p.scale = static_cast<uint8_t*>(scale), p.scale_stride_group = scale_stride_group;
+    p.num_tokens = num_tokens, p.padded_tokens = padded_tokens, p.num_heads = num_heads, p.heads_per_group = heads_per_group;
+    p.eps = eps;
+    const InvRopeGeometry geo{nope_dim, rope_dim, group_size, (nope_dim + rope_dim) / group_size};
+    if (packed) inv_rope_fp8_quant_any_kernel<WARPS, true><<<static_cast<unsigned>(grid), WARPS * 32, 0, stream>>>(p, geo);
+    else inv_rope_fp8_quant_any_kernel<WARPS, false><<<static_cast<unsigned>(grid), WARPS * 32, 0, stream>>>(p, geo);
+    count_launch();
+    return cudaGetLastError();
+}
 
 cudaError_t launch_inv_rope_fp8_quant(const void* o, int64_t o_stride_token, int64_t o_stride_head, const int64_t* positions,
                                       const float* cos_sin, int64_t cos_sin_stride, void* fp8, void* scale,

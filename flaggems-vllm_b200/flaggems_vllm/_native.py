@@ -21,6 +21,7 @@ EXPORTS = (
     "dsv4_fused_q_kv_rmsnorm",
     "dsv4_fused_q_kv_rmsnorm_dtypes",
     "dsv4_fused_inv_rope_fp8_quant",
+    "dsv4_fused_inv_rope_fp8_quant_geometry",
     "dsv4_indexer_k_quant_and_cache",
     "dsv4_cp_gather_indexer_k_quant_cache",
     "dsv4_compute_global_topk_indices_and_lens",
@@ -87,6 +88,8 @@ def lib() -> ctypes.CDLL:
     L.dsv4_fused_q_kv_rmsnorm_dtypes.restype = i32
     L.dsv4_fused_inv_rope_fp8_quant.argtypes = [vp, i64, i64, vp, vp, i64, vp, vp, i64, i64, i64, i64, i64, f32, i32, vp]
     L.dsv4_fused_inv_rope_fp8_quant.restype = i32
+    L.dsv4_fused_inv_rope_fp8_quant_geometry.argtypes = [vp, i64, i64, vp, vp, i64, vp, vp, i64, i64, i64, i64, i64, i64, i64, i64, f32, i32, vp]
+    L.dsv4_fused_inv_rope_fp8_quant_geometry.restype = i32
     L.dsv4_indexer_k_quant_and_cache.argtypes = [vp, i64, i32, vp, i64, vp, i64, i64, i64, i64, i32, vp]
     L.dsv4_indexer_k_quant_and_cache.restype = i32
     L.dsv4_cp_gather_indexer_k_quant_cache.argtypes = [vp, i64, vp, i64, vp, i64, vp, i64, vp, i64, i64, i64, i64, i64, vp]

@@ -2,7 +2,8 @@
 
 Drop-in for the reference operator of the same module path and name
 (src/flaggems_vllm/ops/fused_inv_rope_fp8_quant.py:155-256): same arguments, assertions, output shapes,
-strides and dtypes.  Supports the DeepSeek-V4 geometry only (head_dim 512 = 448 + 64, groups of 128).
+strides and dtypes, for every geometry that passes its assertions (and has an even group size); the DeepSeek-V4
+geometry (head_dim 512 = 448 + 64, groups of 128) runs on the vectorised kernel.
 """
 from __future__ import annotations
 
@@ -34,12 +35,12 @@ def fused_inv_rope_fp8_quant(
 ) -> Tuple[torch.Tensor, torch.Tensor]:
     """
     Args:
-        o: [num_tokens, num_heads, 512] bfloat16
+        o: [num_tokens, num_heads, nope_dim + rope_dim] bfloat16
         positions: [num_tokens] int64
-        cos_sin_cache: [max_position, 64] float32, cos || sin
+        cos_sin_cache: [max_position, rope_dim] float32, cos || sin
 
     Returns:
-        o_fp8: [num_tokens, n_groups, heads_per_group * 512] float8_e4m3fn, strides (d, num_tokens*d, 1)
+        o_fp8: [num_tokens, n_groups, heads_per_group * head_dim] float8_e4m3fn, strides (d, num_tokens*d, 1)
         o_scale: [num_tokens, n_groups, blocks] float32, or int32 with four UE8M0 bytes per head when
                  tma_aligned_scales; token-major storage padded to a multiple of 4 tokens
     """
@@ -59,17 +60,20 @@ def fused_inv_rope_fp8_quant(
     assert rope_dim % 2 == 0
     assert cos_sin_cache.shape[-1] == rope_dim
     assert cos_sin_cache.dtype == torch.float32
-    # this implementation: the DeepSeek-V4 geometry, bf16 activations, int64 positions
-    assert (nope_dim, rope_dim, quant_group_size) == (448, 64, 128), "only nope 448 / rope 64 / groups of 128"
+    # this implementation: bf16 activations, int64 positions, an even group size; the DeepSeek-V4 geometry
+    # (448 + 64, groups of 128) with 16-byte aligned rows takes the vectorised kernel, any other a general one
+    assert quant_group_size % 2 == 0, "the group size must be even"
     assert o.dtype == torch.bfloat16 and positions.dtype == torch.int64
     assert o.device.type == "cuda", "this operator has no CPU path"
     assert positions.device == o.device and cos_sin_cache.device == o.device
     assert positions.is_contiguous() and cos_sin_cache.stride(1) == 1
-    assert o.data_ptr() % 16 == 0 and o.stride(0) % 8 == 0 and o.stride(1) % 8 == 0, "o rows must be 16-byte aligned"
 
     chunks_per_head = head_dim // quant_group_size
     if tma_aligned_scales:
         assert chunks_per_head <= 4, "packed UE8M0 path currently expects at most 4 scale blocks per head"
+        # with fewer than four the reference's kernel writes one int32 per head into storage sized for one per four
+        # groups (:133-143 against :206-217 there): only four groups per head have a defined packed layout
+        assert chunks_per_head == 4, "packed UE8M0 scales need four groups per head"
 
     d = heads_per_group * head_dim
     num_scale_blocks = d // quant_group_size
@@ -86,10 +90,11 @@ def fused_inv_rope_fp8_quant(
         with torch.cuda.device(o.device):
             stream = torch.cuda.current_stream(o.device).cuda_stream
             _native.check(
-                _native.lib().dsv4_fused_inv_rope_fp8_quant(
+                _native.lib().dsv4_fused_inv_rope_fp8_quant_geometry(
                     o.data_ptr(), o.stride(0), o.stride(1), positions.data_ptr(), cos_sin_cache.data_ptr(),
                     cos_sin_cache.stride(0), fp8_q.data_ptr(), scale.data_ptr(), scale_inner * tma_aligned_t, num_tokens,
-                    tma_aligned_t, n_groups, heads_per_group, float(eps), 1 if tma_aligned_scales else 0, stream,
+                    tma_aligned_t, n_groups, heads_per_group, int(nope_dim), int(rope_dim), int(quant_group_size), float(eps),
+                    1 if tma_aligned_scales else 0, stream,
                 )
             )
     return fp8_q.transpose(0, 1), scale.transpose(0, 1)

@@ -178,6 +178,21 @@ int dsv4_fused_inv_rope_fp8_quant(const void* o, int64_t o_stride_token, int64_t
                                   int64_t heads_per_group, float eps, int32_t packed_ue8m0_scales, void* cuda_stream);
 
 /*
+ * The same operator for every geometry the reference wrapper accepts (:193-200 there): head_dim = nope_dim + rope_dim a
+ * multiple of quant_group_size, nope_dim % quant_group_size == quant_group_size - rope_dim (the rotary tail ends the last
+ * group), rope_dim even; in addition quant_group_size must be even.  Same tensors and layouts with 512 replaced by
+ * head_dim, 64 by rope_dim and 4 by head_dim / quant_group_size scale columns per head; o needs 2-byte alignment only.
+ * packed_ue8m0_scales requires four groups per head (one int32 per head is the only packed layout in which the
+ * reference's kernel and allocation agree).  448 / 64 / 128 with 16-byte aligned rows is forwarded to
+ * dsv4_fused_inv_rope_fp8_quant; anything else runs one warp per (token, head), group by group, with IEEE divisions.
+ */
+int dsv4_fused_inv_rope_fp8_quant_geometry(const void* o, int64_t o_stride_token, int64_t o_stride_head, const int64_t* positions,
+                                           const float* cos_sin_cache, int64_t cos_sin_stride, void* fp8_out, void* scale_out,
+                                           int64_t scale_stride_group, int64_t num_tokens, int64_t padded_tokens, int64_t n_groups,
+                                           int64_t heads_per_group, int64_t nope_dim, int64_t rope_dim, int64_t quant_group_size,
+                                           float eps, int32_t packed_ue8m0_scales, void* cuda_stream);
+
+/*
  * The sparse-indexer sibling of the prologue's KV insert.  Replaces the reference operator
  *   indexer_k_quant_and_cache(k, kv_cache, slot_mapping, quant_block_size, scale_fmt)
  * (src/flaggems_vllm/ops/indexer_k_quant_and_cache.py:103-132, kernel :44-100): token t of k

@@ -46,6 +46,8 @@ def lib() -> ctypes.CDLL:
         L.dsv4_oracle_weighted_rmsnorm.restype = i32
         L.dsv4_oracle_inv_rope_fp8_quant.argtypes = [vp, i64, i64, vp, vp, i64, vp, vp, i64, i64, i64, f32, i32]
         L.dsv4_oracle_inv_rope_fp8_quant.restype = i32
+        L.dsv4_oracle_inv_rope_fp8_quant_geometry.argtypes = [vp, i64, i64, vp, vp, i64, vp, vp, i64, i64, i64, i64, i64, i64, f32, i32]
+        L.dsv4_oracle_inv_rope_fp8_quant_geometry.restype = i32
         L.dsv4_oracle_indexer_k_quant.argtypes = [vp, i64, i32, vp, i64, vp, i64, i64, i64, i64, i32]
         L.dsv4_oracle_indexer_k_quant.restype = i32
         L.dsv4_oracle_cp_gather_indexer.argtypes = [vp, i64, vp, i64, vp, i64, vp, i64, vp, i64, i64, i64, i64, i64]
@@ -128,17 +130,22 @@ def weighted_rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch
     return out
 
 
-def inv_rope_fp8_quant(o, positions, cos_sin_cache, n_groups, heads_per_group, eps=1e-10, packed=False):
-    """(fp8 bytes uint8 [N, G, hpg*512], scales [N, G, hpg*4] fp32 or [N, G, hpg] int32) on CPU tensors."""
-    assert o.dtype == torch.bfloat16 and o.dim() == 3 and o.shape[2] == 512 and o.stride(2) == 1 and o.device.type == "cpu"
+def inv_rope_fp8_quant(o, positions, cos_sin_cache, n_groups, heads_per_group, eps=1e-10, packed=False, nope_dim=448, rope_dim=64,
+                       quant_group_size=128):
+    """(fp8 bytes uint8 [N, G, hpg*head_dim], scales [N, G, hpg*K] fp32 or [N, G, hpg] int32; K = groups per head) on
+    CPU tensors."""
+    head_dim = nope_dim + rope_dim
+    assert o.dtype == torch.bfloat16 and o.dim() == 3 and o.shape[2] == head_dim and o.stride(2) == 1 and o.device.type == "cpu"
     _cpu(positions, torch.int64), _cpu(cos_sin_cache, torch.float32)
     n = o.shape[0]
-    assert o.shape[1] == n_groups * heads_per_group
-    fp8 = torch.empty(n, n_groups, heads_per_group * 512, dtype=torch.uint8)
-    scales = torch.empty(n, n_groups, heads_per_group * (1 if packed else 4), dtype=torch.int32 if packed else torch.float32)
-    rc = lib().dsv4_oracle_inv_rope_fp8_quant(o.data_ptr(), o.stride(0), o.stride(1), positions.data_ptr(),
-                                              cos_sin_cache.data_ptr(), cos_sin_cache.stride(0), fp8.data_ptr(),
-                                              scales.data_ptr(), n, n_groups, heads_per_group, float(eps), 1 if packed else 0)
+    assert o.shape[1] == n_groups * heads_per_group and head_dim % quant_group_size == 0
+    chunks = head_dim // quant_group_size
+    fp8 = torch.empty(n, n_groups, heads_per_group * head_dim, dtype=torch.uint8)
+    scales = torch.empty(n, n_groups, heads_per_group * (1 if packed else chunks), dtype=torch.int32 if packed else torch.float32)
+    rc = lib().dsv4_oracle_inv_rope_fp8_quant_geometry(o.data_ptr(), o.stride(0), o.stride(1), positions.data_ptr(),
+                                                       cos_sin_cache.data_ptr(), cos_sin_cache.stride(0), fp8.data_ptr(),
+                                                       scales.data_ptr(), n, n_groups, heads_per_group, int(nope_dim), int(rope_dim),
+                                                       int(quant_group_size), float(eps), 1 if packed else 0)
     if rc != 0:
         raise ValueError("dsv4_oracle_inv_rope_fp8_quant rejected its arguments")
     return fp8, scales

@@ -346,40 +346,47 @@ int dsv4_oracle_weighted_rmsnorm(const uint16_t* x, const uint16_t* w, uint16_t*
 }
 
 /*
- * Inverse GPT-J RoPE + FP8 quantisation in groups of 128 of o [N, H, 512] (H = n_groups*heads_per_group),
- * the torch statement tests/test_fused_inv_rope_fp8_quant.py:150-198 of
- * src/flaggems_vllm/ops/fused_inv_rope_fp8_quant.py:37-152.
- * fp8 out: dense [N, n_groups, heads_per_group*512] bytes.  scales out: dense [N, n_groups, K]:
- * fp32 with K = heads_per_group*4, or (packed != 0) int32 with K = heads_per_group, byte j = exponent byte of the
- * power-of-two scale of the head's group j.  o strides in elements.
+ * Inverse GPT-J RoPE + FP8 quantisation in groups of `group` values of o [N, H, nope_dim + rope_dim]
+ * (H = n_groups*heads_per_group; the rotary tail ends the last group), the torch statement
+ * tests/test_fused_inv_rope_fp8_quant.py:132-198 of src/flaggems_vllm/ops/fused_inv_rope_fp8_quant.py:37-152.
+ * With K = head_dim / group groups per head:
+ * fp8 out: dense [N, n_groups, heads_per_group*head_dim] bytes.  scales out: dense [N, n_groups, .]:
+ * fp32 with heads_per_group*K columns, or (packed != 0, K <= 4) int32 with heads_per_group columns, byte j = exponent
+ * byte of the power-of-two scale of the head's group j.  o strides in elements.
  */
-int dsv4_oracle_inv_rope_fp8_quant(const uint16_t* o, int64_t stride_token, int64_t stride_head, const int64_t* positions,
-                                   const float* cos_sin, int64_t cos_sin_stride, uint8_t* fp8, void* scales,
-                                   int64_t num_tokens, int64_t n_groups, int64_t heads_per_group, float eps, int packed) {
-    if (num_tokens < 0 || n_groups <= 0 || heads_per_group <= 0) return -1;
+int dsv4_oracle_inv_rope_fp8_quant_geometry(const uint16_t* o, int64_t stride_token, int64_t stride_head, const int64_t* positions,
+                                            const float* cos_sin, int64_t cos_sin_stride, uint8_t* fp8, void* scales,
+                                            int64_t num_tokens, int64_t n_groups, int64_t heads_per_group, int64_t nope_dim,
+                                            int64_t rope_dim, int64_t group, float eps, int packed) {
+    const int64_t head_dim = nope_dim + rope_dim;
+    if (num_tokens < 0 || n_groups <= 0 || heads_per_group <= 0 || nope_dim < 0 || rope_dim < 0 || rope_dim % 2 != 0 || group <= 0 ||
+        head_dim <= 0 || head_dim > 65536 || head_dim % group != 0 || nope_dim % group != group - rope_dim)
+        return -1;
+    const int64_t chunks = head_dim / group, half_rope = rope_dim / 2;
+    if (packed && chunks > 4) return -1;
     const int64_t heads = n_groups * heads_per_group;
     const float inv_fp8_max = (float)(1.0 / 448.0);
 #pragma omp parallel for schedule(static)
     for (int64_t t = 0; t < num_tokens; ++t) {
         const float* cs = cos_sin + positions[t] * cos_sin_stride;
+        float* x = (float*)malloc(sizeof(float) * (size_t)head_dim);
         for (int64_t h = 0; h < heads; ++h) {
             const uint16_t* row = o + t * stride_token + h * stride_head;
-            float x[HEAD_DIM];
-            for (int i = 0; i < NOPE_DIM; ++i) x[i] = bf16_bits_to_f32(row[i]);
-            for (int j = 0; j < HALF_ROPE; ++j) {
-                float e = bf16_bits_to_f32(row[NOPE_DIM + 2 * j]), od = bf16_bits_to_f32(row[NOPE_DIM + 2 * j + 1]);
-                float c = cs[j], sn = cs[HALF_ROPE + j];
+            for (int64_t i = 0; i < nope_dim; ++i) x[i] = bf16_bits_to_f32(row[i]);
+            for (int64_t j = 0; j < half_rope; ++j) {
+                float e = bf16_bits_to_f32(row[nope_dim + 2 * j]), od = bf16_bits_to_f32(row[nope_dim + 2 * j + 1]);
+                float c = cs[j], sn = cs[half_rope + j];
                 float ec = e * c, os = od * sn, oc = od * c, es = e * sn;
-                x[NOPE_DIM + 2 * j] = bf16_bits_to_f32(f32_to_bf16_bits(ec + os));
-                x[NOPE_DIM + 2 * j + 1] = bf16_bits_to_f32(f32_to_bf16_bits(oc - es));
+                x[nope_dim + 2 * j] = bf16_bits_to_f32(f32_to_bf16_bits(ec + os));
+                x[nope_dim + 2 * j + 1] = bf16_bits_to_f32(f32_to_bf16_bits(oc - es));
             }
             int64_t g = h / heads_per_group, hig = h % heads_per_group;
-            uint8_t* out = fp8 + ((t * n_groups + g) * heads_per_group + hig) * HEAD_DIM;
+            uint8_t* out = fp8 + ((t * n_groups + g) * heads_per_group + hig) * head_dim;
             uint32_t word = 0;
-            for (int k = 0; k < 4; ++k) {
+            for (int64_t k = 0; k < chunks; ++k) {
                 float amax = 0.0f;
-                for (int i = 0; i < 128; ++i) {
-                    float a = fabsf(x[128 * k + i]);
+                for (int64_t i = 0; i < group; ++i) {
+                    float a = fabsf(x[group * k + i]);
                     if (a > amax) amax = a;
                 }
                 float scale = (amax < eps ? eps : amax) * inv_fp8_max;
@@ -390,19 +397,28 @@ int dsv4_oracle_inv_rope_fp8_quant(const uint16_t* o, int64_t stride_token, int6
                     memcpy(&bits, &scale, 4);
                     word |= ((bits >> 23) & 0xffu) << (8 * k);
                 } else {
-                    ((float*)scales)[(t * n_groups + g) * heads_per_group * 4 + hig * 4 + k] = scale;
+                    ((float*)scales)[((t * n_groups + g) * heads_per_group + hig) * chunks + k] = scale;
                 }
-                for (int i = 0; i < 128; ++i) {
-                    float q = x[128 * k + i] / scale;
+                for (int64_t i = 0; i < group; ++i) {
+                    float q = x[group * k + i] / scale;
                     if (q < -448.0f) q = -448.0f;
                     if (q > 448.0f) q = 448.0f;
-                    out[128 * k + i] = f32_to_e4m3_bits(q);
+                    out[group * k + i] = f32_to_e4m3_bits(q);
                 }
             }
             if (packed) ((uint32_t*)scales)[(t * n_groups + g) * heads_per_group + hig] = word;
         }
+        free(x);
     }
     return 0;
+}
+
+/* The DeepSeek-V4 geometry of the function above: head_dim 512 = 448 + 64, groups of 128. */
+int dsv4_oracle_inv_rope_fp8_quant(const uint16_t* o, int64_t stride_token, int64_t stride_head, const int64_t* positions,
+                                   const float* cos_sin, int64_t cos_sin_stride, uint8_t* fp8, void* scales,
+                                   int64_t num_tokens, int64_t n_groups, int64_t heads_per_group, float eps, int packed) {
+    return dsv4_oracle_inv_rope_fp8_quant_geometry(o, stride_token, stride_head, positions, cos_sin, cos_sin_stride, fp8, scales,
+                                                   num_tokens, n_groups, heads_per_group, NOPE_DIM, ROPE_DIM, 128, eps, packed);
 }
 
 static inline float fp16_bits_to_f32(uint16_t h) {

@@ -108,6 +108,99 @@ def test_kernel_matches_oracle_and_layout_contract(tokens, heads, groups, packed
     assert int((storage[:, :, tokens:].view(torch.int32) != 0).sum()) == 0
 
 
+# geometries other than the DeepSeek-V4 one that pass the reference wrapper's assertions: (nope, rope, group)
+GEOMETRIES = [(192, 64, 128), (64, 64, 128), (192, 64, 64), (96, 32, 64), (224, 32, 64), (120, 8, 32), (0, 128, 128), (384, 128, 256)]
+
+
+def _cos_sin_any(max_pos: int, rope_dim: int) -> torch.Tensor:
+    half = rope_dim // 2
+    freqs = 1.0 / (10000.0 ** (torch.arange(0, half, dtype=torch.float32) * 2 / rope_dim))
+    angles = torch.arange(max_pos, dtype=torch.float32)[:, None] * freqs[None, :]
+    return torch.cat([angles.cos(), angles.sin()], dim=-1).contiguous()
+
+
+def _statement_any(o, pos, cs, groups, hpg, nope, rope, group, packed):
+    """The upstream test's torch statement (tests/test_fused_inv_rope_fp8_quant.py:132-198 upstream) written for any
+    rotary width: its `native_fused_inv_rope_fp8_quant` fixes the width at 64, its `_reference_inv_rope` does not."""
+    half = rope // 2
+    sel = cs.index_select(0, pos)
+    cos = sel[:, :half].repeat_interleave(2, dim=-1).unsqueeze(1)
+    sin = -sel[:, half:].repeat_interleave(2, dim=-1).unsqueeze(1)
+    tail = o[..., nope:].float()
+    swapped = torch.stack((-tail[..., 1::2], tail[..., ::2]), dim=-1).flatten(-2)
+    rot = torch.cat((o[..., :nope], (tail * cos + swapped * sin).to(o.dtype)), dim=-1)
+    tokens, _, head_dim = rot.shape
+    blocks = rot.view(tokens, groups, hpg * head_dim // group, group).float()
+    scales = blocks.abs().amax(dim=-1).clamp(min=1e-10) * (1.0 / 448.0)
+    if packed:
+        scales = torch.exp2(torch.ceil(torch.log2(scales.clamp(min=1e-10))))
+    fp8 = (blocks / scales.unsqueeze(-1)).clamp(-448.0, 448.0).to(torch.float8_e4m3fn).reshape(tokens, groups, hpg * head_dim)
+    if packed:
+        codes = (scales.view(torch.int32) >> 23) & 0xFF
+        codes = codes.reshape(tokens, groups, hpg, head_dim // group)
+        scales = sum(codes[..., j] << (8 * j) for j in range(head_dim // group)).to(torch.int32)
+    return fp8.view(torch.uint8), scales
+
+
+@pytest.mark.parametrize("nope,rope,group", GEOMETRIES)
+@pytest.mark.parametrize("packed", [False, True])
+def test_oracle_follows_the_statement_for_other_geometries(nope, rope, group, packed):
+    if packed and (nope + rope) // group != 4:
+        pytest.skip("packed scales are defined for four groups per head only")
+    g = torch.Generator().manual_seed(nope + rope + group)
+    tokens, groups, hpg = 9, 2, 3
+    o = (torch.randn(tokens, groups * hpg, nope + rope, generator=g) * torch.logspace(-3, 2, tokens)[:, None, None]).to(torch.bfloat16)
+    pos = torch.randint(0, 512, (tokens,), generator=g)
+    cs = _cos_sin_any(512, rope)
+    want_fp8, want_scale = _statement_any(o, pos, cs, groups, hpg, nope, rope, group, packed)
+    fp8, scale = c_oracle.inv_rope_fp8_quant(o, pos, cs, groups, hpg, packed=packed, nope_dim=nope, rope_dim=rope, quant_group_size=group)
+    assert torch.equal(fp8, want_fp8)
+    assert torch.equal(scale.view(torch.int32), want_scale.contiguous().view(torch.int32))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("nope,rope,group", GEOMETRIES)
+@pytest.mark.parametrize("packed", [False, True])
+@pytest.mark.parametrize("tokens,heads,groups", [(1, 4, 2), (37, 12, 3), (130, 8, 8)])
+def test_other_geometries_match_the_oracle(nope, rope, group, packed, tokens, heads, groups):
+    """Every geometry the reference wrapper accepts runs (on a general kernel) and matches the oracle bit for bit,
+    fp8 bytes, scales, layout and the zeroed token padding of the scale storage."""
+    chunks = (nope + rope) // group
+    if packed and chunks != 4:
+        pytest.skip("packed scales are defined for four groups per head only")
+    g = torch.Generator().manual_seed(tokens * 7 + nope + group)
+    head_dim, hpg = nope + rope, heads // groups
+    o = (torch.randn(tokens, heads, head_dim, generator=g) * torch.logspace(-2, 2, tokens)[:, None, None]).to(torch.bfloat16)
+    pos = torch.randint(0, 512, (tokens,), generator=g)
+    cs = _cos_sin_any(512, rope)
+    fp8, scale = flaggems_vllm.fused_inv_rope_fp8_quant(o.to(DEV), pos.to(DEV), cs.to(DEV), groups, hpg, nope_dim=nope, rope_dim=rope,
+                                                        quant_group_size=group, tma_aligned_scales=packed)
+    want_fp8, want_scale = c_oracle.inv_rope_fp8_quant(o, pos, cs, groups, hpg, packed=packed, nope_dim=nope, rope_dim=rope,
+                                                       quant_group_size=group)
+    assert torch.equal(fp8.cpu().view(torch.uint8), want_fp8)
+    assert torch.equal(scale.cpu().contiguous().view(torch.int32), want_scale.view(torch.int32))
+    d = hpg * head_dim
+    assert fp8.shape == (tokens, groups, d) and fp8.stride() == (d, tokens * d, 1)
+    assert scale.shape == (tokens, groups, hpg if packed else hpg * chunks)
+    padded, k = (tokens + 3) // 4 * 4, scale.shape[2]
+    storage = torch.as_strided(scale, (groups, k, padded), (k * padded, padded, 1))
+    assert int((storage[:, :, tokens:].view(torch.int32) != 0).sum()) == 0
+
+
+@pytest.mark.gpu
+def test_unaligned_rows_of_the_deepseek_geometry_take_the_general_kernel():
+    """448 + 64 / 128 with rows that do not start on 16 bytes (a view one element into its storage)."""
+    g = torch.Generator().manual_seed(5)
+    flat = torch.randn(6 * 4 * 512 + 1, generator=g).to(torch.bfloat16)
+    pos = torch.randint(0, 4096, (6,), generator=g)
+    cs = workloads.cos_sin_table(4096)
+    view = flat.to(DEV)[1:].view(6, 4, 512)
+    assert view.data_ptr() % 16 != 0
+    fp8, scale = flaggems_vllm.fused_inv_rope_fp8_quant(view, pos.to(DEV), cs.to(DEV), 2, 2)
+    want_fp8, want_scale = c_oracle.inv_rope_fp8_quant(flat[1:].view(6, 4, 512), pos, cs, 2, 2)
+    assert torch.equal(fp8.cpu().view(torch.uint8), want_fp8) and torch.equal(scale.cpu().contiguous(), want_scale)
+
+
 @pytest.mark.gpu
 def test_strided_input_and_read_only():
     """o as a view with a larger token stride; o itself is not modified."""
