@@ -553,24 +553,26 @@ def measure_e2e(flaggems_vllm, w, args, dev, stream, sync_all, tokens_all_ranks)
            "ms_per_step": secs * 1e3, "chunk_tokens": 1024, "launches_per_step": pipe.launches,
            "note": "q/kv/slots/positions from pinned host memory, rewritten q back to the same pinned buffer; "
                    "K cache and cos/sin table device-resident"}
+    # What the host side of this box can move with no kernel and no pipeline at all: every rank copies half of its
+    # pinned q to the device while the other half comes back (then the halves swap), all ranks at once.  Beside
+    # it, what the staged pipeline moved per rank in the timed region above.  Equal figures mean the box's host
+    # memory / PCIe fabric is the limit of `e2e`, not the pipeline.
+    bare = bare_copy_rates(hq, w.q, dev, sync_all)
+    mine = torch.tensor([my_h2d / my_secs / 1e9, my_d2h / my_secs / 1e9, bare[0], bare[1], float(w.num_tokens)],
+                        dtype=torch.float64, device=dev)
+    every = [torch.zeros_like(mine) for _ in range(world)]
     if world > 1:
-        # What the host side of this box can move with no kernel and no pipeline at all: every rank copies half of its
-        # pinned q to the device while the other half comes back (then the halves swap), all ranks at once.  Beside
-        # it, what the staged pipeline moved per rank in the timed region above.  Equal figures mean the box's host
-        # memory / PCIe fabric is the limit of `e2e`, not the pipeline.
-        bare = bare_copy_rates(hq, w.q, dev, sync_all)
-        mine = torch.tensor([my_h2d / my_secs / 1e9, my_d2h / my_secs / 1e9, bare[0], bare[1], float(w.num_tokens)],
-                            dtype=torch.float64, device=dev)
-        every = [torch.zeros_like(mine) for _ in range(world)]
         dist.all_gather(every, mine)
-        rows = [[round(float(v), 2) for v in t.tolist()] for t in every]
-        out["staged_gbs_per_rank"] = [[r[0], r[1]] for r in rows]
-        out["bare_copy_gbs_per_rank"] = [[r[2], r[3]] for r in rows]
-        out["tokens_per_rank"] = [int(r[4]) for r in rows]
-        out["bare_copy_gbs_all_ranks"] = [round(sum(r[2] for r in rows), 1), round(sum(r[3] for r in rows), 1)]
-        out["staged_gbs_all_ranks"] = [round(h2d / secs / 1e9, 1), round(d2h / secs / 1e9, 1)]
-        out["bare_copy_note"] = ("[host->device, device->host] GB/s; bare = plain cudaMemcpyAsync of pinned q in both directions at "
-                                 "once on every rank at once, no kernel, measured after the timed region")
+    else:
+        every = [mine]
+    rows = [[round(float(v), 2) for v in t.tolist()] for t in every]
+    out["staged_gbs_per_rank"] = [[r[0], r[1]] for r in rows]
+    out["bare_copy_gbs_per_rank"] = [[r[2], r[3]] for r in rows]
+    out["tokens_per_rank"] = [int(r[4]) for r in rows]
+    out["bare_copy_gbs_all_ranks"] = [round(sum(r[2] for r in rows), 1), round(sum(r[3] for r in rows), 1)]
+    out["staged_gbs_all_ranks"] = [round(h2d / secs / 1e9, 1), round(d2h / secs / 1e9, 1)]
+    out["bare_copy_note"] = ("[host->device, device->host] GB/s; bare = plain cudaMemcpyAsync of pinned q in both directions at "
+                             "once on every rank at once, no kernel, measured after the timed region")
     return out
 
 

@@ -58,9 +58,12 @@ std::atomic<long long> g_bulk_wait_cycles{200000000LL};
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// `any_alignment`: where given, q and kv only need their element's 2-byte alignment and the table its 4 bytes, and
+// *any_alignment says whether the launch has to take the kernel for such pointers; where NULL, 16 bytes are required.
 int validate(const void* q, const void* kv, const void* k_cache, const int64_t* slot_mapping,
              const int64_t* position_ids, const float* cos_sin_cache, int64_t num_tokens, int64_t num_heads,
-             int64_t num_tokens_insert, int64_t cache_block_size, int64_t kv_block_stride_bytes) {
+             int64_t num_tokens_insert, int64_t cache_block_size, int64_t kv_block_stride_bytes, bool* any_alignment = nullptr) {
+    if (any_alignment) *any_alignment = false;
     if (num_tokens < 0 || num_heads < 0 || num_tokens_insert < 0 || num_tokens_insert > num_tokens)
         return DSV4_ERR_BAD_SIZE;
     if (num_tokens == 0) return DSV4_OK;
@@ -71,7 +74,11 @@ int validate(const void* q, const void* kv, const void* k_cache, const int64_t* 
         if (cache_block_size <= 0 || kv_block_stride_bytes < cache_block_size * (kTokenDataBytes + kScaleBytes))
             return DSV4_ERR_BAD_SIZE;
     }
-    if (!aligned16(q) || !aligned16(kv) || !aligned16(cos_sin_cache)) return DSV4_ERR_MISALIGNED;
+    if (!aligned16(q) || !aligned16(kv) || !aligned16(cos_sin_cache)) {
+        const auto low_bits = [](const void* p, uintptr_t mask) { return (reinterpret_cast<uintptr_t>(p) & mask) != 0; };
+        if (!any_alignment || low_bits(q, 1u) || low_bits(kv, 1u) || low_bits(cos_sin_cache, 3u)) return DSV4_ERR_MISALIGNED;
+        *any_alignment = true;
+    }
     // kernels index q rows and tokens with 32 bits (2^31 rows of 1 KiB are 2 TiB, beyond any GPU)
     if (num_tokens >= (1LL << 31) || num_heads >= (1LL << 31)) return DSV4_ERR_TOO_LARGE;
     if (num_heads > 0 && num_tokens > ((1LL << 31) - 1) / num_heads) return DSV4_ERR_TOO_LARGE;
@@ -117,12 +124,14 @@ int dsv4_qnorm_rope_kv_insert(void* q, const void* kv, void* k_cache, const int6
                               const int64_t* position_ids, const float* cos_sin_cache, float eps,
                               int64_t num_tokens, int64_t num_heads, int64_t num_tokens_insert,
                               int64_t cache_block_size, int64_t kv_block_stride_bytes, void* cuda_stream) {
+    bool any_alignment = false;
     const int rc = validate(q, kv, k_cache, slot_mapping, position_ids, cos_sin_cache, num_tokens, num_heads,
-                            num_tokens_insert, cache_block_size, kv_block_stride_bytes);
+                            num_tokens_insert, cache_block_size, kv_block_stride_bytes, &any_alignment);
     if (rc != DSV4_OK || num_tokens == 0) return rc;
     const PrologueParams p = make_params(q, kv, k_cache, slot_mapping, position_ids, cos_sin_cache, eps, num_tokens,
                                          num_heads, num_tokens_insert, cache_block_size, kv_block_stride_bytes);
     cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+    if (any_alignment) return static_cast<int>(launch_prologue_rows_any_alignment(p, stream));
     int variant = current_variant();
     if (variant == DSV4_VARIANT_AUTO) variant = DSV4_VARIANT_ROWS;
     const cudaError_t err = variant == DSV4_VARIANT_BULK ? launch_prologue_bulk(p, stream)

@@ -535,6 +535,7 @@ cudaError_t launch_inv_rope_fp8_quant_any(const void* o, int64_t o_stride_token,
                                           int64_t scale_stride_group, int64_t num_tokens, int64_t padded_tokens, int num_heads,
                                           int heads_per_group, int nope_dim, int rope_dim, int group_size, float eps, int packed,
                                           cudaStream_t stream);
+cudaError_t launch_prologue_rows_any_alignment(const PrologueParams& p, cudaStream_t stream);
 void count_launch();
 cudaError_t read_device_error(int* value);
 

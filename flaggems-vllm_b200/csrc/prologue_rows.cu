@@ -180,6 +180,76 @@ __global__ void __launch_bounds__(WARPS * 32, MIN_CTAS) prologue_rows_kernel(con
     }
 }
 
+// Any 2-byte alignment of q and kv (a contiguous view that starts a few elements into its storage) and any 4-byte
+// alignment of the table: the reference only asks for contiguous tensors.  One warp per row in a "pair" layout - lane l
+// holds the (even, odd) pairs l, l + 32, ..., l + 224 of the row, read and written with 2-byte accesses - so pair l + 224 is
+// the lane's rotary pair and the pairs l + 32g are one quantisation group g of a latent-KV row.  Same arithmetic as the
+// kernels above (the sum of squares is grouped differently, within the freedom the mean has anyway); cache bytes are
+// identical.  Only this plain form exists for such pointers: no range-checked and no out-of-place variant.
+template <int WARPS>
+__global__ void __launch_bounds__(WARPS * 32) prologue_rows_any_alignment_kernel(const PrologueParams p, const int64_t kv_ctas) {
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const bool is_kv = static_cast<int64_t>(blockIdx.x) < kv_ctas;
+    const int64_t r = (is_kv ? static_cast<int64_t>(blockIdx.x) : static_cast<int64_t>(blockIdx.x) - kv_ctas) * WARPS + warp;
+    int64_t token = r, slot = 0;
+    if (is_kv) {
+        if (r >= p.num_tokens_insert) return;
+        slot = p.slot_mapping[r];
+        if (slot < 0) return;
+    } else {
+        if (r >= p.num_tokens * p.num_heads) return;
+        token = r / p.num_heads;
+    }
+    const float* cs = p.cos_sin + p.position_ids[token] * kRopeDim;
+    const float c = cs[lane], sn = cs[32 + lane];
+    const uint16_t* in = reinterpret_cast<const uint16_t*>(is_kv ? p.kv : p.q) + r * (kRowBytes / 2);
+    float e[8], o[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) e[j] = bf16_lo(in[2 * (lane + 32 * j)]), o[j] = bf16_lo(in[2 * (lane + 32 * j) + 1]);
+    if (!is_kv) {
+        sumsq_t acc = sumsq_t(0);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+#if DSV4_EXACT_SUMSQ
+            acc = fma(static_cast<double>(o[j]), static_cast<double>(o[j]), fma(static_cast<double>(e[j]), static_cast<double>(e[j]), acc));
+#else
+            acc = fmaf(o[j], o[j], fmaf(e[j], e[j], acc));
+#endif
+        }
+        const float rr = inv_rms(warp_sum(acc), p.eps);
+        uint16_t* out = reinterpret_cast<uint16_t*>(p.q) + r * (kRowBytes / 2);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const uint32_t packed = static_cast<uint32_t>(in[2 * (lane + 32 * j)]) | (static_cast<uint32_t>(in[2 * (lane + 32 * j) + 1]) << 16);
+            const uint32_t y = j == 7 ? scale_rotate_pair(packed, rr, c, sn) : pack_bf16x2(__fmul_rn(e[j], rr), __fmul_rn(o[j], rr));
+            out[2 * (lane + 32 * j)] = static_cast<uint16_t>(y & 0xffffu);
+            out[2 * (lane + 32 * j) + 1] = static_cast<uint16_t>(y >> 16);
+        }
+        return;
+    }
+    const int64_t block = slot / p.block_size, in_block = slot - block * p.block_size;
+    uint8_t* base = p.k_cache + block * p.block_stride;
+    uint8_t* data = base + in_block * kTokenDataBytes;
+    uint8_t* scales = base + p.block_size * kTokenDataBytes + in_block * kScaleBytes;
+#pragma unroll
+    for (int g = 0; g < 7; ++g) {
+        float amax = fmaxf(fabsf(e[g]), fabsf(o[g]));
+#pragma unroll
+        for (int m = 16; m > 0; m >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
+        const uint32_t code = ue8m0_code(amax);
+        const float scale = __uint_as_float(code << 23);
+        const uint32_t bytes = pack_e4m3x4(__fdiv_rn(e[g], scale), __fdiv_rn(o[g], scale), 0.f, 0.f);
+        data[64 * g + 2 * lane] = static_cast<uint8_t>(bytes & 0xffu);
+        data[64 * g + 2 * lane + 1] = static_cast<uint8_t>((bytes >> 8) & 0xffu);
+        if (lane == 0) scales[g] = static_cast<uint8_t>(code);
+    }
+    if (lane == 0) scales[7] = 0;
+    const uint32_t rot = pack_bf16x2(__fsub_rn(__fmul_rn(e[7], c), __fmul_rn(o[7], sn)), __fadd_rn(__fmul_rn(e[7], sn), __fmul_rn(o[7], c)));
+#pragma unroll
+    for (int b = 0; b < 4; ++b) data[kNopeDim + 4 * lane + b] = static_cast<uint8_t>((rot >> (8 * b)) & 0xffu);
+}
+
 template <int RPW, int WARPS, int MIN_CTAS>
 cudaError_t launch(const PrologueParams& p, bool checked, cudaStream_t stream) {
     constexpr int TILE = RPW * WARPS;
@@ -228,6 +298,17 @@ cudaError_t launch_padded(const PrologueParams& p, cudaStream_t stream) {
 }
 
 }  // namespace
+
+cudaError_t launch_prologue_rows_any_alignment(const PrologueParams& p, cudaStream_t stream) {
+    constexpr int WARPS = 4;
+    const int64_t kv_ctas = (p.num_tokens_insert + WARPS - 1) / WARPS;
+    const int64_t grid = kv_ctas + (p.num_tokens * p.num_heads + WARPS - 1) / WARPS;
+    if (grid == 0) return cudaSuccess;
+    if (grid > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
+    prologue_rows_any_alignment_kernel<WARPS><<<static_cast<unsigned>(grid), WARPS * 32, 0, stream>>>(p, kv_ctas);
+    count_launch();
+    return cudaGetLastError();
+}
 
 cudaError_t launch_prologue_rows(const PrologueParams& p, bool checked, cudaStream_t stream) {
 #ifdef DSV4_ROWS_RPW

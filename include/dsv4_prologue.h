@@ -57,9 +57,10 @@ extern "C" {
  *   position_ids   int64 [num_tokens]; row index into cos_sin_cache
  *   cos_sin_cache  fp32 [max_pos, 64] = 32 cos | 32 sin
  * Nothing is bounds-checked on the device (as in the reference): slots and positions
- * must be in range.  q, kv and cos_sin_cache must be 16-byte aligned; k_cache may have
- * any alignment (a slower byte-store path is taken unless base and stride are
- * multiples of 16).
+ * must be in range.  With q, kv and cos_sin_cache on 16-byte boundaries the vectorised kernels run; q and kv on any
+ * 2-byte and cos_sin_cache on any 4-byte boundary (contiguous views that start inside their storage, which the
+ * reference accepts) run on a kernel with 2-byte accesses and the same results.  k_cache may have any alignment
+ * (a slower byte-store path is taken unless base and stride are multiples of 16).
  */
 int dsv4_qnorm_rope_kv_insert(void* q, const void* kv, void* k_cache, const int64_t* slot_mapping,
                               const int64_t* position_ids, const float* cos_sin_cache, float eps,

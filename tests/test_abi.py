@@ -66,8 +66,13 @@ def test_rejections_happen_before_any_launch():
     assert lib.dsv4_gather_dequant_k_cache(None, None, -1, None, 512, 64, 64 * 584, None) == -2
     assert lib.dsv4_gather_dequant_k_cache(None, None, 3, None, 512, 64, 64 * 584, None) == -1
     assert lib.dsv4_gather_dequant_k_cache(None, None, 0, None, 512, 64, 64 * 584, None) == 0
-    # misaligned q (fake non-null addresses are never dereferenced: validation fails first)
-    assert lib.dsv4_qnorm_rope_kv_insert(0x1008, 0x2000, 0x3000, 0x4000, 0x5000, 0x6000, 1e-6, 4, 8, 4, 64, 64 * 584, None) == -3
+    # q on an odd address, or a table off its 4-byte grid (fake non-null addresses are never dereferenced: validation
+    # fails first); q and kv may start on any even address, which takes the any-alignment kernel
+    assert lib.dsv4_qnorm_rope_kv_insert(0x1001, 0x2000, 0x3000, 0x4000, 0x5000, 0x6000, 1e-6, 4, 8, 4, 64, 64 * 584, None) == -3
+    assert lib.dsv4_qnorm_rope_kv_insert(0x1000, 0x2000, 0x3000, 0x4000, 0x5000, 0x6002, 1e-6, 4, 8, 4, 64, 64 * 584, None) == -3
+    # the range-checked and the out-of-place forms keep the 16-byte requirement
+    assert lib.dsv4_qnorm_rope_kv_insert_checked(0x1008, 0x2000, 0x3000, 0x4000, 0x5000, 0x6000, 1e-6, 4, 8, 4, 64, 64 * 584,
+                                                 100, 4096, 0x7000, None) == -3
     # cache block smaller than block_size * 584 bytes
     assert lib.dsv4_qnorm_rope_kv_insert(0x1000, 0x2000, 0x3000, 0x4000, 0x5000, 0x6000, 1e-6, 4, 8, 4, 64, 64 * 576, None) == -2
     assert _native.launch_count() == before

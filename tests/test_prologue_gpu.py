@@ -571,3 +571,23 @@ def test_every_launch_mode_and_table_staging_gives_the_oracle_result(staging, pd
         _native.set_table_staging(previous_staging)
         _native.set_pdl(previous_pdl)
     assert _native.set_table_staging(previous_staging) == previous_staging
+
+
+@pytest.mark.parametrize("q_off,kv_off,cs_off", [(1, 0, 0), (0, 3, 0), (0, 0, 1), (5, 7, 3), (4, 4, 2)])
+@pytest.mark.parametrize("n,h,bs", [(1, 1, 16), (19, 8, 64), (70, 33, 16)])
+def test_contiguous_views_that_do_not_start_on_16_bytes(variant, q_off, kv_off, cs_off, n, h, bs):
+    """The reference asks for contiguous tensors only (:320 there); a contiguous view may start any number of elements
+    into its storage (a slice of a fused projection's output).  q, kv and the table offset by q_off / kv_off / cs_off
+    elements: such calls take the any-alignment kernel, under either variant, and meet the same bars."""
+    q, kv, kc, slots, pos, cs = random_case(n, h, bs, n // bs + 2, seed=31 * n + q_off + kv_off, minus_one=n // 5)
+
+    def shifted(t, off):
+        flat = torch.empty(t.numel() + off, dtype=t.dtype, device=t.device)
+        view = flat[off:].view(t.shape)
+        view.copy_(t)
+        return view
+
+    q2, kv2, cs2 = shifted(q, q_off), shifted(kv, kv_off), shifted(cs, cs_off)
+    assert q2.is_contiguous() and kv2.is_contiguous() and cs2.is_contiguous()
+    assert any(t.data_ptr() % 16 for t in (q2, kv2, cs2))
+    run_and_check(q2, kv2, kc, slots, pos, cs2, 1e-6, bs)
