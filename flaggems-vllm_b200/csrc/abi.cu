@@ -519,7 +519,7 @@ const char* dsv4_error_string(int code) {
         case DSV4_OK: return "success";
         case DSV4_ERR_NULL_POINTER: return "a required pointer is NULL";
         case DSV4_ERR_BAD_SIZE: return "bad size (negative, num_tokens_insert > num_tokens, or cache block too small)";
-        case DSV4_ERR_MISALIGNED: return "q, kv, cos_sin_cache and out must be 16-byte aligned";
+        case DSV4_ERR_MISALIGNED: return "a pointer or stride is not aligned as this entry point requires (see include/dsv4_prologue.h)";
         case DSV4_ERR_BAD_VARIANT: return "unknown kernel variant";
         case DSV4_ERR_TOO_LARGE: return "size exceeds what this entry point supports";
         default: return code > 0 ? cudaGetErrorString(static_cast<cudaError_t>(code)) : "unknown dsv4 error";

@@ -24,7 +24,7 @@ extern "C" {
 #define DSV4_OK 0
 #define DSV4_ERR_NULL_POINTER (-1) /* a required pointer is NULL */
 #define DSV4_ERR_BAD_SIZE (-2)     /* negative size, num_tokens_insert > num_tokens, block too small */
-#define DSV4_ERR_MISALIGNED (-3)   /* q / kv / cos_sin_cache / out not 16-byte aligned */
+#define DSV4_ERR_MISALIGNED (-3)   /* a pointer or stride is not aligned as the entry point requires */
 #define DSV4_ERR_BAD_VARIANT (-4)  /* unknown kernel variant id */
 #define DSV4_ERR_TOO_LARGE (-5)    /* size exceeds what the entry point supports */
 
