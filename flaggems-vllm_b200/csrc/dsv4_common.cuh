@@ -349,8 +349,10 @@ enum : int { kDivideIeee = 0, kDivideFast = 1, kMultiplyReciprocal = 2 };
 // q can differ from RN(x/scale) in the last fp32 bit, but never in the e4m3 byte: a CPU test enumerates every bf16
 // group maximum (hence every reachable scale, for the reference's eps = 1e-10) against every bf16 value below it, for
 // each of the three values y can take (the correctly rounded reciprocal and its two neighbours) and both forms -
-// 1.6e9 cases each, zero differing bytes.  Callers pick the form once per warp (see all_scales_allow_two_term), so the
-// choice is a uniform branch around straight-line code.  For any other eps the kernels divide.
+// 1.6e9 cases each, zero differing bytes.  The form is a template argument: a caller that uses the two-term form votes once
+// per warp on the scales' range (`__all_sync`), so the choice is a uniform branch around straight-line code; the epilogue
+// quantiser uses the corrected form throughout (no second code path measured faster there).  For any other eps the
+// kernels divide.
 // kMultiplyReciprocal: x * RN(1/scale), what the statement of `act_quant` computes.
 constexpr float kTwoTermMaxScale = 0x1p100f;
 
@@ -377,16 +379,6 @@ struct ScaleDivider {
         return __fmaf_rn(__fmaf_rn(-scale, q0, x), recip, q0);
     }
 };
-
-// True in every lane iff every lane's scales are in the range of the two-term form (warp-uniform by construction).
-template <int MODE>
-__device__ __forceinline__ bool all_scales_allow_two_term(const ScaleDivider<MODE>& a) {
-    return MODE == kDivideFast && __all_sync(0xffffffffu, a.allows_two_term());
-}
-template <int MODE>
-__device__ __forceinline__ bool all_scales_allow_two_term(const ScaleDivider<MODE>& a, const ScaleDivider<MODE>& b, const ScaleDivider<MODE>& c) {
-    return MODE == kDivideFast && __all_sync(0xffffffffu, a.allows_two_term() && b.allows_two_term() && c.allows_two_term());
-}
 
 template <int MODE, bool TWO_TERM>
 __device__ __forceinline__ uint2 quant8_by(const uint4& v, const ScaleDivider<MODE>& d) {
