@@ -33,12 +33,18 @@ struct InvRopeParams {
 // every lane rotates exactly one pair with a cosine and sine it loaded once for the whole task.  The four
 // quantisation groups of 128 are: A lanes 0-15, A lanes 16-31, B lanes 0-15, and B lanes 16-23 together with T.
 constexpr int kHeadsPerTask = 16;
+#ifndef DSV4_INVROPE_UE8M0_CTAS
+#define DSV4_INVROPE_UE8M0_CTAS 8  // CTAs per SM of the UE8M0-scale instantiation (64 registers with two passes in flight)
+#endif
 #ifndef DSV4_INVROPE_FP32_CTAS
 #define DSV4_INVROPE_FP32_CTAS 9  // CTAs per SM of the fp32-scale instantiation (fixes its register budget)
 #endif
 
 // FASTDIV (fp32-scale mode only): see ScaleDivider.
-template <int WARPS, bool PACKED, bool FASTDIV, int U, int MIN_CTAS>
+// PREFETCH: two passes of U heads in flight - the loads of the next pass go out before the current one is worked on, so
+// a warp always has rows on their way while it computes.  Pays where the kernel waits for memory (UE8M0 scales: 267 ->
+// 257 us on 1 Mi rows at 8 CTAs per SM), not where it is bound by instruction issue (fp32 scales: 294 us either way).
+template <int WARPS, bool PACKED, bool FASTDIV, int U, int MIN_CTAS, bool PREFETCH>
 __global__ void __launch_bounds__(WARPS * 32, MIN_CTAS) inv_rope_fp8_quant_kernel(const InvRopeParams p, const uint32_t tasks_per_token,
                                                                       const uint32_t tpt_mul, const uint32_t tpt_shift) {
     const int lane = threadIdx.x & 31;
@@ -64,20 +70,24 @@ __global__ void __launch_bounds__(WARPS * 32, MIN_CTAS) inv_rope_fp8_quant_kerne
     const float* cs = p.cos_sin + p.positions[token] * p.cos_sin_stride;
     const float c = cs[lane], sn = cs[32 + lane];
     const uint8_t* in_token = p.o + static_cast<int64_t>(token) * p.o_stride_token * 2;
-    for (int h0 = head_begin; h0 < head_end; h0 += U) {
-        uint4 a[U], b[U];
-        uint32_t tail[U];
+    uint4 a[U], b[U], a_next[U], b_next[U];
+    uint32_t tail[U], tail_next[U];
+    const auto load_pass = [&](int h0, uint4 (&ra)[U], uint4 (&rb)[U], uint32_t (&rt)[U]) {
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-            a[u] = b[u] = make_uint4(0u, 0u, 0u, 0u);
-            tail[u] = 0u;
+            ra[u] = rb[u] = make_uint4(0u, 0u, 0u, 0u);
+            rt[u] = 0u;
             if (h0 + u < head_end) {
                 const uint8_t* in = in_token + (h0 + u) * p.o_stride_head * 2;
-                a[u] = ld_stream16(in + 16 * lane);
-                if (lane < kFirstRopeLane) b[u] = ld_stream16(in + 512 + 16 * lane);
-                tail[u] = ld_stream4(in + 2 * kNopeDim + 4 * lane);
+                ra[u] = ld_stream16(in + 16 * lane);
+                if (lane < kFirstRopeLane) rb[u] = ld_stream16(in + 512 + 16 * lane);
+                rt[u] = ld_stream4(in + 2 * kNopeDim + 4 * lane);
             }
         }
+    };
+    load_pass(head_begin, a, b, tail);
+    for (int h0 = head_begin; h0 < head_end; h0 += U) {
+        if (PREFETCH) load_pass(h0 + U, a_next, b_next, tail_next);  // past the last head of the task: nothing is loaded
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             const int head = h0 + u;
@@ -134,6 +144,12 @@ __global__ void __launch_bounds__(WARPS * 32, MIN_CTAS) inv_rope_fp8_quant_kerne
                     *reinterpret_cast<float*>(scale_row + (k + 2) * p.padded_tokens * 4) = sb;  // lane 16: sb is s3
                 }
             }
+        }
+        if (PREFETCH) {
+#pragma unroll
+            for (int u = 0; u < U; ++u) a[u] = a_next[u], b[u] = b_next[u], tail[u] = tail_next[u];
+        } else {
+            load_pass(h0 + U, a, b, tail);
         }
     }
 }
@@ -260,11 +276,11 @@ cudaError_t launch_inv_rope_fp8_quant(const void* o, int64_t o_stride_token, int
     make_fast_divisor(static_cast<uint32_t>(tasks_per_token), &tpt_mul, &tpt_shift);
     const unsigned g = static_cast<unsigned>(grid);
     const uint32_t tpt = static_cast<uint32_t>(tasks_per_token);
-    // Heads in flight per warp (2) and CTAs per SM, measured on 1 Mi rows: UE8M0 mode 10 CTAs (48 registers) 268 us
-    // against 280 us at 8; fp32-scale mode 9 CTAs (56 registers) 294 us, the same at 10, 306 us at 8.
-    if (packed) inv_rope_fp8_quant_kernel<WARPS, true, false, 2, 10><<<g, WARPS * 32, 0, stream>>>(p, tpt, tpt_mul, tpt_shift);
-    else if (eps == 1e-10f) inv_rope_fp8_quant_kernel<WARPS, false, true, 2, DSV4_INVROPE_FP32_CTAS><<<g, WARPS * 32, 0, stream>>>(p, tpt, tpt_mul, tpt_shift);
-    else inv_rope_fp8_quant_kernel<WARPS, false, false, 2, 8><<<g, WARPS * 32, 0, stream>>>(p, tpt, tpt_mul, tpt_shift);
+    // Heads in flight per warp and CTAs per SM, measured on 1 Mi rows: UE8M0 mode with two passes of 2 heads in flight
+    // 8 CTAs (64 registers) 257 us, 7 CTAs 259 us, 10 CTAs (spills) 394 us, one pass in flight at 10 CTAs 265-268 us; fp32-scale mode 9 CTAs (56 registers) 294 us, the same at 10, 306 us at 8.
+    if (packed) inv_rope_fp8_quant_kernel<WARPS, true, false, 2, DSV4_INVROPE_UE8M0_CTAS, true><<<g, WARPS * 32, 0, stream>>>(p, tpt, tpt_mul, tpt_shift);
+    else if (eps == 1e-10f) inv_rope_fp8_quant_kernel<WARPS, false, true, 2, DSV4_INVROPE_FP32_CTAS, false><<<g, WARPS * 32, 0, stream>>>(p, tpt, tpt_mul, tpt_shift);
+    else inv_rope_fp8_quant_kernel<WARPS, false, false, 2, 8, false><<<g, WARPS * 32, 0, stream>>>(p, tpt, tpt_mul, tpt_shift);
     count_launch();
     return cudaGetLastError();
 }
