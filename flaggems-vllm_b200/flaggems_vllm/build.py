@@ -1,7 +1,8 @@
 """Builds the CUDA libraries in place with nvcc for sm_100a: `python -m flaggems_vllm.build`.
 
   libdsv4_prologue.so            the operators (the product)
-  testing/libdsv4_hbm_probe.so   the bandwidth probe the benchmark compares the kernels with (a measurement aid)
+  testing/libdsv4_hbm_probe.so   aids: the bandwidth probe the benchmark compares the kernels with, and the on-device
+                                 check of the quantisers' division shortcut that a test runs
 
 Cross-compiles without a GPU.  The CUDA runtime is linked statically so the libraries
 load (and export their symbols) on a machine that has no driver.
@@ -18,7 +19,7 @@ PKG = Path(__file__).resolve().parent
 CSRC = PKG.parent / "csrc"
 OUT = PKG / "libdsv4_prologue.so"
 PROBE_OUT = PKG / "testing" / "libdsv4_hbm_probe.so"
-PROBE_SOURCES = ("hbm_probe.cu",)
+PROBE_SOURCES = ("hbm_probe.cu", "division_probe.cu")
 SOURCES = ("abi.cu", "prologue_rows.cu", "prologue_bulk.cu", "gather_dequant.cu", "q_kv_rmsnorm.cu", "inv_rope_fp8_quant.cu", "indexer_k_quant.cu",
            "indexer_q_rope_quant.cu", "cp_gather_indexer.cu", "topk_indices.cu", "topk_per_row.cu", "topk_per_row_short.cu", "group_quant_fp8.cu")
 HEADERS = ("dsv4_common.cuh", "../../include/dsv4_prologue.h", "../../include/dsv4_hbm_probe.h")

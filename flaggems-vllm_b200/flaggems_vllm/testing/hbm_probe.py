@@ -17,8 +17,18 @@ def lib() -> ctypes.CDLL:
         L = ctypes.CDLL(str(LIB_PATH))
         L.dsv4_hbm_probe.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p]
         L.dsv4_hbm_probe.restype = ctypes.c_int
+        L.dsv4_division_probe.argtypes = [ctypes.c_float, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p]
+        L.dsv4_division_probe.restype = ctypes.c_int
         _lib = L
     return _lib
+
+
+def division_probe(eps: float, form: int, counts_ptr: int, stream: int) -> None:
+    """Launch the on-device check of the division shortcut (see dsv4_division_probe); `counts_ptr` -> three zeroed
+    64-bit words on the device: pairs examined, differing e4m3 bytes, reciprocals more than one ulp off."""
+    code = lib().dsv4_division_probe(float(eps), int(form), counts_ptr, stream)
+    if code != 0:
+        raise RuntimeError(f"dsv4_division_probe failed with code {code}")
 
 
 def probe(mode: int, buffer_ptr: int, rows: int, stream: int) -> None:

@@ -56,6 +56,23 @@ def test_division_shortcut_never_changes_a_byte(form, y_ulps):
     assert pairs > enough and byte_mismatches == 0
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("form", [2, 3])
+@pytest.mark.parametrize("eps_rounded_to_bf16", [False, True])
+def test_division_shortcut_on_the_device_itself(form, eps_rounded_to_bf16):
+    """The same enumeration as the CPU proof above, run by the GPU with its own approximate reciprocal: every bf16 group
+    maximum against every bf16 value below it - no e4m3 byte differs from the IEEE quotient's, and the refined reciprocal
+    is within one unit in the last place of the correctly rounded one for every scale (the premise of the CPU proof)."""
+    from flaggems_vllm.testing import hbm_probe
+
+    eps = float(torch.tensor(1e-10).to(torch.bfloat16)) if eps_rounded_to_bf16 else 1e-10
+    counts = torch.zeros(3, dtype=torch.int64, device=DEV)
+    hbm_probe.division_probe(eps, form, counts.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    pairs, byte_mismatches, reciprocals_off = counts.cpu().tolist()
+    assert pairs > (4.5e8 if form == 2 else 5.3e8)
+    assert byte_mismatches == 0 and reciprocals_off == 0
+
+
 @pytest.mark.parametrize("packed", [False, True])
 @pytest.mark.parametrize("name", NAMES)
 def test_oracle_reproduces_upstream_reference(name, packed):
