@@ -34,16 +34,16 @@ struct InvRopeParams {
 // quantisation groups of 128 are: A lanes 0-15, A lanes 16-31, B lanes 0-15, and B lanes 16-23 together with T.
 constexpr int kHeadsPerTask = 16;
 #ifndef DSV4_INVROPE_UE8M0_CTAS
-#define DSV4_INVROPE_UE8M0_CTAS 8  // CTAs per SM of the UE8M0-scale instantiation (64 registers with two passes in flight)
+#define DSV4_INVROPE_UE8M0_CTAS 7  // CTAs per SM of the UE8M0-scale instantiation (72 registers with two passes in flight)
 #endif
 #ifndef DSV4_INVROPE_FP32_CTAS
-#define DSV4_INVROPE_FP32_CTAS 9  // CTAs per SM of the fp32-scale instantiation (fixes its register budget)
+#define DSV4_INVROPE_FP32_CTAS 8  // CTAs per SM of the fp32-scale instantiation (64 registers with two passes in flight)
 #endif
 
 // FASTDIV (fp32-scale mode only): see ScaleDivider.
 // PREFETCH: two passes of U heads in flight - the loads of the next pass go out before the current one is worked on, so
-// a warp always has rows on their way while it computes.  Pays where the kernel waits for memory (UE8M0 scales: 267 ->
-// 257 us on 1 Mi rows at 8 CTAs per SM), not where it is bound by instruction issue (fp32 scales: 294 us either way).
+// a warp always has rows on their way while it computes (UE8M0 scales: 267 -> 256 us on 1 Mi rows; fp32 scales, once the
+// per-head address arithmetic was reduced to increments: 272 -> 269 us).
 template <int WARPS, bool PACKED, bool FASTDIV, int U, int MIN_CTAS, bool PREFETCH>
 __global__ void __launch_bounds__(WARPS * 32, MIN_CTAS) inv_rope_fp8_quant_kernel(const InvRopeParams p, const uint32_t tasks_per_token,
                                                                       const uint32_t tpt_mul, const uint32_t tpt_shift) {
@@ -85,6 +85,18 @@ __global__ void __launch_bounds__(WARPS * 32, MIN_CTAS) inv_rope_fp8_quant_kerne
             }
         }
     };
+    // Output addresses advance by constants from one head to the next and are recomputed only where a new group of heads
+    // begins: `out` = the head's 512 e4m3 bytes, `scale_at` = its first scale (this lane's half of the four in fp32 mode).
+    int group = static_cast<int>(fast_div(static_cast<uint32_t>(head_begin), p.hpg_mul, p.hpg_shift));
+    int head_in_group = head_begin - group * p.heads_per_group;
+    const int64_t group_bytes = static_cast<int64_t>(p.heads_per_group) * (kRowBytes / 2);
+    const int64_t scale_column = p.padded_tokens * 4;                       // bytes between scale columns of one token
+    const int64_t scale_step = PACKED ? scale_column : 4 * scale_column;    // ... between consecutive heads
+    const int64_t lane_scale = PACKED ? 0 : (lane >> 4) * scale_column;     // fp32: lanes 0 / 16 store groups 0,2 / 1,3
+    const auto group_out = [&](int g) { return p.fp8 + (static_cast<int64_t>(g) * p.num_tokens + token) * group_bytes; };
+    const auto group_scale = [&](int g) { return p.scale + (g * p.scale_stride_group + token) * 4 + lane_scale; };
+    uint8_t* out = group_out(group) + static_cast<int64_t>(head_in_group) * (kRowBytes / 2);
+    uint8_t* scale_at = group_scale(group) + head_in_group * scale_step;
     load_pass(head_begin, a, b, tail);
     for (int h0 = head_begin; h0 < head_end; h0 += U) {
         if (PREFETCH) load_pass(h0 + U, a_next, b_next, tail_next);  // past the last head of the task: nothing is loaded
@@ -113,11 +125,6 @@ __global__ void __launch_bounds__(WARPS * 32, MIN_CTAS) inv_rope_fp8_quant_kerne
             const float m3 = lane >= 16 ? mb : bf16_hi(both_other);
             const float sa = __fmul_rn(fmaxf(ma, p.eps), 1.0f / 448.0f), sb = __fmul_rn(fmaxf(mb, p.eps), 1.0f / 448.0f);
             const float s3 = __fmul_rn(fmaxf(m3, p.eps), 1.0f / 448.0f);
-            const int group = static_cast<int>(fast_div(static_cast<uint32_t>(head), p.hpg_mul, p.hpg_shift));
-            const int head_in_group = head - group * p.heads_per_group;
-            uint8_t* scale_row = p.scale + (group * p.scale_stride_group + token) * 4;
-            uint8_t* out = p.fp8 + (static_cast<int64_t>(group) * p.num_tokens + token) * (static_cast<int64_t>(p.heads_per_group) * kRowBytes / 2) +
-                           static_cast<int64_t>(head_in_group) * (kRowBytes / 2);
             if (PACKED) {
                 const uint32_t code_a = pow2_ceil_code(sa), code_b = pow2_ceil_code(sb), code_3 = pow2_ceil_code(s3);
                 st_global8(out + 8 * lane, quant8_pow2(a[u], code_a));
@@ -128,7 +135,7 @@ __global__ void __launch_bounds__(WARPS * 32, MIN_CTAS) inv_rope_fp8_quant_kerne
                 // chunk k of the head in byte k: lane 0 holds the codes of groups 0 and 2, lane 16 those of 1 and 3
                 const uint32_t mine = code_a | (code_b << 16);
                 const uint32_t word = mine | (__shfl_xor_sync(0xffffffffu, mine, 16) << 8);
-                if (lane == 0) *reinterpret_cast<uint32_t*>(scale_row + head_in_group * p.padded_tokens * 4) = word;
+                if (lane == 0) *reinterpret_cast<uint32_t*>(scale_at) = word;
             } else {
                 // the three-instruction form of the fast division for every scale: measured here, a warp-uniform choice
                 // between it and the two-instruction form was no faster (296 us against 294 us on 1 Mi rows)
@@ -139,10 +146,15 @@ __global__ void __launch_bounds__(WARPS * 32, MIN_CTAS) inv_rope_fp8_quant_kerne
                 *reinterpret_cast<uint16_t*>(out + kNopeDim + 2 * lane) = static_cast<uint16_t>(
                     pack_e4m3x4(by_3.template quotient<false>(te), by_3.template quotient<false>(to), 0.f, 0.f));
                 if ((lane & 15) == 0) {
-                    const int k = head_in_group * 4 + (lane >> 4);
-                    *reinterpret_cast<float*>(scale_row + k * p.padded_tokens * 4) = sa;
-                    *reinterpret_cast<float*>(scale_row + (k + 2) * p.padded_tokens * 4) = sb;  // lane 16: sb is s3
+                    *reinterpret_cast<float*>(scale_at) = sa;
+                    *reinterpret_cast<float*>(scale_at + 2 * scale_column) = sb;  // lane 16: sb is s3
                 }
+            }
+            // on to the next head
+            out += kRowBytes / 2, scale_at += scale_step;
+            if (++head_in_group == p.heads_per_group) {
+                head_in_group = 0, ++group;
+                out = group_out(group), scale_at = group_scale(group);
             }
         }
         if (PREFETCH) {
@@ -276,10 +288,12 @@ cudaError_t launch_inv_rope_fp8_quant(const void* o, int64_t o_stride_token, int
     make_fast_divisor(static_cast<uint32_t>(tasks_per_token), &tpt_mul, &tpt_shift);
     const unsigned g = static_cast<unsigned>(grid);
     const uint32_t tpt = static_cast<uint32_t>(tasks_per_token);
-    // Heads in flight per warp and CTAs per SM, measured on 1 Mi rows: UE8M0 mode with two passes of 2 heads in flight
-    // 8 CTAs (64 registers) 257 us, 7 CTAs 259 us, 10 CTAs (spills) 394 us, one pass in flight at 10 CTAs 265-268 us; fp32-scale mode 9 CTAs (56 registers) 294 us, the same at 10, 306 us at 8.
+    // Heads in flight per warp and CTAs per SM, measured on 1 Mi rows.  UE8M0 mode, two passes of 2 heads in flight: 7 CTAs
+    // (72 registers) 256 us, 8 CTAs (64 registers, 8 bytes spilled) 257 us, 6 CTAs 262 us; one pass in flight at 10 CTAs
+    // 265-282 us.  fp32-scale mode: two passes at 8 CTAs (64 registers) 269 us, at 7 CTAs 270 us; one pass at 10 CTAs
+    // (48 registers) 272 us, at 9 CTAs 274 us, at 11 CTAs 301 us.
     if (packed) inv_rope_fp8_quant_kernel<WARPS, true, false, 2, DSV4_INVROPE_UE8M0_CTAS, true><<<g, WARPS * 32, 0, stream>>>(p, tpt, tpt_mul, tpt_shift);
-    else if (eps == 1e-10f) inv_rope_fp8_quant_kernel<WARPS, false, true, 2, DSV4_INVROPE_FP32_CTAS, false><<<g, WARPS * 32, 0, stream>>>(p, tpt, tpt_mul, tpt_shift);
+    else if (eps == 1e-10f) inv_rope_fp8_quant_kernel<WARPS, false, true, 2, DSV4_INVROPE_FP32_CTAS, true><<<g, WARPS * 32, 0, stream>>>(p, tpt, tpt_mul, tpt_shift);
     else inv_rope_fp8_quant_kernel<WARPS, false, false, 2, 8, false><<<g, WARPS * 32, 0, stream>>>(p, tpt, tpt_mul, tpt_shift);
     count_launch();
     return cudaGetLastError();
