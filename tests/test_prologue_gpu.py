@@ -591,3 +591,38 @@ def test_contiguous_views_that_do_not_start_on_16_bytes(variant, q_off, kv_off, 
     assert q2.is_contiguous() and kv2.is_contiguous() and cs2.is_contiguous()
     assert any(t.data_ptr() % 16 for t in (q2, kv2, cs2))
     run_and_check(q2, kv2, kc, slots, pos, cs2, 1e-6, bs)
+
+
+@pytest.mark.parametrize("mode", [0, 1, 2])
+def test_graph_capture_with_a_cross_stream_join_in_front(mode):
+    """The operator captured right behind a join of two streams (kv produced on a side stream, q on the capturing one):
+    in the dependent-launch modes the launch carries the programmatic-serialization attribute, which must degrade to an
+    ordinary dependency where the node in front is not a kernel of the same stream.  Replayed twice, exact both times."""
+    q0, kv0, kc0, slots, pos, cs = random_case(150, 12, 64, 6, seed=91)
+    q_ref, kc_ref = oracle_of(q0, kv0, kc0, slots, pos, cs, 1e-6, 64)
+    q, kv, kc = torch.zeros_like(q0), torch.zeros_like(kv0), kc0.clone()
+    previous = _native.set_pdl(mode)
+    try:
+        main, side = torch.cuda.Stream(), torch.cuda.Stream()
+        main.wait_stream(torch.cuda.current_stream())
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(main):
+            op(q0.clone(), kv0, kc0.clone(), slots, pos, cs, 1e-6, 64)  # warm-up outside the capture
+            main.synchronize()
+            with torch.cuda.graph(graph, stream=main):
+                side.wait_stream(main)
+                with torch.cuda.stream(side):
+                    kv.copy_(kv0)
+                q.copy_(q0)
+                main.wait_stream(side)
+                op(q, kv, kc, slots, pos, cs, 1e-6, 64)
+        for _ in range(2):
+            q.zero_(), kv.zero_(), kc.copy_(kc0)
+            torch.cuda.synchronize()
+            graph.replay()
+            torch.cuda.synchronize()
+            assert torch.equal(kc.cpu(), kc_ref)
+            compare.assert_q_close(q.cpu(), q_ref)
+    finally:
+        _native.set_pdl(previous)
+    assert _native.device_error() == 0
